@@ -1,0 +1,217 @@
+"""Oracle (test infrastructure): expert computation of the fused-MoE path on CPU.
+
+All GEMMs are fp32 ``torch.matmul`` on up-cast operands; values are rounded to
+the activation dtype at exactly the points where the reference materialises a
+tensor.  Nothing here is imported by the product path.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import quant as Q
+from . import routing as R
+
+
+def _rb(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """Round to ``dtype`` (round-to-nearest-even) and come back to fp32."""
+    if dtype == torch.float32:
+        return x
+    return x.to(dtype).to(torch.float32)
+
+
+def silu_and_mul(y1: torch.Tensor, dtype: torch.dtype | None = None) -> torch.Tensor:
+    """out[r,c] = (g / (1 + exp(-g))) * u, g = y1[r,c], u = y1[r,I+c], fp32 math.
+
+    Restates ref:src/flaggems_sglang/ops/fused_moe.py:58-62 (gate = first half,
+    up = second half; the result is stored in the input dtype, :63).
+    """
+    dtype = y1.dtype if dtype is None else dtype
+    f = y1.to(torch.float32)
+    half = f.shape[-1] // 2
+    g, u = f[..., :half], f[..., half:]
+    return ((g / (1.0 + torch.exp(-g))) * u).to(dtype)
+
+
+def _expert_segments(hist):
+    offs = np.concatenate(([0], np.cumsum(hist)))
+    return [(e, int(offs[e]), int(offs[e + 1])) for e in range(len(hist)) if hist[e] > 0]
+
+
+def reference_fused_experts(
+    x: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    routing: dict,
+    apply_router_weight_on_input: bool = False,
+    no_combine: bool = False,
+) -> torch.Tensor:
+    """The reference op on its own layouts: w1 [E,H,2I], w2 [E,I,H], routing tables.
+
+    Restates ref:src/flaggems_sglang/ops/fused_moe.py:197-232 together with the
+    behaviour of the two grouped-GEMM calls it makes:
+      GEMM1 (:205-212)  Y1[p] = rb((x[topk_indx[p]//k] @ w1[e(p)]) * gamma_in[p])
+                        gather by ``//k`` TK:matmul_ogs_details/_matmul_ogs.py:198,
+                        fp32 accumulate :354, epilogue acc -> *gamma -> round :384-429
+      act   (:214-218)  A = rb(silu(Y1[:, :I]) * Y1[:, I:])
+      GEMM2 (:224-231)  Z[p] = rb((A[p] @ w2[e(p)]) * gamma_out[p]) into a scratch
+                        in the activation dtype (TK:matmul_ogs.py:168-170)
+      combine           out[t] = rb(sum_j f32(Z[gate_indx[t*k+j]])), j ascending,
+                        sequential fp32 adds (TK:matmul_ogs_details/_reduce_grouped.py:51-71)
+    ``no_combine`` (scatter_indx=None, ref:...:371,408-413) returns Z in sorted order.
+    """
+    dtype = x.dtype
+    k = routing["n_expts_act"]
+    T, H = x.shape
+    M = T * k
+    xf = x.detach().cpu().to(torch.float32)
+    topk_indx = torch.from_numpy(routing["topk_indx"].astype(np.int64))
+    gate_indx = torch.from_numpy(routing["gate_indx"].astype(np.int64))
+    gate_scal = torch.from_numpy(np.asarray(routing["gate_scal"], dtype=np.float32))
+    tok = topk_indx // k
+    Z = torch.zeros(M, H, dtype=torch.float32)
+    for e, lo, hi in _expert_segments(routing["hist"]):
+        rows = tok[lo:hi]
+        acc1 = xf[rows] @ w1[e].detach().cpu().to(torch.float32)
+        if apply_router_weight_on_input:
+            acc1 = acc1 * gate_scal[lo:hi, None]
+        y1 = _rb(acc1, dtype)
+        a = silu_and_mul(y1, dtype).to(torch.float32)
+        acc2 = a @ w2[e].detach().cpu().to(torch.float32)
+        if not apply_router_weight_on_input:
+            acc2 = acc2 * gate_scal[lo:hi, None]
+        Z[lo:hi] = _rb(acc2, dtype)
+    if no_combine:
+        return Z.to(dtype)
+    out = torch.zeros(T, H, dtype=torch.float32)
+    zs = Z[gate_indx].view(T, k, H)
+    for j in range(k):
+        out = out + zs[:, j]
+    return out.to(dtype)
+
+
+def fused_experts(
+    x: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    apply_router_weight_on_input: bool = False,
+    no_combine: bool = False,
+    routed_scaling_factor: float | None = None,
+) -> torch.Tensor:
+    """Same computation on the serving-side layouts: w1 [E,2I,H], w2 [E,H,I].
+
+    These layouts are the per-expert transposes of the reference op's
+    (ref:src/flaggems_sglang/ops/fused_moe.py:342-343); rows [0,I) of w1 are the
+    gate projection and [I,2I) the up projection, consistent with :58-62.
+    Slots keep the order of ``topk_ids``; Z is indexed by flat slot t*k+j and
+    the combine sums j = 0..k-1 in fp32 (``no_combine`` returns Z as [T,k,H]).
+    ``routed_scaling_factor`` multiplies the combined output afterwards
+    (ref:...:415-420).  Ids outside [0,E) contribute nothing.
+    """
+    dtype = x.dtype
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E = w1.shape[0]
+    xf = x.detach().cpu().to(torch.float32)
+    ids = topk_ids.detach().cpu().to(torch.int64).reshape(-1)
+    wts = topk_weights.detach().cpu().to(torch.float32).reshape(-1)
+    Z = torch.zeros(T * k, H, dtype=torch.float32)
+    for e in range(E):
+        slots = torch.nonzero(ids == e).reshape(-1)
+        if slots.numel() == 0:
+            continue
+        acc1 = xf[slots // k] @ w1[e].detach().cpu().to(torch.float32).t()
+        if apply_router_weight_on_input:
+            acc1 = acc1 * wts[slots, None]
+        y1 = _rb(acc1, dtype)
+        a = silu_and_mul(y1, dtype).to(torch.float32)
+        acc2 = a @ w2[e].detach().cpu().to(torch.float32).t()
+        if not apply_router_weight_on_input:
+            acc2 = acc2 * wts[slots, None]
+        Z[slots] = _rb(acc2, dtype)
+    if no_combine:
+        return Z.view(T, k, H).to(dtype)
+    out = moe_sum(Z.view(T, k, H))
+    if routed_scaling_factor is not None and routed_scaling_factor != 1.0:
+        out = _rb(out, dtype) * routed_scaling_factor
+    return out.to(dtype)
+
+
+def moe_sum(z: torch.Tensor) -> torch.Tensor:
+    """out[t] = sum_j z[t,j], sequential fp32 adds in ascending j; returns fp32."""
+    zf = z.detach().cpu().to(torch.float32)
+    out = torch.zeros(zf.shape[0], zf.shape[2], dtype=torch.float32)
+    for j in range(zf.shape[1]):
+        out = out + zf[:, j]
+    return out
+
+
+def fused_experts_fp8(
+    x: torch.Tensor,
+    w1_q: torch.Tensor,
+    w1_scale: torch.Tensor,
+    w2_q: torch.Tensor,
+    w2_scale: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    no_combine: bool = False,
+    routed_scaling_factor: float | None = None,
+) -> torch.Tensor:
+    """w8a8 block-quant experts: e4m3 weights with 128x128 scales, activations
+    quantised per token per 128 channels before each GEMM.
+
+    Builder-defined contract (the reference rejects fp8): quantise x ->
+    GEMM1 on de-quantised operands in fp32 -> silu*mul in fp32 -> quantise ->
+    GEMM2 -> * top-k weight -> round to bf16 -> combine as in ``fused_experts``.
+    """
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E = w1_q.shape[0]
+    xq, xs = Q.quant_act_group128(x)
+    xf = Q.dequant_act_group128(xq, xs)
+    ids = topk_ids.detach().cpu().to(torch.int64).reshape(-1)
+    wts = topk_weights.detach().cpu().to(torch.float32).reshape(-1)
+    Z = torch.zeros(T * k, H, dtype=torch.float32)
+    for e in range(E):
+        slots = torch.nonzero(ids == e).reshape(-1)
+        if slots.numel() == 0:
+            continue
+        w1f = Q.dequant_weight_block128(w1_q[e], w1_scale[e])
+        w2f = Q.dequant_weight_block128(w2_q[e], w2_scale[e])
+        acc1 = xf[slots // k] @ w1f.t()
+        a = silu_and_mul(acc1, torch.float32)
+        aq, as_ = Q.quant_act_group128(a)
+        af = Q.dequant_act_group128(aq, as_)
+        acc2 = (af @ w2f.t()) * wts[slots, None]
+        Z[slots] = _rb(acc2, torch.bfloat16)
+    if no_combine:
+        return Z.view(T, k, H).to(torch.bfloat16)
+    out = moe_sum(Z.view(T, k, H))
+    if routed_scaling_factor is not None and routed_scaling_factor != 1.0:
+        out = _rb(out, torch.bfloat16) * routed_scaling_factor
+    return out.to(torch.bfloat16)
+
+
+def dense_moe(x, w1, w2, topk_weights, topk_ids) -> torch.Tensor:
+    """Independent per-token formulation in fp32 with no intermediate rounding;
+    used only to cross-check the restatements above (w1 [E,2I,H], w2 [E,H,I])."""
+    xf = x.detach().cpu().to(torch.float32)
+    T, H = xf.shape
+    k = topk_ids.shape[1]
+    out = torch.zeros(T, H, dtype=torch.float32)
+    for t in range(T):
+        for j in range(k):
+            e = int(topk_ids[t, j])
+            y = w1[e].detach().cpu().to(torch.float32) @ xf[t]
+            half = y.shape[0] // 2
+            a = torch.nn.functional.silu(y[:half]) * y[half:]
+            out[t] += float(topk_weights[t, j]) * (w2[e].detach().cpu().to(torch.float32) @ a)
+    return out
+
+
+def fused_moe(x, w1, w2, gating_output, topk: int, renormalize: bool = True, **kw):
+    """router (softmax top-k) -> fused_experts."""
+    w, ids = R.softmax_topk(gating_output, topk, renormalize)
+    return fused_experts(x, w1, w2, w, ids, **kw)

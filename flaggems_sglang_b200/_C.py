@@ -1,0 +1,120 @@
+"""ctypes binding of libfmoe_b200.so (the C ABI declared in include/fmoe_b200.h).
+
+There is no CPU implementation behind these ops: a missing library or a call
+without a CUDA device raises instead of falling back.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+
+import torch  # noqa: F401  (loads the CUDA runtime the library links against)
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfmoe_b200.so")
+
+OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_TIMEOUT = 0, 1, 2, 3, 4
+F32, BF16, E4M3 = 0, 1, 2
+VARIANT_AUTO, VARIANT_SIMT, VARIANT_STREAM, VARIANT_TCGEN05 = 0, 1, 2, 3
+VARIANTS = {"auto": 0, "simt": 1, "stream": 2, "tcgen05": 3}
+
+DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float8_e4m3fn: E4M3}
+
+
+class FmoeError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"fmoe_b200 error {code}: {msg}")
+        self.code = code
+
+
+class GemmArgs(Structure):
+    """Mirror of struct fmoe_gemm_args."""
+
+    _fields_ = [
+        ("dtype", c_int32), ("out_dtype", c_int32), ("variant", c_int32), ("num_experts", c_int32),
+        ("top_k", c_int32), ("block_size", c_int32), ("a_gather", c_int32), ("reserved", c_int32),
+        ("numel", c_int64), ("n", c_int64), ("k", c_int64), ("a_rows", c_int64),
+        ("sorted_cap", c_int64), ("max_blocks", c_int64),
+        ("a", c_void_p), ("a_scale", c_void_p), ("w", c_void_p), ("w_scale", c_void_p),
+        ("sorted_token_ids", c_void_p), ("expert_ids", c_void_p), ("num_tokens_post_padded", c_void_p),
+        ("row_scale", c_void_p), ("out", c_void_p), ("out_scale", c_void_p),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/fmoe_b200.h declares
+SIGNATURES = {
+    "fmoe_version": (c_int, []),
+    "fmoe_last_error": (c_char_p, []),
+    "fmoe_sm_count": (c_int, []),
+    "fmoe_topk_softmax": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "fmoe_topk_grouped": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_float,
+                                  c_void_p, c_void_p, c_void_p]),
+    "fmoe_moe_align_block_size": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_int64,
+                                          c_void_p, c_void_p]),
+    "fmoe_quant_fp8_group128": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p,
+                                        c_void_p, c_void_p, c_void_p]),
+    "fmoe_gather_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p, c_void_p,
+                                 c_void_p]),
+    "fmoe_gemm1_silu": (c_int, [POINTER(GemmArgs), c_void_p]),
+    "fmoe_gemm2": (c_int, [POINTER(GemmArgs), c_void_p]),
+    "fmoe_moe_sum": (c_int, [c_void_p, c_int, c_int64, c_int, c_int64, c_float, c_void_p, c_void_p]),
+    "fmoe_check_device_status": (c_int, [c_void_p]),
+}
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library; raises ImportError when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m flaggems_sglang_b200.build` "
+                "(there is no CPU fallback for these ops)"
+            )
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)  # AttributeError if the library lacks a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(rc: int) -> None:
+    if rc != OK:
+        raise FmoeError(rc, lib().fmoe_last_error().decode("utf-8", "replace"))
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device=None) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def require_cuda(*tensors) -> torch.device:
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(
+                "flaggems_sglang_b200 ops run on CUDA (sm_100a) tensors only; there is no CPU path "
+                f"(got a tensor on {t.device})"
+            )
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"tensors on different devices: {dev} and {t.device}")
+    if dev is None:
+        raise RuntimeError("no tensor given")
+    return dev
+
+
+def check_device_status(device=None) -> None:
+    """Synchronises the current stream and raises if a bounded wait inside a tcgen05 kernel gave up."""
+    check(lib().fmoe_check_device_status(stream_ptr(device)))

@@ -1,0 +1,98 @@
+// extern "C" entry points that are not tied to a single kernel file: error
+// reporting, device queries and the grouped-GEMM dispatcher.
+#include "gemm.cuh"
+
+namespace fmoe {
+
+char* last_error_buffer() {
+  static thread_local char buf[kErrBufSize] = {0};
+  return buf;
+}
+
+namespace {
+
+int validate_gemm(const GemmParams& a, bool gated, const char* who) {
+  FMOE_REQUIRE(a.dtype == FMOE_F32 || a.dtype == FMOE_BF16 || a.dtype == FMOE_E4M3, "%s: unknown dtype %d", who, a.dtype);
+  FMOE_REQUIRE(a.num_experts >= 1 && a.top_k >= 1 && a.block_size >= 1, "%s: bad E/top_k/block_size", who);
+  FMOE_REQUIRE(a.numel >= 0 && a.n >= 1 && a.k >= 1, "%s: bad sizes numel=%lld n=%lld k=%lld", who,
+               (long long)a.numel, (long long)a.n, (long long)a.k);
+  FMOE_REQUIRE(a.max_blocks >= 0 && a.max_blocks * a.block_size <= a.sorted_cap,
+               "%s: max_blocks*block_size (%lld) exceeds sorted_cap (%lld)", who,
+               (long long)(a.max_blocks * a.block_size), (long long)a.sorted_cap);
+  if (a.max_blocks == 0 || a.numel == 0) return FMOE_OK;
+  FMOE_REQUIRE(a.a && a.w && a.out && a.sorted_token_ids && a.expert_ids && a.num_tokens_post_padded,
+               "%s: null pointer", who);
+  if (a.dtype == FMOE_E4M3) {
+    FMOE_REQUIRE(a.a_scale && a.w_scale, "%s: e4m3 needs a_scale and w_scale", who);
+    FMOE_REQUIRE(a.k % 128 == 0 && a.n % 128 == 0, "%s: e4m3 needs k and n to be multiples of 128", who);
+  }
+  if (!a.a_gather)
+    FMOE_REQUIRE(a.a_rows >= a.max_blocks * a.block_size, "%s: a has %lld rows, the launch covers %lld", who,
+                 (long long)a.a_rows, (long long)(a.max_blocks * a.block_size));
+  else
+    FMOE_REQUIRE(a.a_rows * a.top_k >= a.numel, "%s: a has %lld rows but numel/top_k needs more", who,
+                 (long long)a.a_rows);
+  (void)gated;
+  return FMOE_OK;
+}
+
+int dispatch_gemm(const fmoe_gemm_args* args, bool gated, void* stream, const char* who) {
+  if (!args) return fail(FMOE_ERR_INVALID_ARG, "%s: args is null", who);
+  const GemmParams& a = *args;
+  int rc = validate_gemm(a, gated, who);
+  if (rc) return rc;
+  if (a.max_blocks == 0 || a.numel == 0) return FMOE_OK;
+  auto st = (cudaStream_t)stream;
+  int variant = a.variant;
+  if (variant == FMOE_VARIANT_AUTO) {
+    if (gemm_tcgen05_supports(a, gated))
+      variant = FMOE_VARIANT_TCGEN05;
+    else if (gemm_stream_supports(a, gated))
+      variant = FMOE_VARIANT_STREAM;
+    else
+      variant = FMOE_VARIANT_SIMT;
+  }
+  switch (variant) {
+    case FMOE_VARIANT_SIMT: return gemm_simt(a, gated, st);
+    case FMOE_VARIANT_STREAM: return gemm_stream(a, gated, st);
+    case FMOE_VARIANT_TCGEN05: return gemm_tcgen05(a, gated, st);
+  }
+  return fail(FMOE_ERR_INVALID_ARG, "%s: unknown variant %d", who, a.variant);
+}
+
+}  // namespace
+}  // namespace fmoe
+
+extern "C" int fmoe_version(void) { return 1; }
+
+extern "C" const char* fmoe_last_error(void) { return fmoe::last_error_buffer(); }
+
+extern "C" int fmoe_sm_count(void) {
+  int dev = 0, n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return n;
+}
+
+extern "C" int fmoe_gemm1_silu(const fmoe_gemm_args* args, void* stream) {
+  return fmoe::dispatch_gemm(args, true, stream, "gemm1_silu");
+}
+
+extern "C" int fmoe_gemm2(const fmoe_gemm_args* args, void* stream) {
+  return fmoe::dispatch_gemm(args, false, stream, "gemm2");
+}
+
+extern "C" int fmoe_check_device_status(void* stream) {
+  int status = 0;
+  int rc = fmoe::read_and_clear_device_status((cudaStream_t)stream, &status);
+  if (rc) return rc;
+  if (status != 0)
+    return fmoe::fail(FMOE_ERR_DEVICE_TIMEOUT, "a bounded wait inside a tcgen05 kernel gave up (site code 0x%x)", status);
+  return FMOE_OK;
+}

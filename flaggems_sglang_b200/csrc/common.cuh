@@ -1,0 +1,93 @@
+// Shared host/device helpers for the fmoe_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/fmoe_b200.h"
+
+namespace fmoe {
+
+// Thread-local message buffer behind fmoe_last_error().
+char* last_error_buffer();
+constexpr int kErrBufSize = 512;
+
+inline int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(last_error_buffer(), kErrBufSize, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define FMOE_REQUIRE(cond, ...)                                  \
+  do {                                                           \
+    if (!(cond)) return ::fmoe::fail(FMOE_ERR_INVALID_ARG, __VA_ARGS__); \
+  } while (0)
+
+#define FMOE_CUDA_OK(expr)                                                        \
+  do {                                                                            \
+    cudaError_t err__ = (expr);                                                   \
+    if (err__ != cudaSuccess)                                                     \
+      return ::fmoe::fail(FMOE_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__)); \
+  } while (0)
+
+inline int launch_status(const char* what) {
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail(FMOE_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(err));
+  return FMOE_OK;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+template <typename T>
+__host__ __device__ constexpr T ceil_div(T a, T b) {
+  return (a + b - 1) / b;
+}
+
+// ---- element conversions -------------------------------------------------
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+__device__ __forceinline__ float to_f32(__nv_fp8_e4m3 v) { return float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ uint8_t f32_to_e4m3_bits(float v) {
+  return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+
+// silu(g) * u exactly as the reference kernel writes it: (g / (1 + exp(-g))) * u in fp32
+// (FlagGems-sglang src/flaggems_sglang/ops/fused_moe.py:62).
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  return __fdiv_rn(g, 1.0f + expf(-g)) * u;
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Streaming 16-byte load that does not allocate in L1 (weights are read once).
+__device__ __forceinline__ uint4 ldg_stream_v4(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p));
+  return r;
+}
+// 16-byte load through L1 (small operands re-read by every warp of the CTA).
+__device__ __forceinline__ uint4 ldg_cached_v4(const void* p) {
+  return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+}  // namespace fmoe

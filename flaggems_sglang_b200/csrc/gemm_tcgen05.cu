@@ -1,0 +1,402 @@
+// Large-M grouped GEMM for sm_100a: persistent, warp-specialised, TMA -> shared
+// memory -> tcgen05.mma -> TMEM, epilogue from TMEM.
+//
+//   tile      : 128 sorted rows (one moe_align block of one expert) x 256 accumulator columns
+//   K step    : 128 bytes per row (64 bf16), one 128-byte swizzle atom; 4 MMAs of K=16 per step
+//   pipeline  : 4 shared-memory stages (A 16 KB + B 32 KB each), full/empty mbarriers
+//   TMEM      : 512 columns = two 128x256 fp32 accumulators, so the epilogue of tile i
+//               overlaps the main loop of tile i+1
+//   warps     : 0-3 epilogue (TMEM lane quarter = warp id), 4 TMA producer, 5 MMA issuer
+//   schedule  : static round-robin over (n_tile, m_block) with m_block fastest, so CTAs that
+//               run at the same time share the weight tile through L2
+//
+// gemm1 (gated): the 256 accumulator columns are 128 gate rows of W and the
+// matching 128 up rows, so silu(gate)*up is applied in the epilogue and only
+// [rows, I] is written.  gemm2: 256 plain columns, multiplied by the row's top-k
+// weight and scattered to the row's flat slot.
+//
+// No TMA multicast, cluster size 1.  Every mbarrier wait is bounded; on expiry the
+// kernel records a code in a device status word, leaves its loops, frees TMEM and returns.
+#include "gemm.cuh"
+#include "ptx_sm100.cuh"
+
+#include <mutex>
+
+namespace fmoe {
+
+__device__ int g_device_status = 0;  // 0 = fine; otherwise (role << 8 | site) of the first wait that gave up
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int KBYTES = 128;  // bytes of K per stage row
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * KBYTES;  // 16 KB
+constexpr int B_BYTES = BN * KBYTES;  // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 512;
+constexpr int kThreads = 192;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+struct TcParams {
+  const int32_t* sorted_token_ids;
+  const int32_t* expert_ids;
+  const int32_t* num_tokens_post_padded;
+  const float* row_scale;
+  void* out;
+  int64_t numel;
+  int64_t n;           // gemm1: I, gemm2: H
+  int64_t w_rows;      // rows of W per expert
+  int64_t sorted_cap;
+  int32_t num_experts;
+  int32_t k_steps;     // ceil(K*elem / 128)
+  int32_t n_tiles;
+  int32_t max_blocks;
+};
+
+__device__ __forceinline__ void report(int code) { atomicCAS(&g_device_status, 0, code); }
+
+// Bounded wait whose verdict is uniform across the warp (all lanes poll; any time-out fails the warp),
+// so that the role loops never diverge around their __syncwarp() points.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity));
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                            const TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                  // [STAGES] TMA -> MMA
+  uint64_t* empty_bar = bars + STAGES;        // [STAGES] MMA -> TMA
+  uint64_t* acc_full = bars + 2 * STAGES;     // [2] MMA -> epilogue
+  uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&acc_full[a], 1);
+      ptx::mbar_init(&acc_empty[a], 128);
+    }
+    ptx::fence_barrier_init();
+  }
+  if (warp == 4 && lane == 0) {
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+  }
+  if (warp == 5) {
+    ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int used_blocks = min((int)(*p.num_tokens_post_padded / BM), p.max_blocks);
+  const int64_t total_tiles = (int64_t)used_blocks * p.n_tiles;
+  const int k_steps = p.k_steps;
+
+  if (warp == 4) {
+    // ---------------- TMA producer ----------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool alive = true;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      const int m_blk = (int)(tile % used_blocks), n_tile = (int)(tile / used_blocks);
+      const int e = p.expert_ids[m_blk];
+      if (e < 0 || e >= p.num_experts) continue;
+      const int32_t row_a = m_blk * BM;
+      const int32_t row_b0 = (int32_t)((int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256));
+      const int32_t row_b1 = GATED ? (int32_t)(row_b0 + p.n) : row_b0 + 128;
+      for (int ks = 0; ks < k_steps; ++ks) {
+        if (!warp_wait(&empty_bar[stage], phase ^ 1)) {
+          report(0x100 | stage);
+          alive = false;
+          break;
+        }
+        if (lane == 0) {
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          ptx::mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const int32_t x = ks * (KBYTES / 2);  // element coordinate (bf16)
+          ptx::tma_load_2d(sa, &map_a, x, row_a, &full_bar[stage]);
+          ptx::tma_load_2d(sb, &map_b, x, row_b0, &full_bar[stage]);
+          ptx::tma_load_2d(sb + B_BYTES / 2, &map_b, x, row_b1, &full_bar[stage]);
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    // drain: do not leave while our own bulk copies may still be landing in shared memory
+    if (alive) {
+      for (int s = 0; s < STAGES; ++s) {
+        // the consumer releases a stage only after its data arrived, so waiting for every
+        // stage to be free again covers all outstanding copies
+        if (!warp_wait(&empty_bar[stage], phase ^ 1)) {
+          report(0x180 | stage);
+          break;
+        }
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    constexpr uint32_t idesc = ptx::make_idesc(/*bf16*/ 1, BM, BN);
+    int stage = 0;
+    uint32_t phase = 0;
+    int local = 0;
+    bool alive = true;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      const int m_blk = (int)(tile % used_blocks);
+      const int e = p.expert_ids[m_blk];
+      if (e < 0 || e >= p.num_experts) continue;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ++local;
+      if (!warp_wait(&acc_empty[acc], acc_phase ^ 1)) {
+        report(0x200 | acc);
+        alive = false;
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + acc * BN;
+      for (int ks = 0; ks < k_steps; ++ks) {
+        if (!warp_wait(&full_bar[stage], phase)) {
+          report(0x240 | stage);
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t sa = ptx::smem_u32(smem + stage * STAGE_BYTES);
+          const uint64_t da = ptx::smem_desc_sw128(sa);
+          const uint64_t db = ptx::smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < KBYTES / 32; ++kk) {
+            // 32 bytes of K per MMA (16 bf16): advance the start address by 32 B = 2 units
+            ptx::mma_f16_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (ks | kk) != 0);
+          }
+          ptx::mma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (alive && lane == 0) ptx::mma_commit(&acc_full[acc]);
+      __syncwarp();
+    }
+  } else {
+    // ---------------- epilogue (warps 0-3) ----------------
+    int local = 0;
+    bool alive = true;
+    const int row = warp * 32 + lane;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      const int m_blk = (int)(tile % used_blocks), n_tile = (int)(tile / used_blocks);
+      const int e = p.expert_ids[m_blk];
+      if (e < 0 || e >= p.num_experts) continue;
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ++local;
+      const int64_t pos = (int64_t)m_blk * BM + row;
+      const int32_t slot = (pos < p.sorted_cap) ? p.sorted_token_ids[pos] : -1;
+      const bool valid = slot >= 0 && slot < p.numel;
+      const float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
+      if (!warp_wait(&acc_full[acc], acc_phase)) {
+        report(0x300 | acc);
+        alive = false;
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(warp * 32) << 16);
+      if constexpr (GATED) {
+        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + pos * p.n + (int64_t)n_tile * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t g[32], u[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c * 32, g);
+          ptx::tmem_ld_32x32b_x32(taddr + 128 + c * 32, u);
+          ptx::tmem_ld_wait();
+          if (pos < p.sorted_cap) {
+            uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int i = v * 8 + j * 2;
+                float o0 = silu_mul(__uint_as_float(g[i]) * rs, __uint_as_float(u[i]) * rs);
+                float o1 = silu_mul(__uint_as_float(g[i + 1]) * rs, __uint_as_float(u[i + 1]) * rs);
+                w[j] = pack_bf16x2(o0, o1);
+              }
+              dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      } else {
+        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)(valid ? slot : 0) * p.n +
+                              (int64_t)n_tile * 256;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (valid && (int64_t)n_tile * 256 + c * 32 < p.n) {
+            uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int i = v * 8 + j * 2;
+                w[j] = pack_bf16x2(__uint_as_float(r[i]) * rs, __uint_as_float(r[i + 1]) * rs);
+              }
+              dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          }
+        }
+      }
+      // accumulator may be overwritten by the MMA warp from here on
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side ----------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// 2-D row-major [rows, cols] tensor of `elem_bytes` elements; box = 128 bytes x box_rows, 128-byte swizzle.
+int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int elem_bytes, int box_rows,
+             bool weights) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * elem_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)(KBYTES / elem_bytes), (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B,
+                  weights ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return FMOE_OK;
+}
+
+template <bool GATED>
+int launch(const GemmParams& g, cudaStream_t st) {
+  static int sm_count = 0;
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  });
+  static std::once_flag once_attr;
+  std::call_once(once_attr, [] {
+    attr_err = cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    SMEM_BYTES);
+  });
+  if (attr_err != cudaSuccess)
+    return fail(FMOE_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", SMEM_BYTES, cudaGetErrorString(attr_err));
+
+  const int64_t w_rows = GATED ? 2 * g.n : g.n;
+  CUtensorMap map_a, map_b;
+  int rc = make_map(&map_a, g.a, g.a_rows, g.k, 2, BM, false);
+  if (rc) return rc;
+  rc = make_map(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 2, 128, true);
+  if (rc) return rc;
+
+  TcParams p;
+  p.sorted_token_ids = g.sorted_token_ids;
+  p.expert_ids = g.expert_ids;
+  p.num_tokens_post_padded = g.num_tokens_post_padded;
+  p.row_scale = g.row_scale;
+  p.out = g.out;
+  p.numel = g.numel;
+  p.n = g.n;
+  p.w_rows = w_rows;
+  p.sorted_cap = g.sorted_cap;
+  p.num_experts = g.num_experts;
+  p.k_steps = (int)ceil_div<int64_t>(g.k * 2, KBYTES);
+  p.n_tiles = (int)ceil_div<int64_t>(g.n, GATED ? 128 : 256);
+  p.max_blocks = (int)g.max_blocks;
+  const int64_t max_tiles = g.max_blocks * p.n_tiles;
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sm_count > 0 ? sm_count : 148, max_tiles));
+  grouped_gemm_tcgen05_kernel<GATED><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
+  return launch_status("grouped_gemm_tcgen05_kernel");
+}
+
+}  // namespace
+
+bool gemm_tcgen05_supports(const GemmParams& p, bool gated) {
+  if (p.dtype != FMOE_BF16 || p.out_dtype != FMOE_BF16) return false;
+  if (p.block_size != BM || p.a_gather) return false;
+  if (p.k <= 0 || (p.k * 2) % 16 != 0) return false;            // TMA row stride must be a multiple of 16 bytes
+  if (p.n <= 0 || p.n % (gated ? 128 : 32) != 0) return false;  // gate/up pairing; 64-byte epilogue stores
+  if (!aligned16(p.a) || !aligned16(p.w) || !aligned16(p.out)) return false;
+  if ((int64_t)p.num_experts * (gated ? 2 * p.n : p.n) >= (1ll << 31) || p.a_rows >= (1ll << 31)) return false;
+  if (p.max_blocks >= (1ll << 24)) return false;
+  return true;
+}
+
+int gemm_tcgen05(const GemmParams& p, bool gated, cudaStream_t st) {
+  if (!gemm_tcgen05_supports(p, gated))
+    return fail(FMOE_ERR_UNSUPPORTED,
+                "tcgen05 gemm: needs bf16 in/out, block_size 128, input rows already in sorted order, "
+                "n %% %d == 0, 16-byte aligned pointers (got dtype=%d block=%d a_gather=%d n=%lld k=%lld)",
+                gated ? 128 : 32, p.dtype, p.block_size, p.a_gather, (long long)p.n, (long long)p.k);
+  if (p.max_blocks <= 0) return FMOE_OK;
+  return gated ? launch<true>(p, st) : launch<false>(p, st);
+}
+
+int read_and_clear_device_status(cudaStream_t st, int* status_out) {
+  int zero = 0;
+  FMOE_CUDA_OK(cudaStreamSynchronize(st));
+  FMOE_CUDA_OK(cudaMemcpyFromSymbol(status_out, g_device_status, sizeof(int)));
+  if (*status_out != 0) FMOE_CUDA_OK(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+  return FMOE_OK;
+}
+
+}  // namespace fmoe

@@ -1,0 +1,153 @@
+// Row-wise helper kernels around the grouped GEMMs (all HBM-bound, 16-byte accesses):
+//   fmoe_quant_fp8_group128 : per-row, per-128-channel e4m3 quantisation (+ optional row gather)
+//   fmoe_gather_rows        : copy rows into the padded expert-sorted order
+//   fmoe_moe_sum            : out[t] = sum_j z[t,j], optional post-scale
+#include "common.cuh"
+
+namespace fmoe {
+namespace {
+
+__device__ __forceinline__ int64_t mapped_row(const int32_t* row_map, int map_div, int64_t sentinel, int64_t p) {
+  if (!row_map) return p;
+  int32_t s = row_map[p];
+  if (s < 0 || (int64_t)s >= sentinel) return -1;
+  return s / map_div;
+}
+
+// one warp per (output row, 128-channel group); lane owns 4 consecutive channels
+template <typename InT>
+__global__ void __launch_bounds__(256)
+quant_group128_kernel(const InT* __restrict__ x, int64_t rows_out, int64_t K, const int32_t* __restrict__ row_map,
+                      int map_div, int64_t sentinel, const int32_t* __restrict__ num_rows_dev,
+                      uint8_t* __restrict__ q, float* __restrict__ scale) {
+  const int lane = threadIdx.x & 31;
+  const int64_t groups = K / 128;
+  const int64_t limit = num_rows_dev ? min((int64_t)*num_rows_dev, rows_out) : rows_out;
+  const int64_t total = limit * groups;
+  for (int64_t w = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); w < total; w += (int64_t)gridDim.x * 8) {
+    const int64_t p = w / groups, g = w % groups;
+    const int64_t r = mapped_row(row_map, map_div, sentinel, p);
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (r >= 0) {
+      const InT* src = x + r * K + g * 128 + lane * 4;
+      if constexpr (sizeof(InT) == 4) {
+        float4 f = *reinterpret_cast<const float4*>(src);
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+      } else {
+        uint2 raw = *reinterpret_cast<const uint2*>(src);
+        __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&raw.x);
+        __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
+        v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+      }
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    float s = (r >= 0) ? __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f) : 1.0f;
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) packed |= (uint32_t)f32_to_e4m3_bits(__fdiv_rn(v[i], s)) << (8 * i);
+    *reinterpret_cast<uint32_t*>(q + p * K + g * 128 + lane * 4) = packed;
+    if (lane == 0) scale[p * groups + g] = s;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const uint4* __restrict__ x, int64_t rows_out, int64_t vec_per_row,
+                   const int32_t* __restrict__ row_map, int map_div, int64_t sentinel,
+                   const int32_t* __restrict__ num_rows_dev, uint4* __restrict__ out) {
+  const int64_t limit = num_rows_dev ? min((int64_t)*num_rows_dev, rows_out) : rows_out;
+  for (int64_t p = blockIdx.x; p < limit; p += gridDim.x) {
+    const int64_t r = mapped_row(row_map, map_div, sentinel, p);
+    for (int64_t c = threadIdx.x; c < vec_per_row; c += blockDim.x)
+      out[p * vec_per_row + c] = (r >= 0) ? __ldg(x + r * vec_per_row + c) : make_uint4(0, 0, 0, 0);
+  }
+}
+
+// each thread owns 8 bf16 (or 4 f32) columns of one token and adds the k slots in order
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_sum_kernel(const T* __restrict__ z, int64_t Tn, int k, int64_t H, float scale, T* __restrict__ out) {
+  constexpr int V = 16 / sizeof(T);
+  const int64_t vec_per_row = H / V;
+  const int64_t total = Tn * vec_per_row;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = i / vec_per_row, c = i % vec_per_row;
+    float acc[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) acc[v] = 0.f;
+    for (int j = 0; j < k; ++j) {
+      uint4 raw = __ldg(reinterpret_cast<const uint4*>(z + ((t * k + j) * H)) + c);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int v = 0; v < V; ++v) acc[v] += to_f32(e[v]);
+    }
+    uint4 res;
+    T* o = reinterpret_cast<T*>(&res);
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      T r = from_f32<T>(acc[v]);
+      if (scale != 1.0f) r = from_f32<T>(to_f32(r) * scale);
+      o[v] = r;
+    }
+    reinterpret_cast<uint4*>(out + t * H)[c] = res;
+  }
+}
+
+}  // namespace
+}  // namespace fmoe
+
+extern "C" int fmoe_quant_fp8_group128(const void* x, int in_dtype, int64_t rows_out, int64_t K,
+                                       const int32_t* row_map, int map_div, int64_t map_sentinel,
+                                       const int32_t* num_rows_dev, void* q, float* scale, void* stream) {
+  using namespace fmoe;
+  FMOE_REQUIRE(K > 0 && K % 128 == 0, "quant_fp8_group128: K must be a positive multiple of 128 (got %lld)", (long long)K);
+  FMOE_REQUIRE(in_dtype == FMOE_BF16 || in_dtype == FMOE_F32, "quant_fp8_group128: in_dtype must be bf16 or f32");
+  FMOE_REQUIRE(!row_map || map_div >= 1, "quant_fp8_group128: map_div must be >= 1");
+  if (rows_out <= 0) return FMOE_OK;
+  FMOE_REQUIRE(x && q && scale, "quant_fp8_group128: null pointer");
+  FMOE_REQUIRE(aligned16(x) && (reinterpret_cast<uintptr_t>(q) & 3u) == 0, "quant_fp8_group128: misaligned pointer");
+  int64_t warps = rows_out * (K / 128);
+  unsigned grid = (unsigned)std::min<int64_t>(ceil_div<int64_t>(warps, 8), 148 * 16);
+  auto st = (cudaStream_t)stream;
+  if (in_dtype == FMOE_BF16)
+    quant_group128_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, rows_out, K, row_map, map_div,
+                                                               map_sentinel, num_rows_dev, (uint8_t*)q, scale);
+  else
+    quant_group128_kernel<float><<<grid, 256, 0, st>>>((const float*)x, rows_out, K, row_map, map_div, map_sentinel,
+                                                       num_rows_dev, (uint8_t*)q, scale);
+  return launch_status("quant_group128_kernel");
+}
+
+extern "C" int fmoe_gather_rows(const void* x, int elem_bytes, int64_t rows_out, int64_t K,
+                                const int32_t* row_map, int map_div, int64_t map_sentinel,
+                                const int32_t* num_rows_dev, void* out, void* stream) {
+  using namespace fmoe;
+  FMOE_REQUIRE(elem_bytes == 2 || elem_bytes == 4 || elem_bytes == 1, "gather_rows: elem_bytes must be 1, 2 or 4");
+  FMOE_REQUIRE(K > 0 && (K * elem_bytes) % 16 == 0, "gather_rows: row size must be a multiple of 16 bytes");
+  FMOE_REQUIRE(row_map && map_div >= 1, "gather_rows: row_map required");
+  if (rows_out <= 0) return FMOE_OK;
+  FMOE_REQUIRE(x && out && aligned16(x) && aligned16(out), "gather_rows: null or misaligned pointer");
+  unsigned grid = (unsigned)std::min<int64_t>(rows_out, 148 * 8);
+  gather_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)x, rows_out, K * elem_bytes / 16, row_map,
+                                                             map_div, map_sentinel, num_rows_dev, (uint4*)out);
+  return launch_status("gather_rows_kernel");
+}
+
+extern "C" int fmoe_moe_sum(const void* z, int dtype, int64_t T, int k, int64_t H, float scale, void* out,
+                            void* stream) {
+  using namespace fmoe;
+  FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "moe_sum: dtype must be bf16 or f32");
+  const int eb = dtype == FMOE_BF16 ? 2 : 4;
+  FMOE_REQUIRE(k >= 1 && H > 0 && (H * eb) % 16 == 0, "moe_sum: need k >= 1 and H*elem %% 16 == 0");
+  if (T <= 0) return FMOE_OK;
+  FMOE_REQUIRE(z && out && aligned16(z) && aligned16(out), "moe_sum: null or misaligned pointer");
+  int64_t total = T * (H * eb / 16);
+  unsigned grid = (unsigned)std::min<int64_t>(ceil_div<int64_t>(total, 256), 148 * 16);
+  auto st = (cudaStream_t)stream;
+  if (dtype == FMOE_BF16)
+    moe_sum_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)z, T, k, H, scale, (__nv_bfloat16*)out);
+  else
+    moe_sum_kernel<float><<<grid, 256, 0, st>>>((const float*)z, T, k, H, scale, (float*)out);
+  return launch_status("moe_sum_kernel");
+}

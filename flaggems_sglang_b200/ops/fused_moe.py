@@ -1,0 +1,446 @@
+"""Fused MoE expert computation on B200: align -> gate/up GEMM + silu*mul -> down GEMM * weight -> sum.
+
+Host-side mirror of the reference operator
+(FlagGems-sglang src/flaggems_sglang/ops/fused_moe.py): the same entry points
+(`triton_kernel_fused_experts`, `fused_moe_flagos`), argument meaning and error
+behaviour, plus the serving-side `fused_experts` / `fused_moe` signatures on the
+`w1 [E,2I,H]`, `w2 [E,H,I]` layouts.  All arithmetic runs in the hand-written
+CUDA kernels behind the C ABI (include/fmoe_b200.h); nothing falls back to
+torch or the CPU.
+
+Kernel selection (per call, from shapes only, no host sync):
+  rows per active expert <= ~40  -> "stream": small-M weight-streaming kernel,
+                                    moe_align block 8/16/32, x gathered on the fly
+  larger                         -> "tcgen05": rows copied into expert-sorted order
+                                    (block 128), TMA + tcgen05/TMEM persistent kernel
+  fp32 inputs                    -> "simt"
+"""
+from __future__ import annotations
+
+import logging
+import os
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import _C
+from .moe_align_block_size import moe_align_block_size
+from .topk import topk as _route
+
+logger = logging.getLogger(__name__)
+
+_UNSUPPORTED_FEATURE_MSG = "{name} is not supported"
+
+# Optional per-stage timing for benchmarks: set to a list and every fused_experts call appends
+# (stage name, start event, end event) recorded on the launching stream.  None = no events.
+STAGE_EVENTS: Optional[list] = None
+
+
+class _stage:
+    """Context manager bracketing one kernel launch with CUDA events when STAGE_EVENTS is a list."""
+
+    def __init__(self, name: str):
+        self.name = name
+
+    def __enter__(self):
+        if STAGE_EVENTS is not None:
+            self.t0 = torch.cuda.Event(enable_timing=True)
+            self.t0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if STAGE_EVENTS is not None:
+            t1 = torch.cuda.Event(enable_timing=True)
+            t1.record()
+            STAGE_EVENTS.append((self.name, self.t0, t1))
+        return False
+
+
+# --------------------------------------------------------------------------
+# routing containers accepted by the reference-layout entry point
+# --------------------------------------------------------------------------
+@dataclass
+class GatherIndx:
+    src_indx: torch.Tensor  # sorted position -> flat slot
+    dst_indx: torch.Tensor  # flat slot -> sorted position
+
+
+@dataclass
+class ScatterIndx:
+    src_indx: torch.Tensor
+    dst_indx: torch.Tensor
+
+
+@dataclass
+class RoutingData:
+    gate_scal: torch.Tensor  # [T*k] weights in expert-sorted order
+    expt_hist: torch.Tensor  # [E] rows per expert
+    n_expts_tot: int
+    n_expts_act: int
+    expt_data: object = None
+
+
+def standard_topk_to_routing(topk_weights: torch.Tensor, topk_ids: torch.Tensor, n_expts_tot: int):
+    """(topk_weights, topk_ids) -> (RoutingData, GatherIndx, ScatterIndx).
+
+    Same tables as the reference's `_standard_topk_to_triton_kernels`
+    (src/flaggems_sglang/ops/fused_moe.py:119-146) without the per-block tile maps,
+    which only the third-party grouped GEMM needs.  Torch ops; kept for callers that
+    hold routing in this format — `fused_experts` does not go through it.
+    """
+    T, k = topk_weights.shape
+    ids2, perm = torch.sort(topk_ids, dim=1)
+    w2 = torch.gather(topk_weights, 1, perm)
+    expt = ids2.reshape(-1).to(torch.int32)
+    topk_indx = torch.argsort(expt, stable=True).to(torch.int32)
+    gate_indx = torch.argsort(topk_indx, stable=True).to(torch.int32)
+    gate_scal = w2.reshape(-1)[topk_indx.long()]
+    hist = torch.bincount(expt.long(), minlength=n_expts_tot)[:n_expts_tot].to(torch.int32)
+    rd = RoutingData(gate_scal, hist, n_expts_tot, k)
+    return rd, GatherIndx(topk_indx, gate_indx), ScatterIndx(gate_indx, topk_indx)
+
+
+# --------------------------------------------------------------------------
+# kernel selection
+# --------------------------------------------------------------------------
+def _pick_variant(dtype, numel: int, E: int, I: int, H: int, forced: Optional[str]):
+    """-> (variant name, moe_align block size)"""
+    forced = forced or os.environ.get("FMOE_VARIANT") or None
+    if dtype == torch.float32:
+        if forced not in (None, "simt"):
+            raise ValueError("fp32 inputs run on the simt kernels only")
+        return "simt", 16
+    active = max(1, min(E, numel))
+    rows = numel / active
+    if forced is None:
+        stream_ok = (H % 128 == 0) and (I % 128 == 0)
+        tc_ok = dtype == torch.bfloat16 and I % 128 == 0 and H % 32 == 0
+        if stream_ok and (rows <= 40 or not tc_ok):
+            forced = "stream"
+        elif tc_ok:
+            forced = "tcgen05"
+        elif stream_ok:
+            forced = "stream"
+        else:
+            forced = "simt"
+    if forced == "tcgen05":
+        return "tcgen05", 128
+    if forced == "stream":
+        if rows <= 6:
+            return "stream", 8
+        if rows <= 12:
+            return "stream", 16
+        return "stream", 32
+    if forced == "simt":
+        return "simt", 16
+    raise ValueError(f"unknown variant {forced!r}")
+
+
+def _gemm_args(**kw) -> _C.GemmArgs:
+    a = _C.GemmArgs()
+    for key, val in kw.items():
+        setattr(a, key, val)
+    return a
+
+
+# --------------------------------------------------------------------------
+# serving-side entry points
+# --------------------------------------------------------------------------
+def fused_experts(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    topk_weights: torch.Tensor,
+    topk_ids: torch.Tensor,
+    inplace: bool = False,
+    activation: str = "silu",
+    apply_router_weight_on_input: bool = False,
+    use_fp8_w8a8: bool = False,
+    per_channel_quant: bool = False,
+    w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+    a1_scale: Optional[torch.Tensor] = None,
+    a2_scale: Optional[torch.Tensor] = None,
+    block_shape: Optional[list[int]] = None,
+    no_combine: bool = False,
+    routed_scaling_factor: Optional[float] = None,
+    expert_map: Optional[torch.Tensor] = None,
+    global_num_experts: int = -1,
+    variant: Optional[str] = None,
+) -> torch.Tensor:
+    """Expert computation for already-routed tokens.
+
+    hidden_states [T,H]; w1 [E,2I,H] (rows [0,I) gate, [I,2I) up); w2 [E,H,I];
+    topk_weights [T,k] float; topk_ids [T,k] int.  bf16 (or fp32) weights, or
+    e4m3 weights with `use_fp8_w8a8=True`, `block_shape=[128,128]` and fp32
+    block scales `w1_scale [E,2I/128,H/128]`, `w2_scale [E,H/128,I/128]`
+    (activations are quantised per token per 128 channels on the fly).
+    Returns [T,H] (or [T,k,H] with `no_combine`).  `expert_map` maps global to
+    local expert ids (-1 = not on this rank; such slots contribute zeros).
+    """
+    logger.debug("FLAGGEMS_SGLANG_B200 FUSED_EXPERTS")
+    assert inplace is False, "Inplace is not supported"
+    assert per_channel_quant is False, _UNSUPPORTED_FEATURE_MSG.format(name="per_channel_quant")
+    assert a1_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="a1_scale")
+    assert a2_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="a2_scale")
+    if activation != "silu":
+        raise ValueError(f"Unsupported FusedMoe activation: {activation}")
+    dev = _C.require_cuda(hidden_states, w1, w2, topk_weights, topk_ids, w1_scale, w2_scale, expert_map)
+    assert hidden_states.ndim == 2, "hidden_states must be 2D"
+    T, H = hidden_states.shape
+    E, twoI, Hw = w1.shape
+    I = twoI // 2
+    assert Hw == H, "hidden size mismatch"
+    assert w2.shape[0] == E and w2.shape[1] == H and w2.shape[2] == I, "intermediate size mismatch"
+    assert topk_ids.shape == topk_weights.shape and topk_ids.shape[0] == T, "topk shape mismatch"
+    k = topk_ids.shape[1]
+    numel = T * k
+
+    if use_fp8_w8a8:
+        assert block_shape is not None and list(block_shape) == [128, 128], "fp8 needs block_shape=[128, 128]"
+        assert w1.dtype == torch.float8_e4m3fn and w2.dtype == torch.float8_e4m3fn, "fp8 weights must be e4m3"
+        assert w1_scale is not None and w2_scale is not None, "fp8 needs w1_scale and w2_scale"
+        assert hidden_states.dtype == torch.bfloat16, "hidden_states must be bfloat16"
+        assert H % 128 == 0 and I % 128 == 0, "fp8 block quantisation needs H and I to be multiples of 128"
+        assert tuple(w1_scale.shape) == (E, twoI // 128, H // 128), "w1_scale shape"
+        assert tuple(w2_scale.shape) == (E, H // 128, I // 128), "w2_scale shape"
+        w1_scale = w1_scale.float().contiguous()
+        w2_scale = w2_scale.float().contiguous()
+    else:
+        assert w1_scale is None and w2_scale is None and block_shape is None, "scales given without use_fp8_w8a8"
+        assert hidden_states.dtype in (torch.bfloat16, torch.float32), "hidden_states must be bfloat16 or float32"
+        assert w1.dtype == hidden_states.dtype and w2.dtype == hidden_states.dtype, "w1/w2 dtype must match hidden_states"
+    out_dtype = hidden_states.dtype
+    x = hidden_states.contiguous()
+    w1 = w1.contiguous()
+    w2 = w2.contiguous()
+    wts = topk_weights.float().contiguous()
+    ids = topk_ids
+    if expert_map is not None:
+        ids = expert_map.to(torch.int32)[topk_ids.long()]
+    ids = ids.to(torch.int32).contiguous()
+
+    if T == 0:
+        return x.new_empty((0, k, H) if no_combine else (0, H))
+
+    lib = _C.lib()
+    st = _C.stream_ptr(dev)
+    name, block = _pick_variant(w1.dtype if not use_fp8_w8a8 else torch.float8_e4m3fn, numel, E, I, H, variant)
+    if use_fp8_w8a8 and name == "tcgen05":
+        name, block = _pick_variant(torch.float8_e4m3fn, numel, E, I, H, "stream")
+    vcode = _C.VARIANTS[name]
+
+    sorted_ids, expert_ids, num_post = moe_align_block_size(ids, block, E)
+    cap = sorted_ids.numel()
+    max_blocks = min(cap // block, numel)
+    row_w = wts.data_ptr()
+    code = _C.DTYPE_CODE[out_dtype]
+    common = dict(variant=vcode, num_experts=E, top_k=k, block_size=block, numel=numel, sorted_cap=cap,
+                  max_blocks=max_blocks, sorted_token_ids=sorted_ids.data_ptr(), expert_ids=expert_ids.data_ptr(),
+                  num_tokens_post_padded=num_post.data_ptr())
+
+    # Z holds one output row per flat slot; slots that no kernel writes (dropped ids) must read as zero
+    z_alloc = torch.zeros if expert_map is not None else torch.empty
+    z = z_alloc((numel, H), dtype=out_dtype, device=dev)
+
+    if not use_fp8_w8a8:
+        if name == "tcgen05":
+            xs = torch.empty((cap, H), dtype=out_dtype, device=dev)
+            _C.check(lib.fmoe_gather_rows(x.data_ptr(), x.element_size(), cap, H, sorted_ids.data_ptr(), k, numel,
+                                          num_post.data_ptr(), xs.data_ptr(), st))
+            a_ptr, a_rows, gather = xs.data_ptr(), cap, 0
+        else:
+            a_ptr, a_rows, gather = x.data_ptr(), T, 1
+        act = torch.empty((cap, I), dtype=out_dtype, device=dev)
+        g1 = _gemm_args(dtype=code, out_dtype=code, a_gather=gather, n=I, k=H, a_rows=a_rows, a=a_ptr,
+                        w=w1.data_ptr(), row_scale=row_w if apply_router_weight_on_input else None,
+                        out=act.data_ptr(), **common)
+        with _stage("gemm1_" + name):
+            _C.check(lib.fmoe_gemm1_silu(g1, st))
+        g2 = _gemm_args(dtype=code, out_dtype=code, a_gather=0, n=H, k=I, a_rows=cap, a=act.data_ptr(),
+                        w=w2.data_ptr(), row_scale=None if apply_router_weight_on_input else row_w,
+                        out=z.data_ptr(), **common)
+        with _stage("gemm2_" + name):
+            _C.check(lib.fmoe_gemm2(g2, st))
+    else:
+        xq = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=dev)
+        xsc = torch.empty((T, H // 128), dtype=torch.float32, device=dev)
+        _C.check(lib.fmoe_quant_fp8_group128(x.data_ptr(), _C.BF16, T, H, None, 1, 0, None, xq.data_ptr(),
+                                             xsc.data_ptr(), st))
+        act = torch.empty((cap, I), dtype=torch.float32, device=dev)
+        g1 = _gemm_args(dtype=_C.E4M3, out_dtype=_C.F32, a_gather=1, n=I, k=H, a_rows=T, a=xq.data_ptr(),
+                        a_scale=xsc.data_ptr(), w=w1.data_ptr(), w_scale=w1_scale.data_ptr(),
+                        row_scale=row_w if apply_router_weight_on_input else None, out=act.data_ptr(), **common)
+        with _stage("gemm1_fp8_" + name):
+            _C.check(lib.fmoe_gemm1_silu(g1, st))
+        aq = torch.empty((cap, I), dtype=torch.float8_e4m3fn, device=dev)
+        asc = torch.empty((cap, I // 128), dtype=torch.float32, device=dev)
+        _C.check(lib.fmoe_quant_fp8_group128(act.data_ptr(), _C.F32, cap, I, None, 1, 0, num_post.data_ptr(),
+                                             aq.data_ptr(), asc.data_ptr(), st))
+        g2 = _gemm_args(dtype=_C.E4M3, out_dtype=_C.BF16, a_gather=0, n=H, k=I, a_rows=cap, a=aq.data_ptr(),
+                        a_scale=asc.data_ptr(), w=w2.data_ptr(), w_scale=w2_scale.data_ptr(),
+                        row_scale=None if apply_router_weight_on_input else row_w, out=z.data_ptr(), **common)
+        with _stage("gemm2_fp8_" + name):
+            _C.check(lib.fmoe_gemm2(g2, st))
+
+    if no_combine:
+        return z.view(T, k, H)
+    out = torch.empty((T, H), dtype=out_dtype, device=dev)
+    scale = 1.0 if routed_scaling_factor is None else float(routed_scaling_factor)
+    _C.check(lib.fmoe_moe_sum(z.data_ptr(), _C.DTYPE_CODE[out_dtype], T, k, H, scale, out.data_ptr(), st))
+    return out
+
+
+def fused_moe(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    gating_output: torch.Tensor,
+    topk: int,
+    renormalize: bool = True,
+    use_grouped_topk: bool = False,
+    num_expert_group: Optional[int] = None,
+    topk_group: Optional[int] = None,
+    correction_bias: Optional[torch.Tensor] = None,
+    routed_scaling_factor: Optional[float] = None,
+    **kwargs,
+) -> torch.Tensor:
+    """Router (softmax top-k, or grouped biased-sigmoid top-k) followed by `fused_experts`.
+
+    `routed_scaling_factor` is applied exactly once, after the combine
+    (as the reference hook does, src/flaggems_sglang/ops/fused_moe.py:415-420).
+    """
+    w, ids = _route(hidden_states, gating_output, topk, renormalize, use_grouped_topk, num_expert_group,
+                    topk_group, correction_bias, None)
+    return fused_experts(hidden_states, w1, w2, w, ids, routed_scaling_factor=routed_scaling_factor, **kwargs)
+
+
+# --------------------------------------------------------------------------
+# reference-layout entry points
+# --------------------------------------------------------------------------
+def _k_major(w: torch.Tensor) -> torch.Tensor:
+    """[E, K, N] (reference layout) -> [E, N, K] contiguous.  Free when the caller passes
+    the transposed view of a serving-side weight, a copy otherwise."""
+    wt = w.transpose(-1, -2)
+    return wt if wt.is_contiguous() else wt.contiguous()
+
+
+def triton_kernel_fused_experts(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w2: torch.Tensor,
+    routing_data,
+    gather_indx,
+    scatter_indx,
+    inplace: bool = False,
+    activation: str = "silu",
+    apply_router_weight_on_input: bool = False,
+    use_fp8_w8a8: bool = False,
+    per_channel_quant: bool = False,
+    global_num_experts: int = -1,
+    expert_map: Optional[torch.Tensor] = None,
+    w1_scale: Optional[torch.Tensor] = None,
+    w2_scale: Optional[torch.Tensor] = None,
+    a1_scale: Optional[torch.Tensor] = None,
+    a2_scale: Optional[torch.Tensor] = None,
+    block_shape: Optional[list[int]] = None,
+) -> torch.Tensor:
+    """Drop-in for the reference op of the same name (src/flaggems_sglang/ops/fused_moe.py:149-232).
+
+    Same signature, layouts (w1 [E,H,2I], w2 [E,I,H], routing triple) and assertions.
+    `scatter_indx=None` returns the un-combined rows in expert-sorted order, as the
+    reference does.  Weights given as transposed views of [E,2I,H]/[E,H,I] tensors are
+    used in place; truly [E,H,2I]-contiguous weights are transposed once per call.
+    """
+    logger.debug("FLAGGEMS_SGLANG FUSED_MOE")
+    assert use_fp8_w8a8 is False, _UNSUPPORTED_FEATURE_MSG.format(name="use_fp8_w8a8")
+    assert per_channel_quant is False, _UNSUPPORTED_FEATURE_MSG.format(name="per_channel_quant")
+    assert expert_map is None, _UNSUPPORTED_FEATURE_MSG.format(name="expert_map")
+    assert w1_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="w1_scale")
+    assert w2_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="w2_scale")
+    assert a1_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="a1_scale")
+    assert a2_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="a2_scale")
+    assert block_shape is None, _UNSUPPORTED_FEATURE_MSG.format(name="block_shape")
+    assert inplace is False, "Inplace is not supported"
+    assert hidden_states.ndim == 2, "hidden_states must be 2D"
+    assert hidden_states.dtype == torch.bfloat16, "hidden_states must be bfloat16"
+    assert w1.dtype == torch.bfloat16, "w1 must be bfloat16"
+    assert w2.dtype == torch.bfloat16, "w2 must be bfloat16"
+    assert hidden_states.shape[-1] == w1.shape[-2], "hidden size mismatch"
+    assert w2.shape[-1] == w1.shape[1], "intermediate size mismatch"
+    if activation != "silu":
+        raise ValueError(f"Unsupported FusedMoe activation: {activation}")
+
+    T, H = hidden_states.shape
+    k = routing_data.n_expts_act
+    E = w1.shape[0]
+    M = T * k
+    dev = hidden_states.device
+    topk_indx = gather_indx.src_indx.long()          # sorted position -> flat slot
+    hist = routing_data.expt_hist.long()
+    expert_of_pos = torch.repeat_interleave(torch.arange(E, device=dev), hist, output_size=M)
+    ids_flat = torch.empty(M, dtype=torch.int32, device=dev)
+    ids_flat[topk_indx] = expert_of_pos.to(torch.int32)
+    w_flat = torch.empty(M, dtype=torch.float32, device=dev)
+    w_flat[topk_indx] = routing_data.gate_scal.float()
+    z_or_out = fused_experts(
+        hidden_states, _k_major(w1), _k_major(w2), w_flat.view(T, k), ids_flat.view(T, k),
+        apply_router_weight_on_input=apply_router_weight_on_input, no_combine=scatter_indx is None,
+    )
+    if scatter_indx is None:
+        # reference returns rows in sorted order p; ours are by flat slot
+        return z_or_out.view(M, H)[topk_indx]
+    return z_or_out.view(T, H)
+
+
+@dataclass
+class StandardCombineInput:
+    hidden_states: torch.Tensor
+
+
+def fused_moe_flagos(obj, layer: torch.nn.Module, dispatch_output):
+    """Serving-side hook with the reference's signature (src/flaggems_sglang/ops/fused_moe.py:328-422).
+
+    Reads `layer.w13_weight [E,2I,H]` / `layer.w2_weight [E,H,I]` in place (the reference
+    transposes and copies both on every call, :342-343), accepts either the standard
+    `(topk_weights, topk_ids)` output or a routing triple, honours `no_combine`,
+    `apply_router_weight_on_input` and `routed_scaling_factor` of `obj.runner.config`,
+    and returns an object with `.hidden_states`.
+    """
+    cfg = obj.runner.config
+    if getattr(layer, "w13_weight_bias", None) is not None or getattr(layer, "w2_weight_bias", None) is not None:
+        raise NotImplementedError("expert biases (fused swiglu variant) are not supported")
+    hidden_states = dispatch_output.hidden_states
+    topk_output = dispatch_output.topk_output
+    if hasattr(topk_output, "topk_weights"):
+        tw, ti = topk_output.topk_weights, topk_output.topk_ids
+        out = fused_experts(
+            hidden_states, layer.w13_weight, layer.w2_weight, tw, ti, activation=cfg.activation,
+            apply_router_weight_on_input=cfg.apply_router_weight_on_input, no_combine=cfg.no_combine,
+            routed_scaling_factor=None if cfg.no_combine else cfg.routed_scaling_factor,
+        )
+    else:
+        routing_data, gather_indx, scatter_indx = topk_output
+        out = triton_kernel_fused_experts(
+            hidden_states, layer.w13_weight.transpose(-1, -2), layer.w2_weight.transpose(-1, -2), routing_data,
+            gather_indx, None if cfg.no_combine else scatter_indx, activation=cfg.activation,
+            apply_router_weight_on_input=cfg.apply_router_weight_on_input,
+        )
+        if cfg.no_combine:
+            out = out.view(hidden_states.shape[0], -1, hidden_states.shape[-1])
+        elif cfg.routed_scaling_factor is not None and cfg.routed_scaling_factor != 1.0:
+            out.mul_(cfg.routed_scaling_factor)
+    return StandardCombineInput(hidden_states=out)
+
+
+__all__ = [
+    "fused_experts",
+    "fused_moe",
+    "triton_kernel_fused_experts",
+    "fused_moe_flagos",
+    "standard_topk_to_routing",
+    "RoutingData",
+    "GatherIndx",
+    "ScatterIndx",
+]

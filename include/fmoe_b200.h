@@ -1,0 +1,175 @@
+/*
+ * fmoe_b200 — C ABI of the B200 (sm_100a) fused-MoE kernels.
+ *
+ * The reference project (FlagGems-sglang) has no native boundary: its operator
+ * is a Python function that launches Triton kernels.  Each entry point below
+ * names the reference interface (file:line inside that project) whose work it
+ * takes over, so a maintainer can bind it from the Python operator with ctypes.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless stated otherwise; the caller owns
+ *     all memory, the library never allocates or frees (workspaces are passed in);
+ *   - every function returns FMOE_OK (0) or an FMOE_ERR_* code; a human-readable
+ *     message for the calling thread's last failure is at fmoe_last_error();
+ *   - `stream` is a cudaStream_t passed as void*; work is enqueued, not awaited;
+ *   - nothing here falls back to the CPU: without a CUDA device every compute
+ *     entry point returns FMOE_ERR_CUDA.
+ */
+#ifndef FMOE_B200_H
+#define FMOE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FMOE_OK 0
+#define FMOE_ERR_INVALID_ARG 1
+#define FMOE_ERR_CUDA 2
+#define FMOE_ERR_UNSUPPORTED 3
+#define FMOE_ERR_DEVICE_TIMEOUT 4
+
+/* element types of activations / weights */
+#define FMOE_F32 0
+#define FMOE_BF16 1
+#define FMOE_E4M3 2
+
+/* grouped-GEMM kernel families (fmoe_gemm_args.variant) */
+#define FMOE_VARIANT_AUTO 0
+#define FMOE_VARIANT_SIMT 1    /* plain CUDA-core kernel; any shape; validation and fp32 */
+#define FMOE_VARIANT_STREAM 2  /* small-M weight-streaming kernel, split-K over warps */
+#define FMOE_VARIANT_TCGEN05 3 /* TMA + tcgen05/TMEM persistent kernel for large M */
+
+int fmoe_version(void);
+/* Message of the last error returned on the calling thread ("" if none). */
+const char* fmoe_last_error(void);
+/* Number of SMs of the current device (0 when there is no device). */
+int fmoe_sm_count(void);
+
+/*
+ * Router: softmax over E experts, top-k, optional renormalisation.
+ * Replaces the routing the reference's caller performs before the hook
+ * (src/flaggems_sglang/ops/fused_moe.py:355-366 consumes topk_weights/topk_ids;
+ * tests/test_fused_moe.py:38-41 builds them with softmax -> topk -> renormalise).
+ * Ranking is on the raw logits, ties go to the lower expert index.
+ *   logits [T,E] f32 row-major -> topk_weights [T,k] f32, topk_ids [T,k] i32
+ * Limits: 1 <= k <= 32, k <= E <= 1024.
+ */
+int fmoe_topk_softmax(const float* logits, int64_t T, int E, int k, int renormalize,
+                      float* topk_weights, int32_t* topk_ids, void* stream);
+
+/*
+ * Router: DeepSeek-V3 style group-limited top-k on sigmoid scores with a
+ * per-expert selection bias (same place in the reference as above; the
+ * reference itself has no grouped router).
+ *   s = sigmoid(logits); c = s + bias (bias may be NULL);
+ *   group score = sum of the 2 largest c of the group; keep topk_group groups;
+ *   ids = top-k of c inside kept groups; weights = s[ids], renormalised by
+ *   (sum + 1e-20) when `renormalize`, then multiplied by `scale`.
+ * Limits: E <= 1024, E % n_group == 0, n_group <= 32, k <= 32.
+ */
+int fmoe_topk_grouped(const float* logits, const float* bias, int64_t T, int E, int k,
+                      int n_group, int topk_group, int renormalize, float scale,
+                      float* topk_weights, int32_t* topk_ids, void* stream);
+
+/*
+ * moe_align_block_size: sort the flat (token, slot) indices by expert and pad
+ * every expert to a multiple of `block`.  Takes over the routing-table
+ * construction of src/flaggems_sglang/ops/fused_moe.py:119-146.
+ *   topk_ids [numel] i32 (ids outside [0,E) are dropped)
+ *   sorted_token_ids [sorted_cap] i32, sorted_cap >= numel + E*(block-1); filled
+ *       with the sentinel `numel`, then per expert its slots in ascending order
+ *   expert_ids [expert_cap] i32, expert_cap >= ceil(sorted_cap/block); expert of
+ *       each used block, -1 after the used blocks
+ *   num_tokens_post_padded [1] i32
+ * Limits: E <= 1024, numel < 2^31.
+ */
+int fmoe_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int E, int block,
+                              int32_t* sorted_token_ids, int64_t sorted_cap,
+                              int32_t* expert_ids, int64_t expert_cap,
+                              int32_t* num_tokens_post_padded, void* stream);
+
+/*
+ * Per-row, per-128-channel dynamic quantisation to e4m3 (the fp8 path the
+ * reference rejects at src/flaggems_sglang/ops/fused_moe.py:170-185).
+ *   x [rows_in, K] (in_dtype FMOE_BF16 or FMOE_F32), K % 128 == 0
+ *   q [rows_out, K] e4m3, scale [rows_out, K/128] f32,
+ *   scale = max(amax,1e-10)/448, q = rne(x/scale) saturated to +-448.
+ * With row_map == NULL rows_out == rows_in and row r reads row r.  With a
+ * row_map (sorted_token_ids) output row p reads input row row_map[p]/map_div,
+ * and rows whose map entry is >= map_sentinel are written as zeros (scale 1).
+ * Only rows p < *num_rows_dev are produced when num_rows_dev != NULL.
+ */
+int fmoe_quant_fp8_group128(const void* x, int in_dtype, int64_t rows_out, int64_t K,
+                            const int32_t* row_map, int map_div, int64_t map_sentinel,
+                            const int32_t* num_rows_dev, void* q, float* scale, void* stream);
+
+/*
+ * Row gather into the padded expert-sorted order (bf16/f32 copy):
+ *   out[p,:] = x[row_map[p]/map_div,:], zeros where row_map[p] >= map_sentinel,
+ *   for p < *num_rows_dev.  elem_bytes is 2 or 4; K*elem_bytes % 16 == 0.
+ */
+int fmoe_gather_rows(const void* x, int elem_bytes, int64_t rows_out, int64_t K,
+                     const int32_t* row_map, int map_div, int64_t map_sentinel,
+                     const int32_t* num_rows_dev, void* out, void* stream);
+
+/*
+ * Grouped GEMMs over the expert-sorted token blocks.  Together they take over
+ * the two matmul_ogs calls and the activation pass of
+ * src/flaggems_sglang/ops/fused_moe.py:205-231.
+ */
+typedef struct fmoe_gemm_args {
+  int32_t dtype;       /* FMOE_F32 | FMOE_BF16 | FMOE_E4M3: type of a and w            */
+  int32_t out_dtype;   /* FMOE_F32 | FMOE_BF16 | FMOE_E4M3 (gemm1+TCGEN05 fp8 only)     */
+  int32_t variant;     /* FMOE_VARIANT_*                                                 */
+  int32_t num_experts; /* E                                                              */
+  int32_t top_k;       /* k                                                              */
+  int32_t block_size;  /* block used for sorted_token_ids / expert_ids                   */
+  int32_t a_gather;    /* 1: row of `a` for sorted position p is slot/top_k ([T,K] input)
+                          0: row of `a` is p itself (input already in sorted order)      */
+  int32_t reserved;
+  int64_t numel;       /* T*k: sentinel in sorted_token_ids, number of output slots      */
+  int64_t n;           /* gemm1: I (w has 2I rows per expert); gemm2: H                  */
+  int64_t k;           /* reduction length: gemm1 H, gemm2 I                             */
+  int64_t a_rows;      /* rows of `a`                                                    */
+  int64_t sorted_cap;  /* length of sorted_token_ids                                     */
+  int64_t max_blocks;  /* upper bound on used blocks the launch must cover               */
+  const void* a;       /* [a_rows, k]                                                    */
+  const float* a_scale;/* e4m3: [a_rows, k/128]                                          */
+  const void* w;       /* gemm1 [E, 2I, H]; gemm2 [E, H, I]; reduction dim contiguous    */
+  const float* w_scale;/* e4m3: [E, rows/128, k/128]                                     */
+  const int32_t* sorted_token_ids;
+  const int32_t* expert_ids;
+  const int32_t* num_tokens_post_padded;
+  const float* row_scale; /* [numel] top-k weights by flat slot, or NULL                 */
+  void* out;           /* gemm1: [sorted_cap, I] in sorted order; gemm2: [numel, H] by slot */
+  float* out_scale;    /* gemm1 with out_dtype e4m3: [sorted_cap, I/128]                 */
+} fmoe_gemm_args;
+
+/* gemm1: out[p, c] = silu(acc[p, c]) * acc[p, I + c], acc = (a_row(p) . w[e(p)]^T) * row_scale. */
+int fmoe_gemm1_silu(const fmoe_gemm_args* args, void* stream);
+/* gemm2: out[slot(p), :] = (a[p, :] . w[e(p)]^T) * row_scale[slot(p)], rounded to out_dtype. */
+int fmoe_gemm2(const fmoe_gemm_args* args, void* stream);
+
+/*
+ * moe_sum / combine: out[t,:] = round(sum_j z[t,j,:]) (fp32, j ascending), then
+ * optionally out = round(out * scale) when scale != 1 (the hook's post-multiply,
+ * src/flaggems_sglang/ops/fused_moe.py:415-420).  Takes over the grouped reduce
+ * the reference's second matmul_ogs call ends with (:224-231).
+ *   z [T, k, H], out [T, H]; dtype FMOE_BF16 or FMOE_F32; H*elem % 16 == 0.
+ */
+int fmoe_moe_sum(const void* z, int dtype, int64_t T, int k, int64_t H, float scale,
+                 void* out, void* stream);
+
+/*
+ * Reads and clears the device-side status word that bounded waits inside the
+ * tcgen05 kernels set when they give up.  Synchronises `stream`.
+ * Returns FMOE_OK or FMOE_ERR_DEVICE_TIMEOUT.
+ */
+int fmoe_check_device_status(void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FMOE_B200_H */

@@ -1,0 +1,109 @@
+"""CPU-side checks of the boundary: the C-ABI library loads, exports every symbol the
+header declares, and the ops refuse to run without CUDA tensors (no CPU fallback)."""
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import __graft_entry__ as ge
+
+    ge.build()
+    from flaggems_sglang_b200 import _C
+
+    return _C.lib()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "fmoe_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fmoe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported_and_bound(lib):
+    from flaggems_sglang_b200 import _C
+
+    names = _declared_symbols()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/fmoe_b200.h but not exported"
+        assert n in _C.SIGNATURES, f"{n} has no ctypes signature"
+    assert sorted(_C.SIGNATURES) == names
+
+
+def test_struct_layout_matches_header():
+    import ctypes
+
+    from flaggems_sglang_b200 import _C
+
+    # 8 int32 + 6 int64 + 10 pointers
+    assert ctypes.sizeof(_C.GemmArgs) == 8 * 4 + 6 * 8 + 10 * 8
+    assert _C.GemmArgs.numel.offset == 32 and _C.GemmArgs.a.offset == 80
+
+
+def test_version_and_error_buffer(lib):
+    assert lib.fmoe_version() == 1
+    # an invalid call reports through the status code and the message buffer, without touching a device
+    rc = lib.fmoe_topk_softmax(None, 4, 0, 1, 1, None, None, None)
+    assert rc == 1
+    assert b"E" in lib.fmoe_last_error()
+    rc = lib.fmoe_moe_align_block_size(None, 8, 4, 0, None, 0, None, 0, None, None)
+    assert rc == 1 and b"block" in lib.fmoe_last_error()
+
+
+def test_ops_refuse_cpu_tensors():
+    import flaggems_sglang_b200 as fg
+
+    x = torch.randn(4, 256)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        fg.fused_topk(x, torch.randn(4, 8), 2)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        fg.moe_align_block_size(torch.zeros(4, 2, dtype=torch.int32), 16, 8)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        fg.fused_experts(x, torch.randn(8, 64, 256), torch.randn(8, 256, 32), torch.rand(4, 2),
+                         torch.zeros(4, 2, dtype=torch.int32))
+
+
+def test_namespace_mirrors_reference_exports():
+    import flaggems_sglang_b200 as fg
+
+    for name in ("triton_kernel_fused_experts", "fused_moe_flagos", "fused_moe", "fused_experts",
+                 "moe_align_block_size", "topk", "grouped_topk", "fused_topk", "moe_sum"):
+        assert callable(getattr(fg, name))
+        assert name in fg.all_registered_ops()
+
+
+def test_reference_entry_point_keeps_its_assertions():
+    """Argument checks of the reference op fire before any device work (ref fused_moe.py:170-195)."""
+    import flaggems_sglang_b200 as fg
+
+    x = torch.randn(4, 128, dtype=torch.bfloat16)
+    w1 = torch.randn(8, 128, 512, dtype=torch.bfloat16)
+    w2 = torch.randn(8, 256, 128, dtype=torch.bfloat16)
+    with pytest.raises(AssertionError, match="use_fp8_w8a8 is not supported"):
+        fg.triton_kernel_fused_experts(x, w1, w2, None, None, None, use_fp8_w8a8=True)
+    with pytest.raises(AssertionError, match="Inplace is not supported"):
+        fg.triton_kernel_fused_experts(x, w1, w2, None, None, None, inplace=True)
+    with pytest.raises(AssertionError, match="hidden_states must be bfloat16"):
+        fg.triton_kernel_fused_experts(x.float(), w1, w2, None, None, None)
+    with pytest.raises(AssertionError, match="hidden size mismatch"):
+        fg.triton_kernel_fused_experts(x[:, :64], w1, w2, None, None, None)
+    with pytest.raises(ValueError, match="Unsupported FusedMoe activation"):
+        fg.triton_kernel_fused_experts(x, w1, w2, None, None, None, activation="relu")
+
+
+def test_variant_selection_is_shape_only():
+    from flaggems_sglang_b200.ops.fused_moe import _pick_variant
+
+    bf = torch.bfloat16
+    assert _pick_variant(torch.float32, 32, 8, 512, 256, None) == ("simt", 16)
+    assert _pick_variant(bf, 2, 8, 14336, 4096, None) == ("stream", 8)        # Mixtral T=1
+    assert _pick_variant(bf, 128, 8, 14336, 4096, None)[0] == "stream"        # Mixtral T=64
+    assert _pick_variant(bf, 8192, 8, 14336, 4096, None) == ("tcgen05", 128)  # Mixtral T=4096
+    assert _pick_variant(bf, 65536, 128, 768, 2048, None) == ("tcgen05", 128)
+    assert _pick_variant(torch.float8_e4m3fn, 512, 256, 2048, 7168, None)[0] == "stream"

@@ -1,0 +1,81 @@
+"""GPU parity: fp8 group quantisation, row gather and moe_sum against the CPU oracle (bit-exact)."""
+import pytest
+import torch
+
+from oracle import experts as OE
+from oracle import quant as OQ
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def fg():
+    import flaggems_sglang_b200 as fg
+
+    return fg
+
+
+@pytest.mark.parametrize("rows,K", [(1, 128), (7, 512), (64, 7168), (300, 2048)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_quant_group128_bit_exact(fg, rows, K, dtype):
+    torch.manual_seed(rows + K)
+    x = (torch.randn(rows, K) * torch.rand(rows, 1) * 4).to(dtype)
+    x[0, :128] = 0  # an all-zero group
+    q, s = fg.per_token_group_quant_fp8(x.cuda())
+    oq, os_ = OQ.quant_act_group128(x)
+    assert torch.equal(s.cpu(), os_)
+    assert torch.equal(q.cpu().view(torch.uint8), oq.view(torch.uint8))
+
+
+def test_weight_quant_matches_oracle(fg):
+    torch.manual_seed(0)
+    w = (torch.randn(3, 256, 384) / 16).bfloat16()
+    q, s = fg.quant_weight_block128(w.cuda())
+    oq, os_ = OQ.quant_weight_block128(w)
+    assert torch.equal(s.cpu(), os_)
+    assert torch.equal(q.cpu().view(torch.uint8), oq.view(torch.uint8))
+
+
+@pytest.mark.parametrize("T,k,H", [(1, 2, 256), (16, 2, 4096), (33, 8, 2048), (512, 8, 7168)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("scale", [None, 2.5])
+def test_moe_sum_bit_exact(fg, T, k, H, dtype, scale):
+    torch.manual_seed(T + k + H)
+    z = torch.randn(T, k, H).to(dtype)
+    out = torch.empty(T, H, dtype=dtype, device="cuda")
+    fg.moe_sum(z.cuda(), out, scale)
+    ref = OE.moe_sum(z).to(dtype)
+    if scale is not None:
+        ref = (ref.float() * scale).to(dtype)
+    assert torch.equal(out.cpu(), ref)
+
+
+def test_gather_rows_and_fused_gather_quant(fg):
+    from flaggems_sglang_b200 import _C
+
+    torch.manual_seed(1)
+    T, k, H, E, block = 37, 4, 512, 16, 16
+    x = torch.randn(T, H).bfloat16()
+    ids = torch.randint(0, E, (T, k), dtype=torch.int32)
+    s, e, n = fg.moe_align_block_size(ids.cuda(), block, E)
+    cap = s.numel()
+    out = torch.full((cap, H), 7.0, dtype=torch.bfloat16, device="cuda")
+    st = _C.stream_ptr()
+    _C.check(_C.lib().fmoe_gather_rows(x.cuda().data_ptr(), 2, cap, H, s.data_ptr(), k, T * k, n.data_ptr(),
+                                       out.data_ptr(), st))
+    sc = s.cpu().long()
+    used = int(n.item())
+    exp = torch.zeros(cap, H, dtype=torch.bfloat16)
+    valid = sc[:used] < T * k
+    exp[:used][valid] = x[sc[:used][valid] // k]
+    assert torch.equal(out.cpu()[:used], exp[:used])
+    assert (out.cpu()[used:] == 7.0).all()  # rows past the padded length are not touched
+    q = torch.empty(cap, H, dtype=torch.float8_e4m3fn, device="cuda")
+    qs = torch.empty(cap, H // 128, dtype=torch.float32, device="cuda")
+    _C.check(_C.lib().fmoe_quant_fp8_group128(x.cuda().data_ptr(), _C.BF16, cap, H, s.data_ptr(), k, T * k,
+                                              n.data_ptr(), q.data_ptr(), qs.data_ptr(), st))
+    oq, os_ = OQ.quant_act_group128(exp[:used])
+    vq = q.cpu().view(torch.uint8)[:used]
+    assert torch.equal(vq[valid], oq.view(torch.uint8)[valid])
+    assert torch.equal(qs.cpu()[:used][valid], os_[valid])
+    assert (vq[~valid] == 0).all() and (qs.cpu()[:used][~valid] == 1.0).all()

@@ -202,7 +202,9 @@ def time_steps(step, steps, warmup):
 
 def stage_times(step, steps):
     """Average device time per stage (ms) with events around each GEMM launch, over `steps` calls."""
-    from flaggems_sglang_b200.ops import fused_moe as FM
+    import importlib
+
+    FM = importlib.import_module("flaggems_sglang_b200.ops.fused_moe")
 
     FM.STAGE_EVENTS = []
     for _ in range(steps):

@@ -39,7 +39,8 @@ def quant_weight_block128(w: torch.Tensor):
         return torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts])
     blk = w.float().reshape(*lead, N // 128, 128, K // 128, 128)
     amax = blk.abs().amax(dim=(-3, -1))
-    scale = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    # tensor / tensor is an IEEE division on every device (tensor / python-scalar may multiply by a reciprocal)
+    scale = torch.where(amax > 0, amax / torch.full_like(amax, FP8_MAX), torch.ones_like(amax))
     q = (blk / scale[..., :, None, :, None]).clamp(-FP8_MAX, FP8_MAX).reshape(*lead, N, K)
     return q.to(torch.float8_e4m3fn), scale.contiguous()
 

@@ -92,7 +92,7 @@ def _quant_weight_cpu(w: torch.Tensor):
     N, K = w.shape
     blk = w.float().reshape(N // 128, 128, K // 128, 128)
     amax = blk.abs().amax(dim=(1, 3))
-    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    scale = torch.where(amax > 0, amax / torch.full_like(amax, 448.0), torch.ones_like(amax))
     q = (blk / scale[:, None, :, None]).clamp(-448.0, 448.0).reshape(N, K)
     return q.to(torch.float8_e4m3fn), scale.contiguous()
 

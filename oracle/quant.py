@@ -27,7 +27,7 @@ def quant_weight_block128(w: torch.Tensor):
     wf = w.detach().cpu().to(torch.float32)
     blk = wf.reshape(*lead, N // GROUP, GROUP, K // GROUP, GROUP)
     amax = blk.abs().amax(dim=(-3, -1))  # [..., N/128, K/128]
-    scale = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
+    scale = torch.where(amax > 0, amax / torch.full_like(amax, FP8_MAX), torch.ones_like(amax))
     q = blk / scale[..., :, None, :, None]
     return to_e4m3(q.reshape(*lead, N, K)), scale.contiguous()
 
@@ -47,7 +47,7 @@ def quant_act_group128(x: torch.Tensor):
     rows, K = x.shape
     xf = x.detach().cpu().to(torch.float32).reshape(rows, K // GROUP, GROUP)
     amax = xf.abs().amax(dim=-1).clamp_min(1e-10)
-    scale = amax / FP8_MAX
+    scale = amax / torch.full_like(amax, FP8_MAX)
     q = xf / scale[..., None]
     return to_e4m3(q.reshape(rows, K)), scale.contiguous()
 

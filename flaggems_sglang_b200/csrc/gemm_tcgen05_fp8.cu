@@ -1,0 +1,372 @@
+// Large-M grouped GEMM on e4m3 operands with 128x128 weight scales and 1x128 activation scales.
+//
+// tcgen05 accumulates in fp32 inside TMEM and cannot apply a different scale to every 128-wide K block, so
+// every K block (128 bytes = 128 e4m3 = one scale block) is multiplied into a FRESH 128x256 TMEM partial
+// (4 MMAs of K=32, the first one overwriting), and the epilogue warps fold it into register accumulators:
+//     acc[row, col] += partial[row, col] * a_scale[row, kb] * w_scale[col/128, kb]
+// Two TMEM partials (2 x 256 columns) ping-pong, so the MMAs of block kb+1 run while block kb is folded.
+//
+//   warps 0-7 : fold + epilogue.  Warp w owns TMEM lanes 32*(w%4).. (rows) and half h = w/4 of the columns:
+//               gemm1: gate columns [64h,64h+64) and the matching up columns [128+64h, ...), 128 accumulators;
+//               gemm2: columns [128h, 128h+128)
+//   warp 8    : TMA producer (A 128x128 B box, B two 128-row boxes), 4-stage ring
+//   warp 9    : MMA issuer
+// Same tile schedule, bounded waits and status word as the bf16 kernel; no multicast, cluster size 1.
+#include "gemm.cuh"
+#include "ptx_sm100.cuh"
+
+#include <mutex>
+
+namespace fmoe {
+
+extern __device__ int g_device_status;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int KBYTES = 128;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * KBYTES;
+constexpr int B_BYTES = BN * KBYTES;
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int TMEM_COLS = 512;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = (kEpiWarps + 2) * 32;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+struct Fp8Params {
+  const int32_t* sorted_token_ids;
+  const int32_t* expert_ids;
+  const int32_t* num_tokens_post_padded;
+  const float* row_scale;
+  const float* a_scale;  // [a_rows, kblocks]
+  const float* w_scale;  // [E, w_rows/128, kblocks]
+  void* out;
+  int64_t numel;
+  int64_t n;
+  int64_t w_rows;
+  int64_t sorted_cap;
+  int32_t num_experts;
+  int32_t kblocks;
+  int32_t n_tiles;
+  int32_t max_blocks;
+};
+
+__device__ __forceinline__ void report(int code) { atomicCAS(&g_device_status, 0, code); }
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity));
+}
+
+template <bool GATED>
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                const Fp8Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                      // [STAGES] TMA -> MMA
+  uint64_t* empty_bar = bars + STAGES;            // [STAGES] MMA -> TMA
+  uint64_t* part_full = bars + 2 * STAGES;        // [2] MMA -> fold
+  uint64_t* part_empty = bars + 2 * STAGES + 2;   // [2] fold -> MMA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(&full_bar[s], 1);
+      ptx::mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(&part_full[a], 1);
+      ptx::mbar_init(&part_empty[a], kEpiWarps * 32);
+    }
+    ptx::fence_barrier_init();
+  }
+  if (warp == kEpiWarps && lane == 0) {
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+  }
+  if (warp == kEpiWarps + 1) {
+    ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int used_blocks = min((int)(*p.num_tokens_post_padded / BM), p.max_blocks);
+  const int64_t total_tiles = (int64_t)used_blocks * p.n_tiles;
+  const int kblocks = p.kblocks;
+
+  if (warp == kEpiWarps) {
+    // ---------------- TMA producer ----------------
+    int stage = 0;
+    uint32_t phase = 0;
+    bool alive = true;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      const int m_blk = (int)(tile % used_blocks), n_tile = (int)(tile / used_blocks);
+      const int e = p.expert_ids[m_blk];
+      if (e < 0 || e >= p.num_experts) continue;
+      const int32_t row_a = m_blk * BM;
+      const int32_t row_b0 = (int32_t)((int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256));
+      const int32_t row_b1 = GATED ? (int32_t)(row_b0 + p.n) : row_b0 + 128;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        if (!warp_wait(&empty_bar[stage], phase ^ 1)) {
+          report(0x500 | stage);
+          alive = false;
+          break;
+        }
+        if (lane == 0) {
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          ptx::mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
+          const int32_t x = kb * KBYTES;  // element coordinate (1-byte elements)
+          ptx::tma_load_2d(sa, &map_a, x, row_a, &full_bar[stage]);
+          ptx::tma_load_2d(sb, &map_b, x, row_b0, &full_bar[stage]);
+          ptx::tma_load_2d(sb + B_BYTES / 2, &map_b, x, row_b1, &full_bar[stage]);
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+    if (alive) {  // drain our own bulk copies before leaving
+      for (int s = 0; s < STAGES; ++s) {
+        if (!warp_wait(&empty_bar[stage], phase ^ 1)) {
+          report(0x580 | stage);
+          break;
+        }
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == kEpiWarps + 1) {
+    // ---------------- MMA issuer: one fresh partial per K block ----------------
+    constexpr uint32_t idesc = ptx::make_idesc(/*e4m3*/ 0, BM, BN);
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t step = 0;  // K blocks issued so far by this CTA (selects the partial and its phase)
+    bool alive = true;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      const int m_blk = (int)(tile % used_blocks);
+      const int e = p.expert_ids[m_blk];
+      if (e < 0 || e >= p.num_experts) continue;
+      for (int kb = 0; kb < kblocks; ++kb, ++step) {
+        const int buf = step & 1;
+        const uint32_t buf_phase = (step >> 1) & 1;
+        if (!warp_wait(&part_empty[buf], buf_phase ^ 1)) {
+          report(0x600 | buf);
+          alive = false;
+          break;
+        }
+        if (!warp_wait(&full_bar[stage], phase)) {
+          report(0x640 | stage);
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t sa = ptx::smem_u32(smem + stage * STAGE_BYTES);
+          const uint64_t da = ptx::smem_desc_sw128(sa);
+          const uint64_t db = ptx::smem_desc_sw128(sa + A_BYTES);
+          const uint32_t d_tmem = tmem_base + buf * BN;
+#pragma unroll
+          for (int kk = 0; kk < KBYTES / 32; ++kk)
+            ptx::mma_f8f6f4_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, kk != 0);
+          ptx::mma_commit(&empty_bar[stage]);
+          ptx::mma_commit(&part_full[buf]);
+        }
+        __syncwarp();
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------- fold + epilogue (warps 0-7) ----------------
+    const int quarter = warp & 3, half = warp >> 2;
+    const int row = quarter * 32 + lane;
+    const int64_t sblocks_per_expert = p.w_rows / 128;
+    uint32_t step = 0;
+    bool alive = true;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      const int m_blk = (int)(tile % used_blocks), n_tile = (int)(tile / used_blocks);
+      const int e = p.expert_ids[m_blk];
+      if (e < 0 || e >= p.num_experts) continue;
+      const int64_t pos = (int64_t)m_blk * BM + row;
+      const bool in_cap = pos < p.sorted_cap;
+      const int32_t slot = in_cap ? p.sorted_token_ids[pos] : -1;
+      const bool valid = slot >= 0 && slot < p.numel;
+      const float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
+      const float* sa_row = p.a_scale + (in_cap ? pos : 0) * kblocks;
+      // weight-scale rows of the two 128-column halves of the accumulator
+      const int64_t sw_blk0 = GATED ? n_tile : 2 * (int64_t)n_tile;
+      const int64_t sw_blk1 = GATED ? (p.n / 128 + n_tile) : min(2 * (int64_t)n_tile + 1, sblocks_per_expert - 1);
+      const float* sw0 = p.w_scale + ((int64_t)e * sblocks_per_expert + sw_blk0) * kblocks;
+      const float* sw1 = p.w_scale + ((int64_t)e * sblocks_per_expert + sw_blk1) * kblocks;
+
+      float acc[128];
+#pragma unroll
+      for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+
+      float sa_n = in_cap ? sa_row[0] : 0.f, s0_n = sw0[0], s1_n = sw1[0];
+      for (int kb = 0; kb < kblocks; ++kb, ++step) {
+        const int buf = step & 1;
+        const uint32_t buf_phase = (step >> 1) & 1;
+        const float sa = sa_n;
+        const float f0 = sa * s0_n, f1 = sa * s1_n;
+        if (kb + 1 < kblocks) {  // prefetch the next block's scales while waiting for the MMAs
+          sa_n = in_cap ? sa_row[kb + 1] : 0.f;
+          s0_n = sw0[kb + 1];
+          s1_n = sw1[kb + 1];
+        }
+        if (!warp_wait(&part_full[buf], buf_phase)) {
+          report(0x700 | buf);
+          alive = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          // gemm1: c = 0,1 gate columns 64h + 32c; c = 2,3 up columns 128 + 64h + 32(c-2)
+          // gemm2: columns 128h + 32c
+          const int col = GATED ? ((c < 2) ? (64 * half + 32 * c) : (128 + 64 * half + 32 * (c - 2))) : (128 * half + 32 * c);
+          const float f = GATED ? ((c < 2) ? f0 : f1) : (half == 0 ? f0 : f1);
+          uint32_t v[32];
+          ptx::tmem_ld_32x32b_x32(taddr + col, v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(v[i]), f, acc[c * 32 + i]);
+        }
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(&part_empty[buf]);
+      }
+      if (!alive) break;
+
+      if constexpr (GATED) {
+        // acc[0..63] gate, acc[64..127] up, output columns n_tile*128 + 64h + [0,64)
+        if (in_cap) {
+          __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + pos * p.n + (int64_t)n_tile * 128 + 64 * half;
+          uint4* dst = reinterpret_cast<uint4*>(orow);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int i = v * 8 + j * 2;
+              w[j] = pack_bf16x2(silu_mul(acc[i] * rs, acc[64 + i] * rs), silu_mul(acc[i + 1] * rs, acc[64 + i + 1] * rs));
+            }
+            dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      } else {
+        const int64_t col0 = (int64_t)n_tile * 256 + 128 * half;
+        if (valid && col0 < p.n) {
+          __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)slot * p.n + col0;
+          uint4* dst = reinterpret_cast<uint4*>(orow);
+#pragma unroll
+          for (int v = 0; v < 16; ++v) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int i = v * 8 + j * 2;
+              w[j] = pack_bf16x2(acc[i] * rs, acc[i + 1] * rs);
+            }
+            dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kEpiWarps + 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+}  // namespace
+
+// defined in gemm_tcgen05.cu
+int make_tensor_map_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int elem_bytes, int box_rows,
+                       bool weights);
+int device_sm_count();
+
+namespace {
+
+template <bool GATED>
+int launch(const GemmParams& g, cudaStream_t st) {
+  static std::once_flag once_attr;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once_attr, [] {
+    attr_err = cudaFuncSetAttribute(grouped_gemm_tcgen05_fp8_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    SMEM_BYTES);
+  });
+  if (attr_err != cudaSuccess)
+    return fail(FMOE_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", SMEM_BYTES, cudaGetErrorString(attr_err));
+  const int64_t w_rows = GATED ? 2 * g.n : g.n;
+  CUtensorMap map_a, map_b;
+  int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 1, BM, false);
+  if (rc) return rc;
+  rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 1, 128, true);
+  if (rc) return rc;
+  Fp8Params p;
+  p.sorted_token_ids = g.sorted_token_ids;
+  p.expert_ids = g.expert_ids;
+  p.num_tokens_post_padded = g.num_tokens_post_padded;
+  p.row_scale = g.row_scale;
+  p.a_scale = g.a_scale;
+  p.w_scale = g.w_scale;
+  p.out = g.out;
+  p.numel = g.numel;
+  p.n = g.n;
+  p.w_rows = w_rows;
+  p.sorted_cap = g.sorted_cap;
+  p.num_experts = g.num_experts;
+  p.kblocks = (int)(g.k / 128);
+  p.n_tiles = (int)ceil_div<int64_t>(g.n, GATED ? 128 : 256);
+  p.max_blocks = (int)g.max_blocks;
+  const int64_t max_tiles = g.max_blocks * p.n_tiles;
+  const int sms = device_sm_count();
+  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sms > 0 ? sms : 148, max_tiles));
+  grouped_gemm_tcgen05_fp8_kernel<GATED><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
+  return launch_status("grouped_gemm_tcgen05_fp8_kernel");
+}
+
+}  // namespace
+
+bool gemm_tcgen05_fp8_supports(const GemmParams& p, bool gated) {
+  if (p.dtype != FMOE_E4M3 || p.out_dtype != FMOE_BF16) return false;
+  if (p.block_size != BM || p.a_gather) return false;
+  if (p.k <= 0 || p.k % 128 != 0 || p.n <= 0 || p.n % 128 != 0) return false;
+  if (!p.a_scale || !p.w_scale) return false;
+  if (!aligned16(p.a) || !aligned16(p.w) || !aligned16(p.out)) return false;
+  if ((int64_t)p.num_experts * (gated ? 2 * p.n : p.n) >= (1ll << 31) || p.a_rows >= (1ll << 31)) return false;
+  if (p.max_blocks >= (1ll << 24)) return false;
+  return true;
+}
+
+int gemm_tcgen05_fp8(const GemmParams& p, bool gated, cudaStream_t st) {
+  if (!gemm_tcgen05_fp8_supports(p, gated))
+    return fail(FMOE_ERR_UNSUPPORTED,
+                "tcgen05 fp8 gemm: needs e4m3 in, bf16 out, block_size 128, sorted input rows, n and k multiples of 128");
+  if (p.max_blocks <= 0) return FMOE_OK;
+  return gated ? launch<true>(p, st) : launch<false>(p, st);
+}
+
+}  // namespace fmoe

@@ -9,8 +9,8 @@ CUDA kernels behind the C ABI (include/fmoe_b200.h); nothing falls back to
 torch or the CPU.
 
 Kernel selection (per call, from shapes only, no host sync):
-  rows per active expert <= ~40  -> "stream": small-M weight-streaming kernel,
-                                    moe_align block 8/16/32, x gathered on the fly
+  rows per active expert <= 8    -> "stream": small-M weight-streaming kernel,
+                                    moe_align block 8/16, x gathered on the fly
   larger                         -> "tcgen05": rows copied into expert-sorted order
                                     (block 128), TMA + tcgen05/TMEM persistent kernel
   fp32 inputs                    -> "simt"
@@ -116,7 +116,7 @@ def _pick_variant(dtype, numel: int, E: int, I: int, H: int, forced: Optional[st
     if forced is None:
         stream_ok = (H % 128 == 0) and (I % 128 == 0)
         tc_ok = dtype == torch.bfloat16 and I % 128 == 0 and H % 32 == 0
-        if stream_ok and (rows <= 40 or not tc_ok):
+        if stream_ok and (rows <= 8 or not tc_ok):
             forced = "stream"
         elif tc_ok:
             forced = "tcgen05"

@@ -103,7 +103,8 @@ def test_variant_selection_is_shape_only():
     bf = torch.bfloat16
     assert _pick_variant(torch.float32, 32, 8, 512, 256, None) == ("simt", 16)
     assert _pick_variant(bf, 2, 8, 14336, 4096, None) == ("stream", 8)        # Mixtral T=1
-    assert _pick_variant(bf, 128, 8, 14336, 4096, None)[0] == "stream"        # Mixtral T=64
+    assert _pick_variant(bf, 32, 8, 14336, 4096, None)[0] == "stream"         # Mixtral T=16
+    assert _pick_variant(bf, 128, 8, 14336, 4096, None)[0] == "tcgen05"       # Mixtral T=64 (HBM-bound, 128-row tiles)
     assert _pick_variant(bf, 8192, 8, 14336, 4096, None) == ("tcgen05", 128)  # Mixtral T=4096
     assert _pick_variant(bf, 65536, 128, 768, 2048, None) == ("tcgen05", 128)
     assert _pick_variant(torch.float8_e4m3fn, 512, 256, 2048, 7168, None)[0] == "stream"

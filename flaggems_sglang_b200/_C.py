@@ -18,6 +18,7 @@ OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_TIMEOUT = 0, 1, 2, 3,
 F32, BF16, E4M3 = 0, 1, 2
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_STREAM, VARIANT_TCGEN05 = 0, 1, 2, 3
 VARIANTS = {"auto": 0, "simt": 1, "stream": 2, "tcgen05": 3}
+VARIANT_NAMES = {v: k for k, v in VARIANTS.items()}
 
 DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float8_e4m3fn: E4M3}
 
@@ -42,6 +43,21 @@ class GemmArgs(Structure):
     ]
 
 
+class FusedArgs(Structure):
+    """Mirror of struct fmoe_fused_args."""
+
+    _fields_ = [
+        ("dtype", c_int32), ("variant", c_int32), ("num_experts", c_int32), ("top_k", c_int32),
+        ("apply_router_weight_on_input", c_int32), ("no_combine", c_int32), ("zero_dropped", c_int32),
+        ("reserved", c_int32),
+        ("T", c_int64), ("H", c_int64), ("I", c_int64),
+        ("routed_scaling_factor", c_float), ("reserved_f", c_float),
+        ("hidden", c_void_p), ("w1", c_void_p), ("w2", c_void_p), ("w1_scale", c_void_p), ("w2_scale", c_void_p),
+        ("topk_weights", c_void_p), ("topk_ids", c_void_p), ("out", c_void_p), ("workspace", c_void_p),
+        ("workspace_bytes", c_int64),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/fmoe_b200.h declares
 SIGNATURES = {
     "fmoe_version": (c_int, []),
@@ -59,6 +75,9 @@ SIGNATURES = {
     "fmoe_gemm1_silu": (c_int, [POINTER(GemmArgs), c_void_p]),
     "fmoe_gemm2": (c_int, [POINTER(GemmArgs), c_void_p]),
     "fmoe_moe_sum": (c_int, [c_void_p, c_int, c_int64, c_int, c_int64, c_float, c_void_p, c_void_p]),
+    "fmoe_pick_variant": (c_int, [c_int, c_int64, c_int, c_int64, c_int64, c_int, POINTER(c_int), POINTER(c_int)]),
+    "fmoe_fused_experts_workspace_bytes": (c_int64, [POINTER(FusedArgs)]),
+    "fmoe_fused_experts": (c_int, [POINTER(FusedArgs), c_void_p]),
     "fmoe_check_device_status": (c_int, [c_void_p]),
 }
 

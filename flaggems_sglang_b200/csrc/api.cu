@@ -45,7 +45,7 @@ int dispatch_gemm(const fmoe_gemm_args* args, bool gated, void* stream, const ch
   auto st = (cudaStream_t)stream;
   int variant = a.variant;
   if (variant == FMOE_VARIANT_AUTO) {
-    if (gemm_tcgen05_supports(a, gated))
+    if (gemm_tcgen05_supports(a, gated) || gemm_tcgen05_fp8_supports(a, gated))
       variant = FMOE_VARIANT_TCGEN05;
     else if (gemm_stream_supports(a, gated))
       variant = FMOE_VARIANT_STREAM;
@@ -55,7 +55,8 @@ int dispatch_gemm(const fmoe_gemm_args* args, bool gated, void* stream, const ch
   switch (variant) {
     case FMOE_VARIANT_SIMT: return gemm_simt(a, gated, st);
     case FMOE_VARIANT_STREAM: return gemm_stream(a, gated, st);
-    case FMOE_VARIANT_TCGEN05: return gemm_tcgen05(a, gated, st);
+    case FMOE_VARIANT_TCGEN05:
+      return a.dtype == FMOE_E4M3 ? gemm_tcgen05_fp8(a, gated, st) : gemm_tcgen05(a, gated, st);
   }
   return fail(FMOE_ERR_INVALID_ARG, "%s: unknown variant %d", who, a.variant);
 }

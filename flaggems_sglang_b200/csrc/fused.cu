@@ -1,0 +1,215 @@
+// fmoe_fused_experts: the whole expert computation behind one C call.  Host-side orchestration only:
+// it carves the caller's workspace and enqueues the kernels of the other files on the given stream.
+#include "fused.cuh"
+
+namespace fmoe {
+
+int pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forced, int* variant, int* block) {
+  if (dtype == FMOE_F32) {
+    if (forced != FMOE_VARIANT_AUTO && forced != FMOE_VARIANT_SIMT)
+      return fail(FMOE_ERR_UNSUPPORTED, "fp32 inputs run on the simt kernels only");
+    *variant = FMOE_VARIANT_SIMT;
+    *block = 16;
+    return FMOE_OK;
+  }
+  if (dtype != FMOE_BF16 && dtype != FMOE_E4M3) return fail(FMOE_ERR_INVALID_ARG, "unknown dtype %d", dtype);
+  const int64_t active = std::max<int64_t>(1, std::min<int64_t>(E, numel));
+  const double rows = (double)numel / (double)active;  // rows per active expert if routing were uniform
+  const bool stream_ok = (H % 128 == 0) && (I % 128 == 0);
+  const bool tc_ok = dtype == FMOE_BF16 ? (I % 128 == 0 && H % 32 == 0) : (I % 128 == 0 && H % 128 == 0);
+  int v = forced;
+  if (v == FMOE_VARIANT_AUTO) {
+    if (stream_ok && (rows <= 8.0 || !tc_ok)) v = FMOE_VARIANT_STREAM;
+    else if (tc_ok) v = FMOE_VARIANT_TCGEN05;
+    else v = FMOE_VARIANT_SIMT;
+  }
+  switch (v) {
+    case FMOE_VARIANT_TCGEN05:
+      if (!tc_ok) return fail(FMOE_ERR_UNSUPPORTED, "tcgen05 kernels need I %% 128 == 0 and H %% 32 == 0 (128 for e4m3)");
+      *block = 128;
+      break;
+    case FMOE_VARIANT_STREAM:
+      if (!stream_ok) return fail(FMOE_ERR_UNSUPPORTED, "stream kernels need H %% 128 == 0 and I %% 128 == 0");
+      *block = rows <= 6.0 ? 8 : (rows <= 12.0 ? 16 : 32);
+      break;
+    case FMOE_VARIANT_SIMT:
+      *block = 16;
+      break;
+    default:
+      return fail(FMOE_ERR_INVALID_ARG, "unknown variant %d", forced);
+  }
+  *variant = v;
+  return FMOE_OK;
+}
+
+namespace {
+inline int64_t up256(int64_t v) { return (v + 255) & ~int64_t(255); }
+}
+
+int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
+  FMOE_REQUIRE(a.num_experts >= 1 && a.num_experts <= 1024 && a.top_k >= 1, "fused_experts: bad E or top_k");
+  FMOE_REQUIRE(a.T >= 0 && a.H >= 1 && a.I >= 1, "fused_experts: bad sizes T=%lld H=%lld I=%lld", (long long)a.T,
+               (long long)a.H, (long long)a.I);
+  FMOE_REQUIRE(a.dtype == FMOE_F32 || a.dtype == FMOE_BF16 || a.dtype == FMOE_E4M3, "fused_experts: unknown dtype %d", a.dtype);
+  if (a.dtype == FMOE_E4M3)
+    FMOE_REQUIRE(a.H % 128 == 0 && a.I % 128 == 0, "fused_experts: e4m3 needs H and I to be multiples of 128");
+  FusedPlan& p = *pl;
+  p.numel = a.T * a.top_k;
+  int rc = pick_variant(a.dtype, p.numel, a.num_experts, a.I, a.H, a.variant, &p.variant, &p.block);
+  if (rc) return rc;
+  p.cap = p.numel + (int64_t)a.num_experts * (p.block - 1);
+  p.nblk = ceil_div<int64_t>(p.cap, p.block);
+  p.max_blocks = std::min<int64_t>(p.cap / p.block, p.numel);
+  const int64_t eb = a.dtype == FMOE_F32 ? 4 : 2;  // element size of hidden / out / z
+  const bool fp8 = a.dtype == FMOE_E4M3, tc = p.variant == FMOE_VARIANT_TCGEN05;
+  int64_t off = 0;
+  auto take = [&](int64_t bytes) {
+    int64_t o = off;
+    off += up256(bytes);
+    return o;
+  };
+  p.off_sorted = take(p.cap * 4);
+  p.off_expert = take(p.nblk * 4);
+  p.off_npp = take(16);
+  p.off_xs = p.off_xs_scale = p.off_actq = p.off_actq_scale = -1;
+  if (fp8) {
+    const int64_t xrows = tc ? p.cap : a.T;
+    p.off_xs = take(xrows * a.H);
+    p.off_xs_scale = take(xrows * (a.H / 128) * 4);
+    p.act_elem = tc ? 2 : 4;  // bf16 from the tcgen05 epilogue, fp32 from the streaming kernel
+    p.off_act = take(p.cap * a.I * p.act_elem);
+    p.off_actq = take(p.cap * a.I);
+    p.off_actq_scale = take(p.cap * (a.I / 128) * 4);
+  } else {
+    if (tc) p.off_xs = take(p.cap * a.H * eb);
+    p.act_elem = (int)eb;
+    p.off_act = take(p.cap * a.I * eb);
+  }
+  p.off_z = a.no_combine ? -1 : take(p.numel * a.H * eb);
+  p.total = off;
+  return FMOE_OK;
+}
+
+int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* stream) {
+  if (a.T == 0) return FMOE_OK;
+  FMOE_REQUIRE(a.hidden && a.w1 && a.w2 && a.topk_weights && a.topk_ids && a.out, "fused_experts: null pointer");
+  const bool fp8 = a.dtype == FMOE_E4M3, tc = p.variant == FMOE_VARIANT_TCGEN05;
+  if (fp8) FMOE_REQUIRE(a.w1_scale && a.w2_scale, "fused_experts: e4m3 needs w1_scale and w2_scale");
+  const int io = fp8 ? FMOE_BF16 : a.dtype;  // dtype of hidden / z / out
+  const int64_t eb = io == FMOE_F32 ? 4 : 2;
+  int32_t* sorted = reinterpret_cast<int32_t*>(ws + p.off_sorted);
+  int32_t* experts = reinterpret_cast<int32_t*>(ws + p.off_expert);
+  int32_t* npp = reinterpret_cast<int32_t*>(ws + p.off_npp);
+  void* act = ws + p.off_act;
+  void* z = a.no_combine ? a.out : (void*)(ws + p.off_z);
+  auto st = (cudaStream_t)stream;
+
+  int rc = fmoe_moe_align_block_size(a.topk_ids, p.numel, a.num_experts, p.block, sorted, p.cap, experts, p.nblk, npp, stream);
+  if (rc) return rc;
+  if (a.zero_dropped) FMOE_CUDA_OK(cudaMemsetAsync(z, 0, (size_t)(p.numel * a.H * eb), st));
+
+  fmoe_gemm_args g{};
+  g.variant = p.variant;
+  g.num_experts = a.num_experts;
+  g.top_k = a.top_k;
+  g.block_size = p.block;
+  g.numel = p.numel;
+  g.sorted_cap = p.cap;
+  g.max_blocks = p.max_blocks;
+  g.sorted_token_ids = sorted;
+  g.expert_ids = experts;
+  g.num_tokens_post_padded = npp;
+
+  fmoe_gemm_args g1 = g, g2 = g;
+  g1.n = a.I;
+  g1.k = a.H;
+  g1.w = a.w1;
+  g1.out = act;
+  g1.row_scale = a.apply_router_weight_on_input ? a.topk_weights : nullptr;
+  g2.n = a.H;
+  g2.k = a.I;
+  g2.w = a.w2;
+  g2.out = z;
+  g2.a_gather = 0;
+  g2.a_rows = p.cap;
+  g2.row_scale = a.apply_router_weight_on_input ? nullptr : a.topk_weights;
+  g2.out_dtype = io;
+
+  if (!fp8) {
+    g1.dtype = g1.out_dtype = g2.dtype = a.dtype;
+    if (tc) {
+      void* xs = ws + p.off_xs;
+      rc = fmoe_gather_rows(a.hidden, (int)eb, p.cap, a.H, sorted, a.top_k, p.numel, npp, xs, stream);
+      if (rc) return rc;
+      g1.a = xs;
+      g1.a_rows = p.cap;
+      g1.a_gather = 0;
+    } else {
+      g1.a = a.hidden;
+      g1.a_rows = a.T;
+      g1.a_gather = 1;
+    }
+    g2.a = act;
+  } else {
+    void* xq = ws + p.off_xs;
+    float* xsc = reinterpret_cast<float*>(ws + p.off_xs_scale);
+    if (tc)
+      rc = fmoe_quant_fp8_group128(a.hidden, FMOE_BF16, p.cap, a.H, sorted, a.top_k, p.numel, npp, xq, xsc, stream);
+    else
+      rc = fmoe_quant_fp8_group128(a.hidden, FMOE_BF16, a.T, a.H, nullptr, 1, 0, nullptr, xq, xsc, stream);
+    if (rc) return rc;
+    g1.dtype = g2.dtype = FMOE_E4M3;
+    g1.out_dtype = p.act_elem == 2 ? FMOE_BF16 : FMOE_F32;
+    g1.a = xq;
+    g1.a_scale = xsc;
+    g1.a_rows = tc ? p.cap : a.T;
+    g1.a_gather = tc ? 0 : 1;
+    g1.w_scale = a.w1_scale;
+    g2.a = ws + p.off_actq;
+    g2.a_scale = reinterpret_cast<float*>(ws + p.off_actq_scale);
+    g2.w_scale = a.w2_scale;
+  }
+  rc = fmoe_gemm1_silu(&g1, stream);
+  if (rc) return rc;
+  if (fp8) {
+    rc = fmoe_quant_fp8_group128(act, g1.out_dtype, p.cap, a.I, nullptr, 1, 0, npp, ws + p.off_actq,
+                                 reinterpret_cast<float*>(ws + p.off_actq_scale), stream);
+    if (rc) return rc;
+  }
+  rc = fmoe_gemm2(&g2, stream);
+  if (rc) return rc;
+  if (a.no_combine) return FMOE_OK;
+  return fmoe_moe_sum(z, io, a.T, a.top_k, a.H, a.routed_scaling_factor == 0.f ? 1.0f : a.routed_scaling_factor, a.out, stream);
+}
+
+}  // namespace fmoe
+
+extern "C" int fmoe_pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forced_variant,
+                                 int* variant_out, int* block_out) {
+  if (!variant_out || !block_out) return fmoe::fail(FMOE_ERR_INVALID_ARG, "pick_variant: null output pointer");
+  return fmoe::pick_variant(dtype, numel, E, I, H, forced_variant, variant_out, block_out);
+}
+
+extern "C" int64_t fmoe_fused_experts_workspace_bytes(const fmoe_fused_args* args) {
+  if (!args) {
+    fmoe::fail(FMOE_ERR_INVALID_ARG, "fused_experts: args is null");
+    return -1;
+  }
+  fmoe::FusedPlan p;
+  if (fmoe::plan_fused(*args, &p)) return -1;
+  return p.total;
+}
+
+extern "C" int fmoe_fused_experts(const fmoe_fused_args* args, void* stream) {
+  using namespace fmoe;
+  if (!args) return fail(FMOE_ERR_INVALID_ARG, "fused_experts: args is null");
+  FusedPlan p;
+  int rc = plan_fused(*args, &p);
+  if (rc) return rc;
+  if (args->T == 0) return FMOE_OK;
+  FMOE_REQUIRE(args->workspace && (reinterpret_cast<uintptr_t>(args->workspace) & 255u) == 0,
+               "fused_experts: workspace must be non-null and 256-byte aligned");
+  FMOE_REQUIRE(args->workspace_bytes >= p.total, "fused_experts: workspace too small (%lld < %lld bytes)",
+               (long long)args->workspace_bytes, (long long)p.total);
+  return run_fused(*args, p, reinterpret_cast<uint8_t*>(args->workspace), stream);
+}

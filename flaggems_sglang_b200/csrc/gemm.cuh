@@ -13,10 +13,12 @@ using GemmParams = fmoe_gemm_args;
 int gemm_simt(const GemmParams& p, bool gated, cudaStream_t st);
 int gemm_stream(const GemmParams& p, bool gated, cudaStream_t st);
 int gemm_tcgen05(const GemmParams& p, bool gated, cudaStream_t st);
+int gemm_tcgen05_fp8(const GemmParams& p, bool gated, cudaStream_t st);
 
 // true when the variant can run these arguments (shape / alignment / dtype rules)
 bool gemm_stream_supports(const GemmParams& p, bool gated);
 bool gemm_tcgen05_supports(const GemmParams& p, bool gated);
+bool gemm_tcgen05_fp8_supports(const GemmParams& p, bool gated);
 
 // device status word written by bounded waits (gemm_tcgen05.cu)
 int read_and_clear_device_status(cudaStream_t st, int* status_out);

@@ -305,9 +305,22 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+}  // namespace
+
+int device_sm_count() {
+  static int sm_count = 0;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  });
+  return sm_count;
+}
+
 // 2-D row-major [rows, cols] tensor of `elem_bytes` elements; box = 128 bytes x box_rows, 128-byte swizzle.
-int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int elem_bytes, int box_rows,
-             bool weights) {
+int make_tensor_map_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int elem_bytes, int box_rows,
+                       bool weights) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -323,16 +336,12 @@ int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int
   return FMOE_OK;
 }
 
+namespace {
+
 template <bool GATED>
 int launch(const GemmParams& g, cudaStream_t st) {
-  static int sm_count = 0;
-  static std::once_flag once;
+  const int sm_count = device_sm_count();
   static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-  });
   static std::once_flag once_attr;
   std::call_once(once_attr, [] {
     attr_err = cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -343,9 +352,9 @@ int launch(const GemmParams& g, cudaStream_t st) {
 
   const int64_t w_rows = GATED ? 2 * g.n : g.n;
   CUtensorMap map_a, map_b;
-  int rc = make_map(&map_a, g.a, g.a_rows, g.k, 2, BM, false);
+  int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 2, BM, false);
   if (rc) return rc;
-  rc = make_map(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 2, 128, true);
+  rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 2, 128, true);
   if (rc) return rc;
 
   TcParams p;

@@ -105,36 +105,18 @@ def standard_topk_to_routing(topk_weights: torch.Tensor, topk_ids: torch.Tensor,
 # kernel selection
 # --------------------------------------------------------------------------
 def _pick_variant(dtype, numel: int, E: int, I: int, H: int, forced: Optional[str]):
-    """-> (variant name, moe_align block size)"""
-    forced = forced or os.environ.get("FMOE_VARIANT") or None
-    if dtype == torch.float32:
-        if forced not in (None, "simt"):
-            raise ValueError("fp32 inputs run on the simt kernels only")
-        return "simt", 16
-    active = max(1, min(E, numel))
-    rows = numel / active
-    if forced is None:
-        stream_ok = (H % 128 == 0) and (I % 128 == 0)
-        tc_ok = dtype == torch.bfloat16 and I % 128 == 0 and H % 32 == 0
-        if stream_ok and (rows <= 8 or not tc_ok):
-            forced = "stream"
-        elif tc_ok:
-            forced = "tcgen05"
-        elif stream_ok:
-            forced = "stream"
-        else:
-            forced = "simt"
-    if forced == "tcgen05":
-        return "tcgen05", 128
-    if forced == "stream":
-        if rows <= 6:
-            return "stream", 8
-        if rows <= 12:
-            return "stream", 16
-        return "stream", 32
-    if forced == "simt":
-        return "simt", 16
-    raise ValueError(f"unknown variant {forced!r}")
+    """-> (kernel family name, moe_align block size); the choice is made by the library (fmoe_pick_variant)."""
+    import ctypes
+
+    forced = forced or os.environ.get("FMOE_VARIANT") or "auto"
+    if forced not in _C.VARIANTS:
+        raise ValueError(f"unknown variant {forced!r}")
+    v, b = ctypes.c_int(0), ctypes.c_int(0)
+    rc = _C.lib().fmoe_pick_variant(_C.DTYPE_CODE[dtype], numel, E, I, H, _C.VARIANTS[forced], ctypes.byref(v),
+                                    ctypes.byref(b))
+    if rc != _C.OK:
+        raise ValueError(_C.lib().fmoe_last_error().decode())
+    return _C.VARIANT_NAMES[v.value], b.value
 
 
 def _gemm_args(**kw) -> _C.GemmArgs:
@@ -226,9 +208,29 @@ def fused_experts(
 
     lib = _C.lib()
     st = _C.stream_ptr(dev)
+    if STAGE_EVENTS is None:
+        # production path: one library call, intermediates in one workspace tensor
+        forced = variant or os.environ.get("FMOE_VARIANT") or "auto"
+        if forced not in _C.VARIANTS:
+            raise ValueError(f"unknown variant {forced!r}")
+        out = torch.empty((T, k, H) if no_combine else (T, H), dtype=out_dtype, device=dev)
+        fa = _C.FusedArgs(
+            dtype=_C.E4M3 if use_fp8_w8a8 else _C.DTYPE_CODE[out_dtype], variant=_C.VARIANTS[forced], num_experts=E,
+            top_k=k, apply_router_weight_on_input=int(apply_router_weight_on_input), no_combine=int(no_combine),
+            zero_dropped=int(expert_map is not None), T=T, H=H, I=I,
+            routed_scaling_factor=1.0 if routed_scaling_factor is None else float(routed_scaling_factor),
+            hidden=x.data_ptr(), w1=w1.data_ptr(), w2=w2.data_ptr(), w1_scale=_C.ptr(w1_scale),
+            w2_scale=_C.ptr(w2_scale), topk_weights=wts.data_ptr(), topk_ids=ids.data_ptr(), out=out.data_ptr())
+        need = lib.fmoe_fused_experts_workspace_bytes(fa)
+        if need < 0:
+            _C.check(_C.ERR_INVALID_ARG)
+        ws = torch.empty(max(int(need), 256), dtype=torch.uint8, device=dev)
+        fa.workspace, fa.workspace_bytes = ws.data_ptr(), ws.numel()
+        _C.check(lib.fmoe_fused_experts(fa, st))
+        return out
+
+    # profiling path (STAGE_EVENTS set): the same kernels launched one by one with events around the GEMMs
     name, block = _pick_variant(w1.dtype if not use_fp8_w8a8 else torch.float8_e4m3fn, numel, E, I, H, variant)
-    if use_fp8_w8a8 and name == "tcgen05":
-        name, block = _pick_variant(torch.float8_e4m3fn, numel, E, I, H, "stream")
     vcode = _C.VARIANTS[name]
 
     sorted_ids, expert_ids, num_post = moe_align_block_size(ids, block, E)
@@ -264,19 +266,28 @@ def fused_experts(
         with _stage("gemm2_" + name):
             _C.check(lib.fmoe_gemm2(g2, st))
     else:
-        xq = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=dev)
-        xsc = torch.empty((T, H // 128), dtype=torch.float32, device=dev)
-        _C.check(lib.fmoe_quant_fp8_group128(x.data_ptr(), _C.BF16, T, H, None, 1, 0, None, xq.data_ptr(),
-                                             xsc.data_ptr(), st))
-        act = torch.empty((cap, I), dtype=torch.float32, device=dev)
-        g1 = _gemm_args(dtype=_C.E4M3, out_dtype=_C.F32, a_gather=1, n=I, k=H, a_rows=T, a=xq.data_ptr(),
+        if name == "tcgen05":
+            # rows quantised straight into the padded expert-sorted order (gather fused into the quantiser)
+            xq = torch.empty((cap, H), dtype=torch.float8_e4m3fn, device=dev)
+            xsc = torch.empty((cap, H // 128), dtype=torch.float32, device=dev)
+            _C.check(lib.fmoe_quant_fp8_group128(x.data_ptr(), _C.BF16, cap, H, sorted_ids.data_ptr(), k, numel,
+                                                 num_post.data_ptr(), xq.data_ptr(), xsc.data_ptr(), st))
+            a_rows, gather, act_dtype, act_code = cap, 0, torch.bfloat16, _C.BF16
+        else:
+            xq = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=dev)
+            xsc = torch.empty((T, H // 128), dtype=torch.float32, device=dev)
+            _C.check(lib.fmoe_quant_fp8_group128(x.data_ptr(), _C.BF16, T, H, None, 1, 0, None, xq.data_ptr(),
+                                                 xsc.data_ptr(), st))
+            a_rows, gather, act_dtype, act_code = T, 1, torch.float32, _C.F32
+        act = torch.empty((cap, I), dtype=act_dtype, device=dev)
+        g1 = _gemm_args(dtype=_C.E4M3, out_dtype=act_code, a_gather=gather, n=I, k=H, a_rows=a_rows, a=xq.data_ptr(),
                         a_scale=xsc.data_ptr(), w=w1.data_ptr(), w_scale=w1_scale.data_ptr(),
                         row_scale=row_w if apply_router_weight_on_input else None, out=act.data_ptr(), **common)
         with _stage("gemm1_fp8_" + name):
             _C.check(lib.fmoe_gemm1_silu(g1, st))
         aq = torch.empty((cap, I), dtype=torch.float8_e4m3fn, device=dev)
         asc = torch.empty((cap, I // 128), dtype=torch.float32, device=dev)
-        _C.check(lib.fmoe_quant_fp8_group128(act.data_ptr(), _C.F32, cap, I, None, 1, 0, num_post.data_ptr(),
+        _C.check(lib.fmoe_quant_fp8_group128(act.data_ptr(), act_code, cap, I, None, 1, 0, num_post.data_ptr(),
                                              aq.data_ptr(), asc.data_ptr(), st))
         g2 = _gemm_args(dtype=_C.E4M3, out_dtype=_C.BF16, a_gather=0, n=H, k=I, a_rows=cap, a=aq.data_ptr(),
                         a_scale=asc.data_ptr(), w=w2.data_ptr(), w_scale=w2_scale.data_ptr(),

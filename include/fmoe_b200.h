@@ -163,6 +163,45 @@ int fmoe_moe_sum(const void* z, int dtype, int64_t T, int k, int64_t H, float sc
                  void* out, void* stream);
 
 /*
+ * Whole expert computation in one call: align -> [row gather / activation quantisation] -> gemm1+silu ->
+ * [quantisation] -> gemm2 * weight -> moe_sum.  Takes over src/flaggems_sglang/ops/fused_moe.py:197-232
+ * (`triton_kernel_fused_experts` body) on the serving-side layouts w1 [E,2I,H], w2 [E,H,I].
+ * All intermediates live in the caller's `workspace` (size from fmoe_fused_experts_workspace_bytes);
+ * nothing is allocated and the host is never synchronised.
+ */
+typedef struct fmoe_fused_args {
+  int32_t dtype;        /* FMOE_F32 | FMOE_BF16: type of hidden/w1/w2/out; FMOE_E4M3: e4m3 weights with
+                           128x128 scales, bf16 hidden/out, activations quantised per token per 128 channels */
+  int32_t variant;      /* FMOE_VARIANT_* (AUTO: chosen from the shape)                                   */
+  int32_t num_experts;  /* E                                                                              */
+  int32_t top_k;        /* k                                                                              */
+  int32_t apply_router_weight_on_input; /* 1: top-k weight scales the gemm1 input rows instead of gemm2's output */
+  int32_t no_combine;   /* 1: out is [T,k,H] (rows by flat slot), no sum over k                            */
+  int32_t zero_dropped; /* 1: slots whose id is outside [0,E) must read as zero (expert-parallel shards)  */
+  int32_t reserved;
+  int64_t T, H, I;
+  float routed_scaling_factor; /* applied after the sum when != 1 (ignored with no_combine)              */
+  float reserved_f;
+  const void* hidden;   /* [T,H]                                                                          */
+  const void* w1;       /* [E,2I,H]                                                                       */
+  const void* w2;       /* [E,H,I]                                                                        */
+  const float* w1_scale;/* e4m3: [E,2I/128,H/128]                                                         */
+  const float* w2_scale;/* e4m3: [E,H/128,I/128]                                                          */
+  const float* topk_weights; /* [T,k]                                                                     */
+  const int32_t* topk_ids;   /* [T,k]                                                                     */
+  void* out;            /* [T,H] or [T,k,H]                                                               */
+  void* workspace;      /* 256-byte aligned                                                               */
+  int64_t workspace_bytes;
+} fmoe_fused_args;
+
+/* Kernel family and moe_align block the AUTO choice takes for a shape.  forced_variant may be AUTO. */
+int fmoe_pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forced_variant,
+                      int* variant_out, int* block_out);
+/* Bytes of workspace fmoe_fused_experts needs for these arguments (pointers are not read); < 0 on error. */
+int64_t fmoe_fused_experts_workspace_bytes(const fmoe_fused_args* args);
+int fmoe_fused_experts(const fmoe_fused_args* args, void* stream);
+
+/*
  * Reads and clears the device-side status word that bounded waits inside the
  * tcgen05 kernels set when they give up.  Synchronises `stream`.
  * Returns FMOE_OK or FMOE_ERR_DEVICE_TIMEOUT.

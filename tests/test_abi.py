@@ -44,6 +44,8 @@ def test_struct_layout_matches_header():
     # 8 int32 + 6 int64 + 10 pointers
     assert ctypes.sizeof(_C.GemmArgs) == 8 * 4 + 6 * 8 + 10 * 8
     assert _C.GemmArgs.numel.offset == 32 and _C.GemmArgs.a.offset == 80
+    # 8 int32 + 3 int64 + 2 float + 9 pointers + 1 int64
+    assert ctypes.sizeof(_C.FusedArgs) == 144 and _C.FusedArgs.hidden.offset == 64
 
 
 def test_version_and_error_buffer(lib):
@@ -107,4 +109,5 @@ def test_variant_selection_is_shape_only():
     assert _pick_variant(bf, 128, 8, 14336, 4096, None)[0] == "tcgen05"       # Mixtral T=64 (HBM-bound, 128-row tiles)
     assert _pick_variant(bf, 8192, 8, 14336, 4096, None) == ("tcgen05", 128)  # Mixtral T=4096
     assert _pick_variant(bf, 65536, 128, 768, 2048, None) == ("tcgen05", 128)
-    assert _pick_variant(torch.float8_e4m3fn, 512, 256, 2048, 7168, None)[0] == "stream"
+    assert _pick_variant(torch.float8_e4m3fn, 512, 256, 2048, 7168, None)[0] == "stream"   # DSV3 T=64
+    assert _pick_variant(torch.float8_e4m3fn, 131072, 256, 2048, 7168, None) == ("tcgen05", 128)

@@ -131,6 +131,32 @@ def test_options(fg, variant):
     assert_close_moe(out, ref, "bf16", "expert_map")
 
 
+@pytest.mark.parametrize("variant", ["stream", "tcgen05"])
+@pytest.mark.parametrize("fp8", [False, True])
+def test_one_call_entry_equals_kernel_by_kernel_path(fg, variant, fp8):
+    """fused_experts goes through the single C entry (fmoe_fused_experts); with stage events switched on it
+    launches the same kernels one by one.  Both must give bit-identical results."""
+    import importlib
+
+    FM = importlib.import_module("flaggems_sglang_b200.ops.fused_moe")
+    T, H, I, E, k = 70, 512, 256, 16, 4
+    x, w1, w2, logits = _layer(T, H, I, E, k, torch.bfloat16, 11)
+    tw, ti = OR.softmax_topk(logits, k, True)
+    kw = dict(variant=variant)
+    if fp8:
+        w1, s1 = OQ.quant_weight_block128(w1)
+        w2, s2 = OQ.quant_weight_block128(w2)
+        kw.update(use_fp8_w8a8=True, w1_scale=s1.cuda(), w2_scale=s2.cuda(), block_shape=[128, 128])
+    a = _run(fg, x, w1, w2, tw, ti, **kw)
+    FM.STAGE_EVENTS = []
+    try:
+        b = _run(fg, x, w1, w2, tw, ti, **kw)
+        assert len(FM.STAGE_EVENTS) == 2
+    finally:
+        FM.STAGE_EVENTS = None
+    assert torch.equal(a, b)
+
+
 def test_empty_batch(fg):
     x, w1, w2, logits = _layer(4, 128, 128, 4, 2, torch.bfloat16, 1)
     out = fg.fused_experts(x[:0].cuda(), w1.cuda(), w2.cuda(), torch.zeros(0, 2).cuda(),
@@ -195,7 +221,8 @@ def test_hook(fg):
 
 
 # ------------------------------------------------------------------ fp8 w8a8 block quant
-@pytest.mark.parametrize("T,variant", [(1, "stream"), (9, "stream"), (64, "stream"), (9, "simt"), (200, "stream")])
+@pytest.mark.parametrize("T,variant", [(1, "stream"), (9, "stream"), (64, "stream"), (9, "simt"), (200, "stream"),
+                                       (9, "tcgen05"), (200, "tcgen05"), (1000, "tcgen05")])
 def test_fp8_block_quant(fg, T, variant):
     H, I, E, k = 512, 256, 16, 4
     x, w1, w2, logits = _layer(T, H, I, E, k, torch.bfloat16, 300 + T)
@@ -255,6 +282,6 @@ def test_qwen3_full_size_sampled(fg, T):
     _sampled_dense_check(fg, "qwen3", T, 3, "bf16")
 
 
-@pytest.mark.parametrize("T", [1, 64])
+@pytest.mark.parametrize("T", [1, 64, 4096])
 def test_dsv3_fp8_full_size_sampled(fg, T):
     _sampled_dense_check(fg, "dsv3", T, 2, "fp8")

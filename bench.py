@@ -26,6 +26,8 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
+# decode-sized batches are replayed from a CUDA graph (launch-bound otherwise); larger ones run eagerly
+GRAPH_MAX_TOKENS = 256
 METRIC = "fused_moe tokens/s"
 UNIT = "tokens/s"
 
@@ -186,6 +188,21 @@ def make_step(cfg, wts, tok):
     return step
 
 
+def graphed(step, warmup=3):
+    """Capture one call into a CUDA graph (the layer call has no host sync) -> replay function."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(warmup):
+            step()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        step()
+    return g.replay
+
+
 def time_steps(step, steps, warmup):
     """Device time of `steps` calls (CUDA events on the current stream) -> ms per step."""
     for _ in range(warmup):
@@ -223,7 +240,8 @@ def measure_point(cfg, wts, T, steps, warmup, peaks, seed=0):
 
     tok = W.make_tokens(cfg, T, "cuda", seed=seed)
     step = make_step(cfg, wts, tok)
-    ms = time_steps(step, steps, warmup)
+    use_graph = T <= GRAPH_MAX_TOKENS
+    ms = time_steps(graphed(step) if use_graph else step, steps, warmup)
     st = stage_times(step, max(3, steps // 2))
     _, ids = W.route(cfg, tok)
     active = int(torch.unique(ids).numel())
@@ -233,7 +251,7 @@ def measure_point(cfg, wts, T, steps, warmup, peaks, seed=0):
     t_tc = flops / (p_tensor * 1e12)
     bound = "tensor" if t_tc > t_hbm else "hbm"
     t_roof = max(t_hbm, t_tc)
-    return {"T": T, "ms": ms, "tokens_per_s": T / (ms * 1e-3), "active_experts": active, "bound": bound,
+    return {"T": T, "ms": ms, "cuda_graph": use_graph, "tokens_per_s": T / (ms * 1e-3), "active_experts": active, "bound": bound,
             "roofline_ms": t_roof * 1e3, "roofline_frac": t_roof / (ms * 1e-3),
             "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "achieved_tflops": flops / (ms * 1e-3) / 1e12,
             "stages_ms": st, "alg_bytes": nbytes, "alg_flops": flops}
@@ -342,7 +360,7 @@ def main():
             pt = point if Ts == T else measure_point(cfg, wts, Ts, max(5, args.steps // 2), 3, peaks)
             dom = dominant_kernel_roofline(cfg, Ts, pt, peaks)
             sweep.append({"T": Ts, "ms": round(pt["ms"], 4), "tokens_per_s": round(pt["tokens_per_s"], 1),
-                          "bound": pt["bound"], "roofline_frac": round(pt["roofline_frac"], 4),
+                          "cuda_graph": pt["cuda_graph"], "bound": pt["bound"], "roofline_frac": round(pt["roofline_frac"], 4),
                           "gemm1_frac": None if dom is None else round(dom["frac"], 4),
                           "active_experts": pt["active_experts"],
                           "stages_ms": {k: round(v, 4) for k, v in pt["stages_ms"].items()}})

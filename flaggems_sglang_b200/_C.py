@@ -78,6 +78,8 @@ SIGNATURES = {
     "fmoe_pick_variant": (c_int, [c_int, c_int64, c_int, c_int64, c_int64, c_int, POINTER(c_int), POINTER(c_int)]),
     "fmoe_fused_experts_workspace_bytes": (c_int64, [POINTER(FusedArgs)]),
     "fmoe_fused_experts": (c_int, [POINTER(FusedArgs), c_void_p]),
+    "fmoe_static_scratch_bytes": (c_int64, []),
+    "fmoe_fused_experts_static": (c_int, [POINTER(FusedArgs), c_void_p]),
     "fmoe_check_device_status": (c_int, [c_void_p]),
 }
 

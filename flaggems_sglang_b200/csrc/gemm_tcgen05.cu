@@ -15,7 +15,7 @@
 // [rows, I] is written.  gemm2: 256 plain columns, multiplied by the row's top-k
 // weight and scattered to the row's flat slot.
 //
-// No TMA multicast, cluster size 1.  Every mbarrier wait is bounded; on expiry the
+// Cluster size 1, every CTA loads its own tiles.  Every mbarrier wait is bounded; on expiry the
 // kernel records a code in a device status word, leaves its loops, frees TMEM and returns.
 #include "gemm.cuh"
 #include "ptx_sm100.cuh"

@@ -11,7 +11,7 @@
 //               gemm2: columns [128h, 128h+128)
 //   warp 8    : TMA producer (A 128x128 B box, B two 128-row boxes), 4-stage ring
 //   warp 9    : MMA issuer
-// Same tile schedule, bounded waits and status word as the bf16 kernel; no multicast, cluster size 1.
+// Same tile schedule, bounded waits and status word as the bf16 kernel; cluster size 1, every CTA loads its own tiles.
 #include "gemm.cuh"
 #include "ptx_sm100.cuh"
 

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the large-M kernel uses:
-// mbarrier, TMA (cp.async.bulk.tensor, no multicast), tcgen05 MMA / TMEM.
+// mbarrier, TMA tile loads into the issuing CTA only, tcgen05 MMA / TMEM.
 // Every wait is bounded: it gives up after kWaitCycles and reports failure.
 #pragma once
 #include <cuda.h>

@@ -202,6 +202,31 @@ int64_t fmoe_fused_experts_workspace_bytes(const fmoe_fused_args* args);
 int fmoe_fused_experts(const fmoe_fused_args* args, void* stream);
 
 /*
+ * fmoe_fused_experts for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference, which allocates its intermediates with torch on every call.
+ *
+ * Who needs it: code that runs the layer where cudaMalloc (or any allocator built on it) is off limits —
+ * inside a stream capture, on a latency-critical thread that may not take the allocator's locks, or inside
+ * a host application that owns all device memory and offers no scratch.  Same arguments and results as
+ * fmoe_fused_experts, except that `workspace` / `workspace_bytes` are ignored: the intermediates go to an
+ * array of FMOE_STATIC_SCRATCH_BYTES that is part of the library image, so every GPU that loads the
+ * library gives up that much memory until the process exits.
+ *
+ *   - Problems whose workspace (fmoe_fused_experts_workspace_bytes) exceeds FMOE_STATIC_SCRATCH_BYTES are
+ *     refused with FMOE_ERR_UNSUPPORTED; nothing is launched.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *     device current) and remembers it.  Make that first call before any stream capture begins.
+ *   - No cudaMalloc, cudaFree or allocating library routine is called, on the first call or later.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call left in it.  The
+ *     kernels rewrite every index buffer they read and clear the per-slot outputs when `zero_dropped` is
+ *     set, so no stale value is ever consumed; but two calls that overlap on the GPU (different streams
+ *     without ordering between them) race on the array and give wrong results.  Serialise them.
+ */
+#define FMOE_STATIC_SCRATCH_BYTES (64ll << 20)
+int64_t fmoe_static_scratch_bytes(void);
+int fmoe_fused_experts_static(const fmoe_fused_args* args, void* stream);
+
+/*
  * Reads and clears the device-side status word that bounded waits inside the
  * tcgen05 kernels set when they give up.  Synchronises `stream`.
  * Returns FMOE_OK or FMOE_ERR_DEVICE_TIMEOUT.

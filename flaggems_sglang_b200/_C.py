@@ -68,6 +68,9 @@ SIGNATURES = {
                                   c_void_p, c_void_p, c_void_p]),
     "fmoe_moe_align_block_size": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_int64,
                                           c_void_p, c_void_p]),
+    "fmoe_moe_align_workspace_bytes": (c_int64, [c_int64, c_int]),
+    "fmoe_moe_align_block_size_ws": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_int64, c_void_p, c_int64,
+                                             c_void_p, c_void_p, c_int64, c_void_p]),
     "fmoe_quant_fp8_group128": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p,
                                         c_void_p, c_void_p, c_void_p]),
     "fmoe_gather_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p, c_void_p,

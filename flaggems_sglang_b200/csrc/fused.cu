@@ -71,6 +71,8 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
   p.off_sorted = take(p.cap * 4);
   p.off_expert = take(p.nblk * 4);
   p.off_npp = take(16);
+  p.align_ws_bytes = fmoe_moe_align_workspace_bytes(p.numel, a.num_experts);
+  p.off_align_ws = take(p.align_ws_bytes);
   p.off_xs = p.off_xs_scale = p.off_actq = p.off_actq_scale = -1;
   if (fp8) {
     const int64_t xrows = tc ? p.cap : a.T;
@@ -104,7 +106,8 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
   void* z = a.no_combine ? a.out : (void*)(ws + p.off_z);
   auto st = (cudaStream_t)stream;
 
-  int rc = fmoe_moe_align_block_size(a.topk_ids, p.numel, a.num_experts, p.block, sorted, p.cap, experts, p.nblk, npp, stream);
+  int rc = fmoe_moe_align_block_size_ws(a.topk_ids, p.numel, a.num_experts, p.block, sorted, p.cap, experts, p.nblk, npp,
+                                        ws + p.off_align_ws, p.align_ws_bytes, stream);
   if (rc) return rc;
   if (a.zero_dropped) FMOE_CUDA_OK(cudaMemsetAsync(z, 0, (size_t)(p.numel * a.H * eb), st));
 

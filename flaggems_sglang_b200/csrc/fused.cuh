@@ -8,7 +8,7 @@ struct FusedPlan {
   int variant, block, act_elem;
   int64_t numel, cap, nblk, max_blocks, total;
   // byte offsets into the workspace (-1: not used)
-  int64_t off_sorted, off_expert, off_npp, off_xs, off_xs_scale, off_act, off_actq, off_actq_scale, off_z;
+  int64_t off_sorted, off_expert, off_npp, off_align_ws, align_ws_bytes, off_xs, off_xs_scale, off_act, off_actq, off_actq_scale, off_z;
 };
 
 int pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forced, int* variant, int* block);

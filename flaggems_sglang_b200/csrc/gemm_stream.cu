@@ -8,10 +8,11 @@
 // 16 contiguous bytes at k-offset 16*t of its row and feeds them to two
 // consecutive MMAs; both operands use the same byte -> k assignment.
 //
-// One CTA = one token block (8*NTG rows of one expert) x one slab pair of W rows;
-// its 8 warps split K in chunks of 128 and are reduced through shared memory in
-// a fixed order (bit-reproducible).  gemm1 pairs 16 gate rows with the matching
-// 16 up rows so that silu(gate)*up is applied in the epilogue.
+// One work item = one token block (8*NTG rows of one expert) x one slab pair of W rows.
+// By default one warp owns an item over the whole K range; when a launch has too few
+// items to fill the GPU, 2/4/8 warps of a CTA share an item, split K in chunks of 128 and
+// are reduced through shared memory in a fixed order (bit-reproducible).  gemm1 pairs 16
+// gate rows with the matching 16 up rows so that silu(gate)*up is applied in registers.
 #include "gemm.cuh"
 
 namespace fmoe {
@@ -37,69 +38,32 @@ __device__ __forceinline__ void mma_e4m3_16832(float (&d)[4], uint32_t a0, uint3
 }
 
 // EB: bytes per element (2 = bf16, 1 = e4m3 with 128-block scales)
+// A work item is (token block b, slab pair s); W = 1, 2, 4 or 8 warps share an item and split its K
+// range (interleaved 128-k chunks).  W is chosen by the host so that the launch has enough warps to
+// keep HBM busy; with W == 1 a warp owns its item end to end and the CTA never synchronises.
 template <int EB, int NTG, bool GATED, typename OutT>
 __global__ void __launch_bounds__(kThreads)
-grouped_gemm_stream_kernel(GemmParams p) {
+grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
   constexpr int BM = 8 * NTG;
   constexpr int U = (EB == 2) ? 4 : 2;      // 64-byte steps per 128-k chunk
-  constexpr int KSTEP = 64 / EB;            // k elements per step
   constexpr int FRAG = RT * NTG * 4 * 32;   // accumulator words per warp
-  __shared__ float s_red[kWarps][FRAG];
-  __shared__ int64_t s_arow[BM];
-  __shared__ int32_t s_slot[BM];
+  extern __shared__ float s_red[];          // [kWarps][FRAG], only when W > 1
 
-  const int64_t b = blockIdx.x;
-  if (b * BM >= (int64_t)*p.num_tokens_post_padded) return;
-  const int e = p.expert_ids[b];
-  if (e < 0 || e >= p.num_experts) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-
-  if (tid < BM) {
-    const int64_t pos = b * BM + tid;
-    const int32_t slot = p.sorted_token_ids[pos];
-    const bool ok = slot >= 0 && slot < p.numel;
-    s_slot[tid] = ok ? slot : -1;
-    s_arow[tid] = ok ? (p.a_gather ? (int64_t)(slot / p.top_k) : pos) : -1;
-  }
-  __syncthreads();
+  const int items_per_cta = kWarps / W;
+  const int64_t item = (int64_t)blockIdx.x * items_per_cta + warp / W;
+  const int part = warp % W;
+  const int64_t b = item / n_slabs;
+  const int slab = (int)(item % n_slabs);
+  bool active = b < p.max_blocks && b * BM < (int64_t)*p.num_tokens_post_padded;
+  int e = active ? p.expert_ids[b] : -1;
+  active = active && e >= 0 && e < p.num_experts;
+  if (W == 1 && !active) return;  // no barrier is ever reached on this path
 
   const int64_t K = p.k;
   const int64_t w_rows = GATED ? 2 * p.n : p.n;
-  const int64_t n0 = (int64_t)blockIdx.y * (GATED ? 16 : 32);
-  // W row of this lane for slab rt, half h (fragment rows g and g+8); clamped so loads stay in bounds
-  const uint8_t* wptr[RT][2];
-  int64_t slab_row0[RT];
-#pragma unroll
-  for (int rt = 0; rt < RT; ++rt) {
-    slab_row0[rt] = GATED ? (rt == 0 ? n0 : p.n + n0) : n0 + 16 * rt;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      int64_t row = min(slab_row0[rt] + g + 8 * h, w_rows - 1);
-      wptr[rt][h] = reinterpret_cast<const uint8_t*>(p.w) + (((int64_t)e * w_rows + row) * K) * EB + t * 16;
-    }
-  }
-  const uint8_t* xptr[NTG];
-#pragma unroll
-  for (int q = 0; q < NTG; ++q) {
-    int64_t ar = s_arow[q * 8 + g];
-    xptr[q] = ar >= 0 ? reinterpret_cast<const uint8_t*>(p.a) + ar * K * EB + t * 16 : nullptr;
-  }
+  const int64_t n0 = (int64_t)slab * (GATED ? 16 : 32);
   const int64_t kblocks = K / 128;
-  // fp8 scales: activations of tokens 2t, 2t+1 of each group; weights of each slab
-  const float* sa_ptr[NTG][2];
-  const float* sw_ptr[RT];
-  if constexpr (EB == 1) {
-#pragma unroll
-    for (int q = 0; q < NTG; ++q)
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        int64_t ar = s_arow[q * 8 + 2 * t + j];
-        sa_ptr[q][j] = ar >= 0 ? p.a_scale + ar * kblocks : nullptr;
-      }
-#pragma unroll
-    for (int rt = 0; rt < RT; ++rt)
-      sw_ptr[rt] = p.w_scale + ((int64_t)e * (w_rows / 128) + min(slab_row0[rt], w_rows - 1) / 128) * kblocks;
-  }
 
   float acc[RT][NTG][4];
 #pragma unroll
@@ -109,109 +73,174 @@ grouped_gemm_stream_kernel(GemmParams p) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[rt][q][i] = 0.f;
 
-  for (int64_t chunk = warp; chunk < kblocks; chunk += kWarps) {
-    const int64_t boff = chunk * 128 * EB;  // byte offset of the chunk inside a row
-    uint4 wq[RT][U][2];
+  // flat slots of the tokens this lane touches: token g of each group feeds the B fragment,
+  // tokens 2t and 2t+1 are the accumulator columns (scales, epilogue)
+  int32_t slot_t[NTG][2];
 #pragma unroll
-    for (int rt = 0; rt < RT; ++rt)
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) wq[rt][u][h] = ldg_stream_v4(wptr[rt][h] + boff + u * 64);
+  for (int q = 0; q < NTG; ++q) slot_t[q][0] = slot_t[q][1] = -1;
 
-    float part[RT][NTG][4];
+  if (active) {
+    // W row of this lane for slab rt, half h (fragment rows g and g+8); clamped so loads stay in bounds
+    const uint8_t* wptr[RT][2];
+    int64_t slab_row0[RT];
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt) {
+      slab_row0[rt] = GATED ? (rt == 0 ? n0 : p.n + n0) : n0 + 16 * rt;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        int64_t row = min(slab_row0[rt] + g + 8 * h, w_rows - 1);
+        wptr[rt][h] = reinterpret_cast<const uint8_t*>(p.w) + (((int64_t)e * w_rows + row) * K) * EB + t * 16;
+      }
+    }
+    const uint8_t* xptr[NTG];
+    const float* sa_ptr[NTG][2];
+#pragma unroll
+    for (int q = 0; q < NTG; ++q) {
+      const int64_t pos_g = b * BM + q * 8 + g;
+      const int32_t sg = p.sorted_token_ids[pos_g];
+      const bool okg = sg >= 0 && sg < p.numel;
+      const int64_t ar = okg ? (p.a_gather ? (int64_t)(sg / p.top_k) : pos_g) : -1;
+      xptr[q] = ar >= 0 ? reinterpret_cast<const uint8_t*>(p.a) + ar * K * EB + t * 16 : nullptr;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int64_t pos_t = b * BM + q * 8 + 2 * t + j;
+        const int32_t st = p.sorted_token_ids[pos_t];
+        const bool okt = st >= 0 && st < p.numel;
+        slot_t[q][j] = okt ? st : -1;
+        if constexpr (EB == 1) {
+          const int64_t art = okt ? (p.a_gather ? (int64_t)(st / p.top_k) : pos_t) : -1;
+          sa_ptr[q][j] = art >= 0 ? p.a_scale + art * kblocks : nullptr;
+        }
+      }
+    }
+    const float* sw_ptr[RT];
     if constexpr (EB == 1) {
 #pragma unroll
       for (int rt = 0; rt < RT; ++rt)
-#pragma unroll
-        for (int q = 0; q < NTG; ++q)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) part[rt][q][i] = 0.f;
+        sw_ptr[rt] = p.w_scale + ((int64_t)e * (w_rows / 128) + min(slab_row0[rt], w_rows - 1) / 128) * kblocks;
     }
+
+    for (int64_t chunk = part; chunk < kblocks; chunk += W) {
+      const int64_t boff = chunk * 128 * EB;  // byte offset of the chunk inside a row
+      uint4 wq[RT][U][2];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
+      for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
-      for (int q = 0; q < NTG; ++q) {
-        uint4 xq = xptr[q] ? ldg_cached_v4(xptr[q] + boff + u * 64) : make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) wq[rt][u][h] = ldg_stream_v4(wptr[rt][h] + boff + u * 64);
+
+      float part_acc[RT][NTG][4];
+      if constexpr (EB == 1) {
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+          for (int q = 0; q < NTG; ++q)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) part_acc[rt][q][i] = 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int q = 0; q < NTG; ++q) {
+          uint4 xq = xptr[q] ? ldg_cached_v4(xptr[q] + boff + u * 64) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+          for (int rt = 0; rt < RT; ++rt) {
+            if constexpr (EB == 2) {
+              mma_bf16_16816(acc[rt][q], wq[rt][u][0].x, wq[rt][u][1].x, wq[rt][u][0].y, wq[rt][u][1].y, xq.x, xq.y);
+              mma_bf16_16816(acc[rt][q], wq[rt][u][0].z, wq[rt][u][1].z, wq[rt][u][0].w, wq[rt][u][1].w, xq.z, xq.w);
+            } else {
+              mma_e4m3_16832(part_acc[rt][q], wq[rt][u][0].x, wq[rt][u][1].x, wq[rt][u][0].y, wq[rt][u][1].y, xq.x, xq.y);
+              mma_e4m3_16832(part_acc[rt][q], wq[rt][u][0].z, wq[rt][u][1].z, wq[rt][u][0].w, wq[rt][u][1].w, xq.z, xq.w);
+            }
+          }
+        }
+      }
+      if constexpr (EB == 1) {
+        // acc += partial * (activation scale of the token) * (weight scale of the slab) for this 128-k block
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt) {
-          if constexpr (EB == 2) {
-            mma_bf16_16816(acc[rt][q], wq[rt][u][0].x, wq[rt][u][1].x, wq[rt][u][0].y, wq[rt][u][1].y, xq.x, xq.y);
-            mma_bf16_16816(acc[rt][q], wq[rt][u][0].z, wq[rt][u][1].z, wq[rt][u][0].w, wq[rt][u][1].w, xq.z, xq.w);
-          } else {
-            mma_e4m3_16832(part[rt][q], wq[rt][u][0].x, wq[rt][u][1].x, wq[rt][u][0].y, wq[rt][u][1].y, xq.x, xq.y);
-            mma_e4m3_16832(part[rt][q], wq[rt][u][0].z, wq[rt][u][1].z, wq[rt][u][0].w, wq[rt][u][1].w, xq.z, xq.w);
+          const float sw = sw_ptr[rt][chunk];
+#pragma unroll
+          for (int q = 0; q < NTG; ++q) {
+            const float s0 = sa_ptr[q][0] ? sa_ptr[q][0][chunk] * sw : 0.f;
+            const float s1 = sa_ptr[q][1] ? sa_ptr[q][1][chunk] * sw : 0.f;
+            acc[rt][q][0] = fmaf(part_acc[rt][q][0], s0, acc[rt][q][0]);
+            acc[rt][q][1] = fmaf(part_acc[rt][q][1], s1, acc[rt][q][1]);
+            acc[rt][q][2] = fmaf(part_acc[rt][q][2], s0, acc[rt][q][2]);
+            acc[rt][q][3] = fmaf(part_acc[rt][q][3], s1, acc[rt][q][3]);
           }
         }
       }
     }
-    if constexpr (EB == 1) {
-      // acc += partial * (activation scale of the token) * (weight scale of the slab) for this 128-k block
+  }
+
+  if (W > 1) {
+    // fixed-order reduction over the W warps of the item (bit-reproducible)
 #pragma unroll
-      for (int rt = 0; rt < RT; ++rt) {
-        const float sw = sw_ptr[rt][chunk];
+    for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
-        for (int q = 0; q < NTG; ++q) {
-          const float s0 = sa_ptr[q][0] ? sa_ptr[q][0][chunk] * sw : 0.f;
-          const float s1 = sa_ptr[q][1] ? sa_ptr[q][1][chunk] * sw : 0.f;
-          acc[rt][q][0] = fmaf(part[rt][q][0], s0, acc[rt][q][0]);
-          acc[rt][q][1] = fmaf(part[rt][q][1], s1, acc[rt][q][1]);
-          acc[rt][q][2] = fmaf(part[rt][q][2], s0, acc[rt][q][2]);
-          acc[rt][q][3] = fmaf(part[rt][q][3], s1, acc[rt][q][3]);
+      for (int q = 0; q < NTG; ++q)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s_red[warp * FRAG + ((rt * NTG + q) * 4 + i) * 32 + lane] = acc[rt][q][i];
+    __syncthreads();
+    if (part != 0 || !active) return;
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+      for (int q = 0; q < NTG; ++q)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float s = 0.f;
+          for (int w = 0; w < W; ++w) s += s_red[(warp + w) * FRAG + ((rt * NTG + q) * 4 + i) * 32 + lane];
+          acc[rt][q][i] = s;
         }
+  }
+
+  // epilogue from registers.  Accumulator word i of lane (g,t): W row g + 8*(i>>1) of the slab, token 2t + (i&1).
+  OutT* out = reinterpret_cast<OutT*>(p.out);
+#pragma unroll
+  for (int q = 0; q < NTG; ++q)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int32_t slot = slot_t[q][i & 1];
+      if (slot < 0) continue;
+      const float rs = p.row_scale ? p.row_scale[slot] : 1.0f;
+      const int col = g + 8 * (i >> 1);
+      if constexpr (GATED) {
+        if (n0 + col < p.n)
+          out[(b * BM + q * 8 + 2 * t + (i & 1)) * p.n + n0 + col] =
+              from_f32<OutT>(silu_mul(acc[0][q][i] * rs, acc[1][q][i] * rs));
+      } else {
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt)
+          if (n0 + rt * 16 + col < p.n)
+            out[(int64_t)slot * p.n + n0 + rt * 16 + col] = from_f32<OutT>(acc[rt][q][i] * rs);
       }
     }
-  }
+}
 
-  // cross-warp reduction in a fixed order
-#pragma unroll
-  for (int rt = 0; rt < RT; ++rt)
-#pragma unroll
-    for (int q = 0; q < NTG; ++q)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) s_red[warp][((rt * NTG + q) * 4 + i) * 32 + lane] = acc[rt][q][i];
-  __syncthreads();
-  for (int idx = tid; idx < FRAG; idx += kThreads) {
-    float s = 0.f;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) s += s_red[w][idx];
-    s_red[0][idx] = s;  // each idx is read and written by the same thread only
-  }
-  __syncthreads();
-
-  // epilogue.  Fragment word (rt, q, i, lane): W row g + 8*(i>>1) of slab rt, token q*8 + 2t + (i&1).
-  OutT* out = reinterpret_cast<OutT*>(p.out);
-  constexpr int PER_SLAB = NTG * 4 * 32;
-  if constexpr (GATED) {
-    for (int idx = tid; idx < PER_SLAB; idx += kThreads) {
-      const int ln = idx & 31, i = (idx >> 5) & 3, q = idx >> 7;
-      const int col = (ln >> 2) + 8 * (i >> 1), tok = q * 8 + 2 * (ln & 3) + (i & 1);
-      const int32_t slot = s_slot[tok];
-      if (slot < 0 || n0 + col >= p.n) continue;
-      const float rs = p.row_scale ? p.row_scale[slot] : 1.0f;
-      const float gate = s_red[0][idx] * rs, up = s_red[0][PER_SLAB + idx] * rs;
-      out[(b * BM + tok) * p.n + n0 + col] = from_f32<OutT>(silu_mul(gate, up));
-    }
-  } else {
-    for (int idx = tid; idx < RT * PER_SLAB; idx += kThreads) {
-      const int rt = idx / PER_SLAB, r = idx % PER_SLAB;
-      const int ln = r & 31, i = (r >> 5) & 3, q = r >> 7;
-      const int col = rt * 16 + (ln >> 2) + 8 * (i >> 1), tok = q * 8 + 2 * (ln & 3) + (i & 1);
-      const int32_t slot = s_slot[tok];
-      if (slot < 0 || n0 + col >= p.n) continue;
-      const float rs = p.row_scale ? p.row_scale[slot] : 1.0f;
-      out[(int64_t)slot * p.n + n0 + col] = from_f32<OutT>(s_red[0][idx] * rs);
-    }
-  }
+// Warps per item: enough warps in flight to cover HBM latency, but at least two 128-k chunks per warp.
+int pick_ksplit(int64_t items, int64_t kblocks) {
+  const int64_t target = 148 * 16;
+  int W = 1;
+  while (W < kWarps && items * W < target && kblocks / (2 * W) >= 2) W *= 2;
+  return W;
 }
 
 template <int EB, int NTG, bool GATED>
 int launch(const GemmParams& p, cudaStream_t st) {
-  dim3 grid((unsigned)p.max_blocks, (unsigned)ceil_div<int64_t>(p.n, GATED ? 16 : 32));
+  const int n_slabs = (int)ceil_div<int64_t>(p.n, GATED ? 16 : 32);
+  const int64_t items = p.max_blocks * n_slabs;
+  const int W = pick_ksplit(items, p.k / 128);
+  const int64_t ctas = ceil_div<int64_t>(items, kWarps / W);
+  if (ctas >= (1ll << 31)) return fail(FMOE_ERR_UNSUPPORTED, "stream gemm: too many work items");
+  const size_t smem = W > 1 ? sizeof(float) * kWarps * RT * NTG * 4 * 32 : 0;
+  dim3 grid((unsigned)ctas);
   if (p.out_dtype == FMOE_F32)
-    grouped_gemm_stream_kernel<EB, NTG, GATED, float><<<grid, kThreads, 0, st>>>(p);
+    grouped_gemm_stream_kernel<EB, NTG, GATED, float><<<grid, kThreads, smem, st>>>(p, W, n_slabs);
   else
-    grouped_gemm_stream_kernel<EB, NTG, GATED, __nv_bfloat16><<<grid, kThreads, 0, st>>>(p);
+    grouped_gemm_stream_kernel<EB, NTG, GATED, __nv_bfloat16><<<grid, kThreads, smem, st>>>(p, W, n_slabs);
   return launch_status("grouped_gemm_stream_kernel");
 }
 
@@ -234,7 +263,6 @@ bool gemm_stream_supports(const GemmParams& p, bool gated) {
   if (p.k <= 0 || p.k % 128 != 0) return false;
   if (p.n <= 0 || p.n % 16 != 0) return false;
   if (gated && p.dtype == FMOE_E4M3 && p.n % 128 != 0) return false;  // up rows must start on a scale block
-  if (ceil_div<int64_t>(p.n, gated ? 16 : 32) > 65535) return false;
   if (!aligned16(p.a) || !aligned16(p.w)) return false;
   return true;
 }

@@ -6,11 +6,11 @@
 //     acc[row, col] += partial[row, col] * a_scale[row, kb] * w_scale[col/128, kb]
 // Two TMEM partials (2 x 256 columns) ping-pong, so the MMAs of block kb+1 run while block kb is folded.
 //
-//   warps 0-7 : fold + epilogue.  Warp w owns TMEM lanes 32*(w%4).. (rows) and half h = w/4 of the columns:
-//               gemm1: gate columns [64h,64h+64) and the matching up columns [128+64h, ...), 128 accumulators;
-//               gemm2: columns [128h, 128h+128)
-//   warp 8    : TMA producer (A 128x128 B box, B two 128-row boxes), 4-stage ring
-//   warp 9    : MMA issuer
+//   warps 0-15: fold + epilogue.  Warp w owns TMEM lanes 32*(w%4).. (rows) and quarter c = w/4 of the columns:
+//               gemm1: gate columns [32c,32c+32) and the matching up columns [128+32c, ...), 64 accumulators;
+//               gemm2: columns [64c, 64c+64).  Four warps per scheduler hide the TMEM load latency.
+//   warp 16   : TMA producer (A 128x128 B box, B two 128-row boxes), 4-stage ring
+//   warp 17   : MMA issuer
 // Same tile schedule, bounded waits and status word as the bf16 kernel; cluster size 1, every CTA loads its own tiles.
 #include "gemm.cuh"
 #include "ptx_sm100.cuh"
@@ -31,8 +31,8 @@ constexpr int A_BYTES = BM * KBYTES;
 constexpr int B_BYTES = BN * KBYTES;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;
-constexpr int kEpiWarps = 8;
-constexpr int kThreads = (kEpiWarps + 2) * 32;
+constexpr int kEpiWarps = 16;
+constexpr int kThreads = (kEpiWarps + 4) * 32;  // warps 18, 19 only exist to complete the fifth warpgroup
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 
 struct Fp8Params {
@@ -190,9 +190,9 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
         }
       }
     }
-  } else {
-    // ---------------- fold + epilogue (warps 0-7) ----------------
-    const int quarter = warp & 3, half = warp >> 2;
+  } else if (warp < kEpiWarps) {
+    // ---------------- fold + epilogue (warps 0-15) ----------------
+    const int quarter = warp & 3, cpart = warp >> 2;  // TMEM lane quarter, column quarter
     const int row = quarter * 32 + lane;
     const int64_t sblocks_per_expert = p.w_rows / 128;
     uint32_t step = 0;
@@ -207,22 +207,23 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
       const bool valid = slot >= 0 && slot < p.numel;
       const float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
       const float* sa_row = p.a_scale + (in_cap ? pos : 0) * kblocks;
-      // weight-scale rows of the two 128-column halves of the accumulator
-      const int64_t sw_blk0 = GATED ? n_tile : 2 * (int64_t)n_tile;
-      const int64_t sw_blk1 = GATED ? (p.n / 128 + n_tile) : min(2 * (int64_t)n_tile + 1, sblocks_per_expert - 1);
+      // weight-scale rows of this warp's two 32-column pieces (gemm1: gate / up; gemm2: both in one 128-block)
+      const int64_t sw_blk0 = GATED ? n_tile : min(2 * (int64_t)n_tile + (cpart >> 1), sblocks_per_expert - 1);
+      const int64_t sw_blk1 = GATED ? (p.n / 128 + n_tile) : sw_blk0;
       const float* sw0 = p.w_scale + ((int64_t)e * sblocks_per_expert + sw_blk0) * kblocks;
       const float* sw1 = p.w_scale + ((int64_t)e * sblocks_per_expert + sw_blk1) * kblocks;
+      const int col0 = GATED ? 32 * cpart : 64 * cpart;
+      const int col1 = GATED ? 128 + 32 * cpart : 64 * cpart + 32;
 
-      float acc[128];
+      float acc[64];
 #pragma unroll
-      for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+      for (int i = 0; i < 64; ++i) acc[i] = 0.f;
 
       float sa_n = in_cap ? sa_row[0] : 0.f, s0_n = sw0[0], s1_n = sw1[0];
       for (int kb = 0; kb < kblocks; ++kb, ++step) {
         const int buf = step & 1;
         const uint32_t buf_phase = (step >> 1) & 1;
-        const float sa = sa_n;
-        const float f0 = sa * s0_n, f1 = sa * s1_n;
+        const float f0 = sa_n * s0_n, f1 = sa_n * s1_n;
         if (kb + 1 < kblocks) {  // prefetch the next block's scales while waiting for the MMAs
           sa_n = in_cap ? sa_row[kb + 1] : 0.f;
           s0_n = sw0[kb + 1];
@@ -237,15 +238,13 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
         const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          // gemm1: c = 0,1 gate columns 64h + 32c; c = 2,3 up columns 128 + 64h + 32(c-2)
-          // gemm2: columns 128h + 32c
-          const int col = GATED ? ((c < 2) ? (64 * half + 32 * c) : (128 + 64 * half + 32 * (c - 2))) : (128 * half + 32 * c);
-          const float f = GATED ? ((c < 2) ? f0 : f1) : (half == 0 ? f0 : f1);
-          uint32_t v[32];
-          ptx::tmem_ld_32x32b_x32(taddr + col, v);
+          // 16 columns at a time keeps the staging registers small (64 accumulators stay live)
+          uint32_t v[16];
+          ptx::tmem_ld_32x32b_x16(taddr + ((c < 2) ? col0 + 16 * c : col1 + 16 * (c - 2)), v);
           ptx::tmem_ld_wait();
+          const float f = (c < 2) ? f0 : f1;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(__uint_as_float(v[i]), f, acc[c * 32 + i]);
+          for (int i = 0; i < 16; ++i) acc[16 * c + i] = fmaf(__uint_as_float(v[i]), f, acc[16 * c + i]);
         }
         ptx::tc_fence_before_sync();
         ptx::mbar_arrive(&part_empty[buf]);
@@ -253,28 +252,28 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
       if (!alive) break;
 
       if constexpr (GATED) {
-        // acc[0..63] gate, acc[64..127] up, output columns n_tile*128 + 64h + [0,64)
+        // acc[0..31] gate, acc[32..63] up -> output columns n_tile*128 + 32*cpart + [0,32)
         if (in_cap) {
-          __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + pos * p.n + (int64_t)n_tile * 128 + 64 * half;
+          __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + pos * p.n + (int64_t)n_tile * 128 + 32 * cpart;
           uint4* dst = reinterpret_cast<uint4*>(orow);
 #pragma unroll
-          for (int v = 0; v < 8; ++v) {
+          for (int v = 0; v < 4; ++v) {
             uint32_t w[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int i = v * 8 + j * 2;
-              w[j] = pack_bf16x2(silu_mul(acc[i] * rs, acc[64 + i] * rs), silu_mul(acc[i + 1] * rs, acc[64 + i + 1] * rs));
+              w[j] = pack_bf16x2(silu_mul(acc[i] * rs, acc[32 + i] * rs), silu_mul(acc[i + 1] * rs, acc[32 + i + 1] * rs));
             }
             dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       } else {
-        const int64_t col0 = (int64_t)n_tile * 256 + 128 * half;
-        if (valid && col0 < p.n) {
-          __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)slot * p.n + col0;
+        const int64_t colg = (int64_t)n_tile * 256 + 64 * cpart;
+        if (valid && colg < p.n) {
+          __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)slot * p.n + colg;
           uint4* dst = reinterpret_cast<uint4*>(orow);
 #pragma unroll
-          for (int v = 0; v < 16; ++v) {
+          for (int v = 0; v < 8; ++v) {
             uint32_t w[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {

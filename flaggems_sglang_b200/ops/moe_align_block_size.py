@@ -32,9 +32,12 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
     sorted_ids = torch.empty(cap, dtype=torch.int32, device=dev)
     expert_ids = torch.empty(nblk, dtype=torch.int32, device=dev)
     num_post = torch.empty(1, dtype=torch.int32, device=dev)
-    _C.check(_C.lib().fmoe_moe_align_block_size(ids.data_ptr(), numel, num_experts, block_size,
-                                                sorted_ids.data_ptr(), cap, expert_ids.data_ptr(), nblk,
-                                                num_post.data_ptr(), _C.stream_ptr(dev)))
+    lib = _C.lib()
+    ws_bytes = lib.fmoe_moe_align_workspace_bytes(numel, num_experts) if numel >= 8192 else 0
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev) if ws_bytes else None
+    _C.check(lib.fmoe_moe_align_block_size_ws(ids.data_ptr(), numel, num_experts, block_size, sorted_ids.data_ptr(),
+                                              cap, expert_ids.data_ptr(), nblk, num_post.data_ptr(), _C.ptr(ws),
+                                              ws_bytes, _C.stream_ptr(dev)))
     return sorted_ids, expert_ids, num_post
 
 

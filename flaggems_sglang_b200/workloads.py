@@ -39,6 +39,9 @@ CONFIGS = {
     # DeepSeek-V3 style, fp8 w8a8 with 128x128 block scales, grouped router
     "dsv3": MoEConfig("dsv3", H=7168, I=2048, E=256, top_k=8, dtype="fp8", router="grouped", n_group=8,
                       topk_group=4, routed_scaling_factor=2.5, sweep_T=(1, 64, 1024, 16384)),
+    # 32-expert cut of the DeepSeek-V3 layer (1.4 GB of weights): same tile shapes, small enough to profile
+    "dsv3_small": MoEConfig("dsv3_small", H=7168, I=2048, E=32, top_k=8, dtype="fp8", router="grouped", n_group=8,
+                            topk_group=4, routed_scaling_factor=2.5, sweep_T=(64, 2048)),
     # shapes of the reference's own test/benchmark list (M,1280,3072,64,8)
     "refbench": MoEConfig("refbench", H=1280, I=3072, E=64, top_k=8, dtype="bf16", sweep_T=(1, 4, 17, 64, 1024, 2048, 4096)),
 }

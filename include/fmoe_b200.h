@@ -91,6 +91,18 @@ int fmoe_moe_align_block_size(const int32_t* topk_ids, int64_t numel, int E, int
                               int32_t* num_tokens_post_padded, void* stream);
 
 /*
+ * Same result with caller scratch: inputs of 8192 slots or more are processed by one CTA per 4096 slots
+ * (three launches) instead of a single CTA.  workspace needs fmoe_moe_align_workspace_bytes(numel, E) bytes;
+ * with workspace == NULL or a small input this is fmoe_moe_align_block_size.
+ */
+int64_t fmoe_moe_align_workspace_bytes(int64_t numel, int E);
+int fmoe_moe_align_block_size_ws(const int32_t* topk_ids, int64_t numel, int E, int block,
+                                 int32_t* sorted_token_ids, int64_t sorted_cap,
+                                 int32_t* expert_ids, int64_t expert_cap,
+                                 int32_t* num_tokens_post_padded, void* workspace, int64_t workspace_bytes,
+                                 void* stream);
+
+/*
  * Per-row, per-128-channel dynamic quantisation to e4m3 (the fp8 path the
  * reference rejects at src/flaggems_sglang/ops/fused_moe.py:170-185).
  *   x [rows_in, K] (in_dtype FMOE_BF16 or FMOE_F32), K % 128 == 0

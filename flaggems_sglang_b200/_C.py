@@ -17,7 +17,8 @@ LIB_PATH = os.path.join(_HERE, "libfmoe_b200.so")
 OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_TIMEOUT = 0, 1, 2, 3, 4
 F32, BF16, E4M3 = 0, 1, 2
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_STREAM, VARIANT_TCGEN05 = 0, 1, 2, 3
-VARIANTS = {"auto": 0, "simt": 1, "stream": 2, "tcgen05": 3}
+VARIANTS = {"auto": 0, "simt": 1, "stream": 2, "tcgen05": 3, "tcgen05_pair": 4}
+ACTIVATIONS = {"silu": 0, "gelu": 1}
 VARIANT_NAMES = {v: k for k, v in VARIANTS.items()}
 
 DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float8_e4m3fn: E4M3}
@@ -34,7 +35,7 @@ class GemmArgs(Structure):
 
     _fields_ = [
         ("dtype", c_int32), ("out_dtype", c_int32), ("variant", c_int32), ("num_experts", c_int32),
-        ("top_k", c_int32), ("block_size", c_int32), ("a_gather", c_int32), ("reserved", c_int32),
+        ("top_k", c_int32), ("block_size", c_int32), ("a_gather", c_int32), ("activation", c_int32),
         ("numel", c_int64), ("n", c_int64), ("k", c_int64), ("a_rows", c_int64),
         ("sorted_cap", c_int64), ("max_blocks", c_int64),
         ("a", c_void_p), ("a_scale", c_void_p), ("w", c_void_p), ("w_scale", c_void_p),
@@ -49,7 +50,7 @@ class FusedArgs(Structure):
     _fields_ = [
         ("dtype", c_int32), ("variant", c_int32), ("num_experts", c_int32), ("top_k", c_int32),
         ("apply_router_weight_on_input", c_int32), ("no_combine", c_int32), ("zero_dropped", c_int32),
-        ("reserved", c_int32),
+        ("activation", c_int32),
         ("T", c_int64), ("H", c_int64), ("I", c_int64),
         ("routed_scaling_factor", c_float), ("reserved_f", c_float),
         ("hidden", c_void_p), ("w1", c_void_p), ("w2", c_void_p), ("w1_scale", c_void_p), ("w2_scale", c_void_p),

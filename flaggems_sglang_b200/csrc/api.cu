@@ -14,6 +14,7 @@ namespace {
 int validate_gemm(const GemmParams& a, bool gated, const char* who) {
   FMOE_REQUIRE(a.dtype == FMOE_F32 || a.dtype == FMOE_BF16 || a.dtype == FMOE_E4M3, "%s: unknown dtype %d", who, a.dtype);
   FMOE_REQUIRE(a.num_experts >= 1 && a.top_k >= 1 && a.block_size >= 1, "%s: bad E/top_k/block_size", who);
+  FMOE_REQUIRE(a.activation == FMOE_ACT_SILU || a.activation == FMOE_ACT_GELU, "%s: unknown activation %d", who, a.activation);
   FMOE_REQUIRE(a.numel >= 0 && a.n >= 1 && a.k >= 1, "%s: bad sizes numel=%lld n=%lld k=%lld", who,
                (long long)a.numel, (long long)a.n, (long long)a.k);
   FMOE_REQUIRE(a.max_blocks >= 0 && a.max_blocks * a.block_size <= a.sorted_cap,
@@ -57,6 +58,7 @@ int dispatch_gemm(const fmoe_gemm_args* args, bool gated, void* stream, const ch
     case FMOE_VARIANT_STREAM: return gemm_stream(a, gated, st);
     case FMOE_VARIANT_TCGEN05:
       return a.dtype == FMOE_E4M3 ? gemm_tcgen05_fp8(a, gated, st) : gemm_tcgen05(a, gated, st);
+    case FMOE_VARIANT_TCGEN05_PAIR: return gemm_tcgen05_pair(a, gated, st);
   }
   return fail(FMOE_ERR_INVALID_ARG, "%s: unknown variant %d", who, a.variant);
 }

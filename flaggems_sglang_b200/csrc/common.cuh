@@ -72,6 +72,13 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fdiv_rn(g, 1.0f + expf(-g)) * u;
 }
 
+// Gated activation of gemm1's epilogue: act(g) * u.  0 = silu (default), 1 = gelu (erf form), as the
+// reference's two activations (src/flaggems_sglang/ops/fused_moe.py:217-220).
+__device__ __forceinline__ float act_mul(float g, float u, int activation) {
+  if (activation == FMOE_ACT_GELU) return 0.5f * g * (1.0f + erff(g * 0.70710678118654752f)) * u;
+  return silu_mul(g, u);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

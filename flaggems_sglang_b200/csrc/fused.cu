@@ -28,6 +28,10 @@ int pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forc
       if (!tc_ok) return fail(FMOE_ERR_UNSUPPORTED, "tcgen05 kernels need I %% 128 == 0 and H %% 32 == 0 (128 for e4m3)");
       *block = 128;
       break;
+    case FMOE_VARIANT_TCGEN05_PAIR:
+      if (!tc_ok || dtype != FMOE_BF16) return fail(FMOE_ERR_UNSUPPORTED, "the CTA-pair kernel needs bf16, I %% 128 == 0 and H %% 32 == 0");
+      *block = 256;
+      break;
     case FMOE_VARIANT_STREAM:
       if (!stream_ok) return fail(FMOE_ERR_UNSUPPORTED, "stream kernels need H %% 128 == 0 and I %% 128 == 0");
       *block = rows <= 6.0 ? 8 : (rows <= 12.0 ? 16 : 32);
@@ -51,6 +55,7 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
   FMOE_REQUIRE(a.T >= 0 && a.H >= 1 && a.I >= 1, "fused_experts: bad sizes T=%lld H=%lld I=%lld", (long long)a.T,
                (long long)a.H, (long long)a.I);
   FMOE_REQUIRE(a.dtype == FMOE_F32 || a.dtype == FMOE_BF16 || a.dtype == FMOE_E4M3, "fused_experts: unknown dtype %d", a.dtype);
+  FMOE_REQUIRE(a.activation == FMOE_ACT_SILU || a.activation == FMOE_ACT_GELU, "fused_experts: unknown activation %d", a.activation);
   if (a.dtype == FMOE_E4M3)
     FMOE_REQUIRE(a.H % 128 == 0 && a.I % 128 == 0, "fused_experts: e4m3 needs H and I to be multiples of 128");
   FusedPlan& p = *pl;
@@ -61,7 +66,8 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
   p.nblk = ceil_div<int64_t>(p.cap, p.block);
   p.max_blocks = std::min<int64_t>(p.cap / p.block, p.numel);
   const int64_t eb = a.dtype == FMOE_F32 ? 4 : 2;  // element size of hidden / out / z
-  const bool fp8 = a.dtype == FMOE_E4M3, tc = p.variant == FMOE_VARIANT_TCGEN05;
+  const bool fp8 = a.dtype == FMOE_E4M3;
+  const bool tc = p.variant == FMOE_VARIANT_TCGEN05 || p.variant == FMOE_VARIANT_TCGEN05_PAIR;
   int64_t off = 0;
   auto take = [&](int64_t bytes) {
     int64_t o = off;
@@ -95,7 +101,8 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
 int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* stream) {
   if (a.T == 0) return FMOE_OK;
   FMOE_REQUIRE(a.hidden && a.w1 && a.w2 && a.topk_weights && a.topk_ids && a.out, "fused_experts: null pointer");
-  const bool fp8 = a.dtype == FMOE_E4M3, tc = p.variant == FMOE_VARIANT_TCGEN05;
+  const bool fp8 = a.dtype == FMOE_E4M3;
+  const bool tc = p.variant == FMOE_VARIANT_TCGEN05 || p.variant == FMOE_VARIANT_TCGEN05_PAIR;
   if (fp8) FMOE_REQUIRE(a.w1_scale && a.w2_scale, "fused_experts: e4m3 needs w1_scale and w2_scale");
   const int io = fp8 ? FMOE_BF16 : a.dtype;  // dtype of hidden / z / out
   const int64_t eb = io == FMOE_F32 ? 4 : 2;
@@ -125,6 +132,7 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
 
   fmoe_gemm_args g1 = g, g2 = g;
   g1.n = a.I;
+  g1.activation = a.activation;
   g1.k = a.H;
   g1.w = a.w1;
   g1.out = act;

@@ -14,11 +14,33 @@ int gemm_simt(const GemmParams& p, bool gated, cudaStream_t st);
 int gemm_stream(const GemmParams& p, bool gated, cudaStream_t st);
 int gemm_tcgen05(const GemmParams& p, bool gated, cudaStream_t st);
 int gemm_tcgen05_fp8(const GemmParams& p, bool gated, cudaStream_t st);
+int gemm_tcgen05_pair(const GemmParams& p, bool gated, cudaStream_t st);
 
 // true when the variant can run these arguments (shape / alignment / dtype rules)
 bool gemm_stream_supports(const GemmParams& p, bool gated);
 bool gemm_tcgen05_supports(const GemmParams& p, bool gated);
 bool gemm_tcgen05_fp8_supports(const GemmParams& p, bool gated);
+bool gemm_tcgen05_pair_supports(const GemmParams& p, bool gated);
+
+// Tile order of the persistent kernels.  Tiles are walked in groups of `group_m` consecutive row blocks:
+// inside a group the row block varies fastest, then the column tile, so that CTAs running at the same
+// time share a weight tile through L2 while the group's activation rows (sized to fit L2) are re-read
+// from L2, not HBM, for every column tile.
+__device__ __forceinline__ void tile_to_mn(int64_t tile, int used_blocks, int n_tiles, int group_m, int* m_blk,
+                                           int* n_tile) {
+  const int64_t per_group = (int64_t)group_m * n_tiles;
+  const int g = (int)(tile / per_group);
+  const int r = (int)(tile % per_group);
+  const int rows = min(group_m, used_blocks - g * group_m);
+  *n_tile = r / rows;
+  *m_blk = g * group_m + r % rows;
+}
+// rows blocks per group so that the group's A operand takes about 48 MB
+inline int pick_group_m(int64_t block_rows, int64_t k_bytes_per_row) {
+  const int64_t per_block = block_rows * k_bytes_per_row;
+  int64_t g = (48ll << 20) / (per_block > 0 ? per_block : 1);
+  return (int)(g < 1 ? 1 : (g > (1 << 20) ? (1 << 20) : g));
+}
 
 // device status word written by bounded waits (gemm_tcgen05.cu)
 int read_and_clear_device_status(cudaStream_t st, int* status_out);

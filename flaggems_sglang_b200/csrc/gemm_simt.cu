@@ -63,7 +63,7 @@ grouped_gemm_simt_kernel(GemmParams p) {
     }
     const float rs = p.row_scale ? p.row_scale[slot] : 1.0f;
     if constexpr (GATED) {
-      reinterpret_cast<OutT*>(p.out)[pos * p.n + c] = from_f32<OutT>(silu_mul(acc_g * rs, acc_u * rs));
+      reinterpret_cast<OutT*>(p.out)[pos * p.n + c] = from_f32<OutT>(act_mul(acc_g * rs, acc_u * rs, p.activation));
     } else {
       reinterpret_cast<OutT*>(p.out)[(int64_t)slot * p.n + c] = from_f32<OutT>(acc_g * rs);
     }

@@ -210,7 +210,7 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
       if constexpr (GATED) {
         if (n0 + col < p.n)
           out[(b * BM + q * 8 + 2 * t + (i & 1)) * p.n + n0 + col] =
-              from_f32<OutT>(silu_mul(acc[0][q][i] * rs, acc[1][q][i] * rs));
+              from_f32<OutT>(act_mul(acc[0][q][i] * rs, acc[1][q][i] * rs, p.activation));
       } else {
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt)

@@ -53,6 +53,8 @@ struct TcParams {
   int32_t k_steps;     // ceil(K*elem / 128)
   int32_t n_tiles;
   int32_t max_blocks;
+  int32_t activation;
+  int32_t group_m;
 };
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_device_status, 0, code); }
@@ -112,7 +114,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     uint32_t phase = 0;
     bool alive = true;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-      const int m_blk = (int)(tile % used_blocks), n_tile = (int)(tile / used_blocks);
+      int m_blk, n_tile;
+      tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile);
       const int e = p.expert_ids[m_blk];
       if (e < 0 || e >= p.num_experts) continue;
       const int32_t row_a = m_blk * BM;
@@ -163,7 +166,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     int local = 0;
     bool alive = true;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-      const int m_blk = (int)(tile % used_blocks);
+      int m_blk, n_tile_unused;
+        tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile_unused);
       const int e = p.expert_ids[m_blk];
       if (e < 0 || e >= p.num_experts) continue;
       const int acc = local & 1;
@@ -209,7 +213,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     bool alive = true;
     const int row = warp * 32 + lane;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-      const int m_blk = (int)(tile % used_blocks), n_tile = (int)(tile / used_blocks);
+      int m_blk, n_tile;
+      tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile);
       const int e = p.expert_ids[m_blk];
       if (e < 0 || e >= p.num_experts) continue;
       const int acc = local & 1;
@@ -242,8 +247,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int i = v * 8 + j * 2;
-                float o0 = silu_mul(__uint_as_float(g[i]) * rs, __uint_as_float(u[i]) * rs);
-                float o1 = silu_mul(__uint_as_float(g[i + 1]) * rs, __uint_as_float(u[i + 1]) * rs);
+                float o0 = act_mul(__uint_as_float(g[i]) * rs, __uint_as_float(u[i]) * rs, p.activation);
+                float o1 = act_mul(__uint_as_float(g[i + 1]) * rs, __uint_as_float(u[i + 1]) * rs, p.activation);
                 w[j] = pack_bf16x2(o0, o1);
               }
               dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -371,6 +376,8 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.k_steps = (int)ceil_div<int64_t>(g.k * 2, KBYTES);
   p.n_tiles = (int)ceil_div<int64_t>(g.n, GATED ? 128 : 256);
   p.max_blocks = (int)g.max_blocks;
+  p.activation = g.activation;
+  p.group_m = pick_group_m(BM, g.k * 2);
   const int64_t max_tiles = g.max_blocks * p.n_tiles;
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sm_count > 0 ? sm_count : 148, max_tiles));
   grouped_gemm_tcgen05_kernel<GATED><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);

@@ -51,6 +51,8 @@ struct Fp8Params {
   int32_t kblocks;
   int32_t n_tiles;
   int32_t max_blocks;
+  int32_t activation;
+  int32_t group_m;
 };
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_device_status, 0, code); }
@@ -107,7 +109,8 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     uint32_t phase = 0;
     bool alive = true;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-      const int m_blk = (int)(tile % used_blocks), n_tile = (int)(tile / used_blocks);
+      int m_blk, n_tile;
+      tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile);
       const int e = p.expert_ids[m_blk];
       if (e < 0 || e >= p.num_experts) continue;
       const int32_t row_a = m_blk * BM;
@@ -155,7 +158,8 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     uint32_t step = 0;  // K blocks issued so far by this CTA (selects the partial and its phase)
     bool alive = true;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-      const int m_blk = (int)(tile % used_blocks);
+      int m_blk, n_tile_unused;
+        tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile_unused);
       const int e = p.expert_ids[m_blk];
       if (e < 0 || e >= p.num_experts) continue;
       for (int kb = 0; kb < kblocks; ++kb, ++step) {
@@ -198,7 +202,8 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     uint32_t step = 0;
     bool alive = true;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-      const int m_blk = (int)(tile % used_blocks), n_tile = (int)(tile / used_blocks);
+      int m_blk, n_tile;
+      tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile);
       const int e = p.expert_ids[m_blk];
       if (e < 0 || e >= p.num_experts) continue;
       const int64_t pos = (int64_t)m_blk * BM + row;
@@ -262,7 +267,8 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int i = v * 8 + j * 2;
-              w[j] = pack_bf16x2(silu_mul(acc[i] * rs, acc[32 + i] * rs), silu_mul(acc[i + 1] * rs, acc[32 + i + 1] * rs));
+              w[j] = pack_bf16x2(act_mul(acc[i] * rs, acc[32 + i] * rs, p.activation),
+                                 act_mul(acc[i + 1] * rs, acc[32 + i + 1] * rs, p.activation));
             }
             dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
           }
@@ -340,6 +346,8 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.kblocks = (int)(g.k / 128);
   p.n_tiles = (int)ceil_div<int64_t>(g.n, GATED ? 128 : 256);
   p.max_blocks = (int)g.max_blocks;
+  p.activation = g.activation;
+  p.group_m = pick_group_m(BM, g.k);
   const int64_t max_tiles = g.max_blocks * p.n_tiles;
   const int sms = device_sm_count();
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sms > 0 ? sms : 148, max_tiles));

@@ -166,7 +166,7 @@ def fused_experts(
     assert per_channel_quant is False, _UNSUPPORTED_FEATURE_MSG.format(name="per_channel_quant")
     assert a1_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="a1_scale")
     assert a2_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="a2_scale")
-    if activation != "silu":
+    if activation not in _C.ACTIVATIONS:
         raise ValueError(f"Unsupported FusedMoe activation: {activation}")
     dev = _C.require_cuda(hidden_states, w1, w2, topk_weights, topk_ids, w1_scale, w2_scale, expert_map)
     assert hidden_states.ndim == 2, "hidden_states must be 2D"
@@ -217,7 +217,7 @@ def fused_experts(
         fa = _C.FusedArgs(
             dtype=_C.E4M3 if use_fp8_w8a8 else _C.DTYPE_CODE[out_dtype], variant=_C.VARIANTS[forced], num_experts=E,
             top_k=k, apply_router_weight_on_input=int(apply_router_weight_on_input), no_combine=int(no_combine),
-            zero_dropped=int(expert_map is not None), T=T, H=H, I=I,
+            zero_dropped=int(expert_map is not None), activation=_C.ACTIVATIONS[activation], T=T, H=H, I=I,
             routed_scaling_factor=1.0 if routed_scaling_factor is None else float(routed_scaling_factor),
             hidden=x.data_ptr(), w1=w1.data_ptr(), w2=w2.data_ptr(), w1_scale=_C.ptr(w1_scale),
             w2_scale=_C.ptr(w2_scale), topk_weights=wts.data_ptr(), topk_ids=ids.data_ptr(), out=out.data_ptr())
@@ -238,7 +238,7 @@ def fused_experts(
     max_blocks = min(cap // block, numel)
     row_w = wts.data_ptr()
     code = _C.DTYPE_CODE[out_dtype]
-    common = dict(variant=vcode, num_experts=E, top_k=k, block_size=block, numel=numel, sorted_cap=cap,
+    common = dict(variant=vcode, activation=_C.ACTIVATIONS[activation], num_experts=E, top_k=k, block_size=block, numel=numel, sorted_cap=cap,
                   max_blocks=max_blocks, sorted_token_ids=sorted_ids.data_ptr(), expert_ids=expert_ids.data_ptr(),
                   num_tokens_post_padded=num_post.data_ptr())
 
@@ -247,7 +247,7 @@ def fused_experts(
     z = z_alloc((numel, H), dtype=out_dtype, device=dev)
 
     if not use_fp8_w8a8:
-        if name == "tcgen05":
+        if name in ("tcgen05", "tcgen05_pair"):
             xs = torch.empty((cap, H), dtype=out_dtype, device=dev)
             _C.check(lib.fmoe_gather_rows(x.data_ptr(), x.element_size(), cap, H, sorted_ids.data_ptr(), k, numel,
                                           num_post.data_ptr(), xs.data_ptr(), st))
@@ -380,7 +380,7 @@ def triton_kernel_fused_experts(
     assert w2.dtype == torch.bfloat16, "w2 must be bfloat16"
     assert hidden_states.shape[-1] == w1.shape[-2], "hidden size mismatch"
     assert w2.shape[-1] == w1.shape[1], "intermediate size mismatch"
-    if activation != "silu":
+    if activation not in _C.ACTIVATIONS:
         raise ValueError(f"Unsupported FusedMoe activation: {activation}")
 
     T, H = hidden_states.shape
@@ -397,7 +397,8 @@ def triton_kernel_fused_experts(
     w_flat[topk_indx] = routing_data.gate_scal.float()
     z_or_out = fused_experts(
         hidden_states, _k_major(w1), _k_major(w2), w_flat.view(T, k), ids_flat.view(T, k),
-        apply_router_weight_on_input=apply_router_weight_on_input, no_combine=scatter_indx is None,
+        activation=activation, apply_router_weight_on_input=apply_router_weight_on_input,
+        no_combine=scatter_indx is None,
     )
     if scatter_indx is None:
         # reference returns rows in sorted order p; ours are by flat slot

@@ -35,11 +35,16 @@ extern "C" {
 #define FMOE_BF16 1
 #define FMOE_E4M3 2
 
+/* gated activation applied by gemm1 */
+#define FMOE_ACT_SILU 0
+#define FMOE_ACT_GELU 1
+
 /* grouped-GEMM kernel families (fmoe_gemm_args.variant) */
 #define FMOE_VARIANT_AUTO 0
 #define FMOE_VARIANT_SIMT 1    /* plain CUDA-core kernel; any shape; validation and fp32 */
 #define FMOE_VARIANT_STREAM 2  /* small-M weight-streaming kernel, split-K over warps */
 #define FMOE_VARIANT_TCGEN05 3 /* TMA + tcgen05/TMEM persistent kernel for large M */
+#define FMOE_VARIANT_TCGEN05_PAIR 4 /* same on CTA pairs (cta_group::2), 256-row blocks, bf16 */
 
 int fmoe_version(void);
 /* Message of the last error returned on the calling thread ("" if none). */
@@ -140,7 +145,7 @@ typedef struct fmoe_gemm_args {
   int32_t block_size;  /* block used for sorted_token_ids / expert_ids                   */
   int32_t a_gather;    /* 1: row of `a` for sorted position p is slot/top_k ([T,K] input)
                           0: row of `a` is p itself (input already in sorted order)      */
-  int32_t reserved;
+  int32_t activation;  /* gemm1: FMOE_ACT_SILU | FMOE_ACT_GELU                          */
   int64_t numel;       /* T*k: sentinel in sorted_token_ids, number of output slots      */
   int64_t n;           /* gemm1: I (w has 2I rows per expert); gemm2: H                  */
   int64_t k;           /* reduction length: gemm1 H, gemm2 I                             */
@@ -159,7 +164,7 @@ typedef struct fmoe_gemm_args {
   float* out_scale;    /* gemm1 with out_dtype e4m3: [sorted_cap, I/128]                 */
 } fmoe_gemm_args;
 
-/* gemm1: out[p, c] = silu(acc[p, c]) * acc[p, I + c], acc = (a_row(p) . w[e(p)]^T) * row_scale. */
+/* gemm1: out[p, c] = act(acc[p, c]) * acc[p, I + c], acc = (a_row(p) . w[e(p)]^T) * row_scale. */
 int fmoe_gemm1_silu(const fmoe_gemm_args* args, void* stream);
 /* gemm2: out[slot(p), :] = (a[p, :] . w[e(p)]^T) * row_scale[slot(p)], rounded to out_dtype. */
 int fmoe_gemm2(const fmoe_gemm_args* args, void* stream);
@@ -190,7 +195,7 @@ typedef struct fmoe_fused_args {
   int32_t apply_router_weight_on_input; /* 1: top-k weight scales the gemm1 input rows instead of gemm2's output */
   int32_t no_combine;   /* 1: out is [T,k,H] (rows by flat slot), no sum over k                            */
   int32_t zero_dropped; /* 1: slots whose id is outside [0,E) must read as zero (expert-parallel shards)  */
-  int32_t reserved;
+  int32_t activation;   /* FMOE_ACT_SILU | FMOE_ACT_GELU                                                  */
   int64_t T, H, I;
   float routed_scaling_factor; /* applied after the sum when != 1 (ignored with no_combine)              */
   float reserved_f;

@@ -33,6 +33,23 @@ def silu_and_mul(y1: torch.Tensor, dtype: torch.dtype | None = None) -> torch.Te
     return ((g / (1.0 + torch.exp(-g))) * u).to(dtype)
 
 
+def gelu_and_mul(y1: torch.Tensor, dtype: torch.dtype | None = None) -> torch.Tensor:
+    """out[r,c] = gelu(y1[r,c]) * y1[r,I+c] with the erf form of gelu, fp32 math: the reference's second
+    activation (ref:src/flaggems_sglang/ops/fused_moe.py:219-220 delegates it to an external kernel)."""
+    dtype = y1.dtype if dtype is None else dtype
+    f = y1.to(torch.float32)
+    half = f.shape[-1] // 2
+    return (torch.nn.functional.gelu(f[..., :half]) * f[..., half:]).to(dtype)
+
+
+def _act(name: str):
+    if name == "silu":
+        return silu_and_mul
+    if name == "gelu":
+        return gelu_and_mul
+    raise ValueError(f"Unsupported FusedMoe activation: {name}")
+
+
 def _expert_segments(hist):
     offs = np.concatenate(([0], np.cumsum(hist)))
     return [(e, int(offs[e]), int(offs[e + 1])) for e in range(len(hist)) if hist[e] > 0]
@@ -45,6 +62,7 @@ def reference_fused_experts(
     routing: dict,
     apply_router_weight_on_input: bool = False,
     no_combine: bool = False,
+    activation: str = "silu",
 ) -> torch.Tensor:
     """The reference op on its own layouts: w1 [E,H,2I], w2 [E,I,H], routing tables.
 
@@ -76,7 +94,7 @@ def reference_fused_experts(
         if apply_router_weight_on_input:
             acc1 = acc1 * gate_scal[lo:hi, None]
         y1 = _rb(acc1, dtype)
-        a = silu_and_mul(y1, dtype).to(torch.float32)
+        a = _act(activation)(y1, dtype).to(torch.float32)
         acc2 = a @ w2[e].detach().cpu().to(torch.float32)
         if not apply_router_weight_on_input:
             acc2 = acc2 * gate_scal[lo:hi, None]
@@ -99,6 +117,7 @@ def fused_experts(
     apply_router_weight_on_input: bool = False,
     no_combine: bool = False,
     routed_scaling_factor: float | None = None,
+    activation: str = "silu",
 ) -> torch.Tensor:
     """Same computation on the serving-side layouts: w1 [E,2I,H], w2 [E,H,I].
 
@@ -126,7 +145,7 @@ def fused_experts(
         if apply_router_weight_on_input:
             acc1 = acc1 * wts[slots, None]
         y1 = _rb(acc1, dtype)
-        a = silu_and_mul(y1, dtype).to(torch.float32)
+        a = _act(activation)(y1, dtype).to(torch.float32)
         acc2 = a @ w2[e].detach().cpu().to(torch.float32).t()
         if not apply_router_weight_on_input:
             acc2 = acc2 * wts[slots, None]

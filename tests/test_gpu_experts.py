@@ -157,6 +157,18 @@ def test_one_call_entry_equals_kernel_by_kernel_path(fg, variant, fp8):
     assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("variant", ["simt", "stream", "tcgen05"])
+def test_gelu_activation(fg, variant):
+    """The reference's second activation (gelu-and-mul, ref fused_moe.py:219-220)."""
+    T, H, I, E, k = 40, 256, 384, 8, 2
+    x, w1, w2, logits = _layer(T, H, I, E, k, torch.bfloat16, 21)
+    tw, ti = OR.softmax_topk(logits, k, True)
+    out = _run(fg, x, w1, w2, tw, ti, variant=variant, activation="gelu")
+    assert_close_moe(out, OE.fused_experts(x, w1, w2, tw, ti, activation="gelu"), "bf16", f"gelu {variant}")
+    with pytest.raises(ValueError, match="Unsupported FusedMoe activation"):
+        _run(fg, x, w1, w2, tw, ti, activation="relu")
+
+
 def test_empty_batch(fg):
     x, w1, w2, logits = _layer(4, 128, 128, 4, 2, torch.bfloat16, 1)
     out = fg.fused_experts(x[:0].cuda(), w1.cuda(), w2.cuda(), torch.zeros(0, 2).cuda(),

@@ -81,6 +81,8 @@ def main():
     ap.add_argument("--config", default="mixtral")
     ap.add_argument("--tokens", default="")
     ap.add_argument("--with-transpose", action="store_true")
+    ap.add_argument("--plain-reps", type=int, default=0,
+                    help="run each path this many times back to back without do_bench (for a profiler's launch list)")
     args = ap.parse_args()
 
     import flaggems_sglang_b200 as fg
@@ -114,6 +116,14 @@ def main():
             return tk_experts(x, a, b, *routing_tables(tw, ti, cfg.E))
 
         rec = {"config": cfg.name, "T": T}
+        if args.plain_reps:
+            for _ in range(args.plain_reps):
+                ref_experts_only()
+            for _ in range(args.plain_reps):
+                ours_experts()
+            torch.cuda.synchronize()
+            print(json.dumps({"config": cfg.name, "T": T, "plain_reps": args.plain_reps}), flush=True)
+            continue
         try:
             ref = ref_experts_only()
             got = ours_experts()

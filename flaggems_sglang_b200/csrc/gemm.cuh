@@ -35,11 +35,32 @@ __device__ __forceinline__ void tile_to_mn(int64_t tile, int used_blocks, int n_
   *n_tile = r / rows;
   *m_blk = g * group_m + r % rows;
 }
-// rows blocks per group so that the group's A operand takes about 48 MB
-inline int pick_group_m(int64_t block_rows, int64_t k_bytes_per_row) {
-  const int64_t per_block = block_rows * k_bytes_per_row;
-  int64_t g = (48ll << 20) / (per_block > 0 ? per_block : 1);
-  return (int)(g < 1 ? 1 : (g > (1 << 20) ? (1 << 20) : g));
+// Row blocks per group.  The `ctas` tiles that run at the same time form a group_m x (ctas/group_m)
+// rectangle; its HBM traffic is one A block per row block plus one B tile per (expert, column tile)
+// present.  Pick the group_m that minimises that, with the expected row blocks per expert estimated
+// from the launch bounds (no reliance on L2 keeping data between waves).
+inline int pick_group_m(const GemmParams& g, int64_t block_rows, int64_t k_bytes_per_row, int n_tiles, int ctas) {
+  const double a_blk = (double)block_rows * (double)k_bytes_per_row;
+  const double b_tile = 256.0 * (double)k_bytes_per_row;
+  const double active = (double)(g.numel < g.num_experts ? (g.numel > 0 ? g.numel : 1) : g.num_experts);
+  double bpe = (double)g.numel / active / (double)block_rows;
+  if (bpe < 1.0) bpe = 1.0;
+  int best = 1;
+  double best_cost = 1e300;
+  const int limit = ctas < 1 ? 1 : ctas;
+  for (int gm = 1; gm <= limit; ++gm) {
+    double gn = (double)limit / gm;
+    if (gn > n_tiles) gn = n_tiles;
+    double experts = gm / bpe;
+    if (experts < 1.0) experts = 1.0;
+    // traffic per tile of the wave
+    const double cost = (gm * a_blk + experts * gn * b_tile) / (gm * gn);
+    if (cost < best_cost * 0.999) {
+      best_cost = cost;
+      best = gm;
+    }
+  }
+  return best;
 }
 
 // device status word written by bounded waits (gemm_tcgen05.cu)

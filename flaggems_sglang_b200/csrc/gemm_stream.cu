@@ -13,6 +13,8 @@
 // items to fill the GPU, 2/4/8 warps of a CTA share an item, split K in chunks of 128 and
 // are reduced through shared memory in a fixed order (bit-reproducible).  gemm1 pairs 16
 // gate rows with the matching 16 up rows so that silu(gate)*up is applied in registers.
+#include <cstdlib>
+
 #include "gemm.cuh"
 
 namespace fmoe {
@@ -221,9 +223,18 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
 }
 
 // Warps per item: enough warps in flight to cover HBM latency, but at least two 128-k chunks per warp.
-int pick_ksplit(int64_t items, int64_t kblocks) {
-  const int64_t target = 148 * 16;
+int pick_ksplit(int64_t items, int64_t kblocks, int elem_bytes) {
+  // FMOE_STREAM_W=1|2|4|8 forces the split (tuning aid)
+  if (const char* env = getenv("FMOE_STREAM_W")) {
+    int w = atoi(env);
+    if (w == 1 || w == 2 || w == 4 || w == 8) return w;
+  }
+  // Measured on B200: with 2-byte elements a warp touches 256 contiguous bytes of a row per step and
+  // HBM streams best when the warps of a CTA walk one row range together (W = 8 gives 2 KB runs);
+  // with 1-byte elements the runs are short either way and fewer, longer-lived warps win.
   int W = 1;
+  if (elem_bytes == 2) W = kblocks >= 16 ? 8 : (kblocks >= 8 ? 4 : (kblocks >= 4 ? 2 : 1));
+  const int64_t target = 148 * 16;
   while (W < kWarps && items * W < target && kblocks / (2 * W) >= 2) W *= 2;
   return W;
 }
@@ -232,7 +243,7 @@ template <int EB, int NTG, bool GATED>
 int launch(const GemmParams& p, cudaStream_t st) {
   const int n_slabs = (int)ceil_div<int64_t>(p.n, GATED ? 16 : 32);
   const int64_t items = p.max_blocks * n_slabs;
-  const int W = pick_ksplit(items, p.k / 128);
+  const int W = pick_ksplit(items, p.k / 128, EB);
   const int64_t ctas = ceil_div<int64_t>(items, kWarps / W);
   if (ctas >= (1ll << 31)) return fail(FMOE_ERR_UNSUPPORTED, "stream gemm: too many work items");
   const size_t smem = W > 1 ? sizeof(float) * kWarps * RT * NTG * 4 * 32 : 0;

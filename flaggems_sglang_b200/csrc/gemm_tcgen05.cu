@@ -377,9 +377,10 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.n_tiles = (int)ceil_div<int64_t>(g.n, GATED ? 128 : 256);
   p.max_blocks = (int)g.max_blocks;
   p.activation = g.activation;
-  p.group_m = pick_group_m(BM, g.k * 2);
+
   const int64_t max_tiles = g.max_blocks * p.n_tiles;
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sm_count > 0 ? sm_count : 148, max_tiles));
+  p.group_m = pick_group_m(g, BM, g.k * 2, p.n_tiles, (int)grid);
   grouped_gemm_tcgen05_kernel<GATED><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_kernel");
 }

@@ -333,10 +333,11 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.n_tiles = (int)ceil_div<int64_t>(g.n, GATED ? 128 : 256);
   p.max_blocks = (int)g.max_blocks;
   p.activation = g.activation;
-  p.group_m = pick_group_m(PAIR_M, g.k * 2);
+
   const int64_t max_tiles = g.max_blocks * p.n_tiles;
   const int sms = device_sm_count();
   const int64_t pairs = std::max<int64_t>(1, std::min<int64_t>((sms > 0 ? sms : 148) / 2, max_tiles));
+  p.group_m = pick_group_m(g, PAIR_M, g.k * 2, p.n_tiles, (int)pairs);
   grouped_gemm_tcgen05_pair_kernel<GATED><<<(unsigned)(2 * pairs), kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_pair_kernel");
 }

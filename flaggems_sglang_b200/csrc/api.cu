@@ -91,6 +91,13 @@ extern "C" int fmoe_gemm2(const fmoe_gemm_args* args, void* stream) {
   return fmoe::dispatch_gemm(args, false, stream, "gemm2");
 }
 
+namespace fmoe { int read_wait_profile(long long* host_out, int n); }
+
+extern "C" int fmoe_debug_tcgen05_wait_profile(int64_t* host_out, int n) {
+  if (!host_out || n < 0 || n > 256 * 8) return fmoe::fail(FMOE_ERR_INVALID_ARG, "wait profile: bad buffer");
+  return fmoe::read_wait_profile(reinterpret_cast<long long*>(host_out), n);
+}
+
 extern "C" int fmoe_check_device_status(void* stream) {
   int status = 0;
   int rc = fmoe::read_and_clear_device_status((cudaStream_t)stream, &status);

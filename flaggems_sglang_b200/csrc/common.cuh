@@ -79,6 +79,14 @@ __device__ __forceinline__ float act_mul(float g, float u, int activation) {
   return silu_mul(g, u);
 }
 
+// Same with the hardware approximations (ex2 / rcp based, relative error ~1e-6, far below the bf16
+// rounding of the result): the exact IEEE division and expf cost ~50 instructions per output, which made
+// the epilogue of the large-M kernels as long as a short main loop.
+__device__ __forceinline__ float act_mul_fast(float g, float u, int activation) {
+  if (activation == FMOE_ACT_GELU) return 0.5f * g * (1.0f + erff(g * 0.70710678118654752f)) * u;
+  return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

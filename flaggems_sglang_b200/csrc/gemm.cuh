@@ -22,45 +22,50 @@ bool gemm_tcgen05_supports(const GemmParams& p, bool gated);
 bool gemm_tcgen05_fp8_supports(const GemmParams& p, bool gated);
 bool gemm_tcgen05_pair_supports(const GemmParams& p, bool gated);
 
-// Tile order of the persistent kernels.  Tiles are walked in groups of `group_m` consecutive row blocks:
-// inside a group the row block varies fastest, then the column tile, so that CTAs running at the same
-// time share a weight tile through L2 while the group's activation rows (sized to fit L2) are re-read
-// from L2, not HBM, for every column tile.
-__device__ __forceinline__ void tile_to_mn(int64_t tile, int used_blocks, int n_tiles, int group_m, int* m_blk,
-                                           int* n_tile) {
-  const int64_t per_group = (int64_t)group_m * n_tiles;
-  const int g = (int)(tile / per_group);
-  const int r = (int)(tile % per_group);
-  const int rows = min(group_m, used_blocks - g * group_m);
-  *n_tile = r / rows;
-  *m_blk = g * group_m + r % rows;
-}
-// Row blocks per group.  The `ctas` tiles that run at the same time form a group_m x (ctas/group_m)
-// rectangle; its HBM traffic is one A block per row block plus one B tile per (expert, column tile)
-// present.  Pick the group_m that minimises that, with the expected row blocks per expert estimated
-// from the launch bounds (no reliance on L2 keeping data between waves).
-inline int pick_group_m(const GemmParams& g, int64_t block_rows, int64_t k_bytes_per_row, int n_tiles, int ctas) {
-  const double a_blk = (double)block_rows * (double)k_bytes_per_row;
-  const double b_tile = 256.0 * (double)k_bytes_per_row;
-  const double active = (double)(g.numel < g.num_experts ? (g.numel > 0 ? g.numel : 1) : g.num_experts);
-  double bpe = (double)g.numel / active / (double)block_rows;
-  if (bpe < 1.0) bpe = 1.0;
-  int best = 1;
-  double best_cost = 1e300;
-  const int limit = ctas < 1 ? 1 : ctas;
-  for (int gm = 1; gm <= limit; ++gm) {
-    double gn = (double)limit / gm;
-    if (gn > n_tiles) gn = n_tiles;
-    double experts = gm / bpe;
-    if (experts < 1.0) experts = 1.0;
-    // traffic per tile of the wave
-    const double cost = (gm * a_blk + experts * gn * b_tile) / (gm * gn);
-    if (cost < best_cost * 0.999) {
-      best_cost = cost;
-      best = gm;
+// Tile order of the persistent kernels: expert by expert, and inside an expert in groups of at most
+// `group_m` row blocks; inside a group the row block varies fastest, then the column tile.  The tiles
+// that run at the same time therefore belong to one or a few experts: each weight tile is fetched
+// from HBM once and shared through L2 by the row blocks of its expert, while the group's activation
+// rows (a few MB) stay hot in L2 across the column tiles.
+//
+// Because every expert's tiles are contiguous in this order, the expert of tile t is the expert of
+// row block floor(t / n_tiles); its first and last block are found by bisection in expert_ids
+// (ascending by construction) and cached while consecutive tiles stay inside the same expert.
+struct TileCursor {
+  int first = 0, last = 0;  // block range [first, last) of the cached expert; empty = nothing cached
+  __device__ __forceinline__ void locate(int64_t tile, int used_blocks, int n_tiles, int group_m,
+                                         const int32_t* __restrict__ expert_ids, int* m_blk, int* n_tile) {
+    const int q = (int)(tile / n_tiles);
+    if (q < first || q >= last) {
+      const int e = expert_ids[q];
+      int lo = 0, hi = q;  // first index with expert_ids[i] >= e
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (expert_ids[mid] < e) lo = mid + 1; else hi = mid;
+      }
+      first = lo;
+      lo = q + 1, hi = used_blocks;  // first index past q with expert_ids[i] != e
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (expert_ids[mid] == e) lo = mid + 1; else hi = mid;
+      }
+      last = lo;
     }
+    const int nb = last - first;
+    const int64_t local = tile - (int64_t)first * n_tiles;
+    const int64_t per_group = (int64_t)group_m * n_tiles;
+    const int g = (int)(local / per_group);
+    const int r = (int)(local % per_group);
+    const int rows = min(group_m, nb - g * group_m);
+    *n_tile = r / rows;
+    *m_blk = first + g * group_m + r % rows;
   }
-  return best;
+};
+// Row blocks per group: the group's A rows should stay around 16 MB.
+inline int pick_group_m(int64_t block_rows, int64_t k_bytes_per_row) {
+  const int64_t per_block = block_rows * k_bytes_per_row;
+  int64_t g = (16ll << 20) / (per_block > 0 ? per_block : 1);
+  return (int)(g < 4 ? 4 : (g > 64 ? 64 : g));
 }
 
 // device status word written by bounded waits (gemm_tcgen05.cu)

@@ -20,24 +20,34 @@
 #include "gemm.cuh"
 #include "ptx_sm100.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace fmoe {
 
 __device__ int g_device_status = 0;  // 0 = fine; otherwise (role << 8 | site) of the first wait that gave up
+// Optional wait-time profile (FMOE_TC_PROFILE=1): per CTA {tiles, mma wait acc, mma wait data, producer wait, epilogue wait, epilogue busy}
+__device__ long long g_wait_prof[256 * 8];
 
 namespace {
 
 constexpr int BM = 128;
 constexpr int BN = 256;
-constexpr int KBYTES = 128;  // bytes of K per stage row
-constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * KBYTES;  // 16 KB
-constexpr int B_BYTES = BN * KBYTES;  // 32 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+// Ring geometry for KB bytes of K per stage row.  KB = 128 (64 bf16, 128-byte swizzle, 4 stages of 48 KB) is the
+// one in use; a 9-stage ring of 64-byte rows (64-byte swizzle) was measured 35-40 % slower on B200 and an L2
+// prefetch of the weight boxes 6-15 % slower, so neither is built.
+template <int KB>
+struct Ring {
+  static constexpr int KBYTES = KB;
+  static_assert(KB == 128, "only the 128-byte ring is built");
+  static constexpr int STAGES = 4;
+  static constexpr int A_BYTES = BM * KB;
+  static constexpr int B_BYTES = BN * KB;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 constexpr int TMEM_COLS = 512;
 constexpr int kThreads = 192;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
 
 struct TcParams {
   const int32_t* sorted_token_ids;
@@ -55,20 +65,27 @@ struct TcParams {
   int32_t max_blocks;
   int32_t activation;
   int32_t group_m;
+  int32_t profile;
 };
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_device_status, 0, code); }
 
-// Bounded wait whose verdict is uniform across the warp (all lanes poll; any time-out fails the warp),
-// so that the role loops never diverge around their __syncwarp() points.
+// Bounded wait whose verdict is uniform across the warp, so that the role loops never diverge around
+// their __syncwarp() points.
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
   return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity));
 }
 
-template <bool GATED>
+__device__ __forceinline__ bool warp_wait_relaxed(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, ptx::mbar_wait_relaxed(bar, parity));
+}
+
+template <bool GATED, int KB>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                             const TcParams p) {
+  constexpr int KBYTES = Ring<KB>::KBYTES, STAGES = Ring<KB>::STAGES, A_BYTES = Ring<KB>::A_BYTES,
+                B_BYTES = Ring<KB>::B_BYTES, STAGE_BYTES = Ring<KB>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -106,6 +123,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
   const int used_blocks = min((int)(*p.num_tokens_post_padded / BM), p.max_blocks);
   const int64_t total_tiles = (int64_t)used_blocks * p.n_tiles;
+  TileCursor cursor;
   const int k_steps = p.k_steps;
 
   if (warp == 4) {
@@ -113,16 +131,25 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
-    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+    long long prof_a = 0;
+    // coordinates of a tile; looked up one tile ahead so that the index loads never stall the ring
+    auto tile_rows = [&](int64_t tile, int32_t* row_a, int32_t* row_b0, int32_t* row_b1) {
       int m_blk, n_tile;
-      tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile);
-      const int e = p.expert_ids[m_blk];
-      if (e < 0 || e >= p.num_experts) continue;
-      const int32_t row_a = m_blk * BM;
-      const int32_t row_b0 = (int32_t)((int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256));
-      const int32_t row_b1 = GATED ? (int32_t)(row_b0 + p.n) : row_b0 + 128;
+      cursor.locate(tile, used_blocks, p.n_tiles, p.group_m, p.expert_ids, &m_blk, &n_tile);
+      const int e = min(max(p.expert_ids[m_blk], 0), p.num_experts - 1);
+      *row_a = m_blk * BM;
+      *row_b0 = (int32_t)((int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256));
+      *row_b1 = GATED ? (int32_t)(*row_b0 + p.n) : *row_b0 + 128;
+    };
+    int32_t row_a = 0, row_b0 = 0, row_b1 = 0, nrow_a = 0, nrow_b0 = 0, nrow_b1 = 0;
+    if ((int64_t)blockIdx.x < total_tiles) tile_rows(blockIdx.x, &row_a, &row_b0, &row_b1);
+    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      const bool has_next = tile + gridDim.x < total_tiles;
       for (int ks = 0; ks < k_steps; ++ks) {
-        if (!warp_wait(&empty_bar[stage], phase ^ 1)) {
+        const long long tp0 = p.profile ? clock64() : 0;
+        const bool okp = warp_wait(&empty_bar[stage], phase ^ 1);
+        if (p.profile) prof_a += clock64() - tp0;
+        if (!okp) {
           report(0x100 | stage);
           alive = false;
           break;
@@ -137,12 +164,17 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           ptx::tma_load_2d(sb + B_BYTES / 2, &map_b, x, row_b1, &full_bar[stage]);
         }
         __syncwarp();
+        if (ks == 0 && has_next) tile_rows(tile + gridDim.x, &nrow_a, &nrow_b0, &nrow_b1);
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1;
         }
       }
+      row_a = nrow_a;
+      row_b0 = nrow_b0;
+      row_b1 = nrow_b1;
     }
+    if (p.profile && lane == 0 && blockIdx.x < 256) g_wait_prof[blockIdx.x * 8 + 3] = prof_a;
     // drain: do not leave while our own bulk copies may still be landing in shared memory
     if (alive) {
       for (int s = 0; s < STAGES; ++s) {
@@ -165,15 +197,15 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     uint32_t phase = 0;
     int local = 0;
     bool alive = true;
+    long long prof_acc = 0, prof_data = 0;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-      int m_blk, n_tile_unused;
-        tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile_unused);
-      const int e = p.expert_ids[m_blk];
-      if (e < 0 || e >= p.num_experts) continue;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ++local;
-      if (!warp_wait(&acc_empty[acc], acc_phase ^ 1)) {
+      const long long tm0 = p.profile ? clock64() : 0;
+      const bool oka = warp_wait(&acc_empty[acc], acc_phase ^ 1);
+      if (p.profile) prof_acc += clock64() - tm0;
+      if (!oka) {
         report(0x200 | acc);
         alive = false;
         break;
@@ -181,7 +213,10 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       ptx::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + acc * BN;
       for (int ks = 0; ks < k_steps; ++ks) {
-        if (!warp_wait(&full_bar[stage], phase)) {
+        const long long tm1 = p.profile ? clock64() : 0;
+        const bool okd = warp_wait(&full_bar[stage], phase);
+        if (p.profile) prof_data += clock64() - tm1;
+        if (!okd) {
           report(0x240 | stage);
           alive = false;
           break;
@@ -207,16 +242,20 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       if (alive && lane == 0) ptx::mma_commit(&acc_full[acc]);
       __syncwarp();
     }
+    if (p.profile && lane == 0 && blockIdx.x < 256) {
+      g_wait_prof[blockIdx.x * 8 + 0] = local;
+      g_wait_prof[blockIdx.x * 8 + 1] = prof_acc;
+      g_wait_prof[blockIdx.x * 8 + 2] = prof_data;
+    }
   } else {
     // ---------------- epilogue (warps 0-3) ----------------
     int local = 0;
     bool alive = true;
+    long long prof_wait = 0, prof_busy = 0;
     const int row = warp * 32 + lane;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
       int m_blk, n_tile;
-      tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile);
-      const int e = p.expert_ids[m_blk];
-      if (e < 0 || e >= p.num_experts) continue;
+      cursor.locate(tile, used_blocks, p.n_tiles, p.group_m, p.expert_ids, &m_blk, &n_tile);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ++local;
@@ -224,7 +263,11 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       const int32_t slot = (pos < p.sorted_cap) ? p.sorted_token_ids[pos] : -1;
       const bool valid = slot >= 0 && slot < p.numel;
       const float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
-      if (!warp_wait(&acc_full[acc], acc_phase)) {
+      const long long te0 = p.profile ? clock64() : 0;
+      const bool oke = warp_wait_relaxed(&acc_full[acc], acc_phase);
+      const long long te1 = p.profile ? clock64() : 0;
+      prof_wait += te1 - te0;
+      if (!oke) {
         report(0x300 | acc);
         alive = false;
         break;
@@ -247,8 +290,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int i = v * 8 + j * 2;
-                float o0 = act_mul(__uint_as_float(g[i]) * rs, __uint_as_float(u[i]) * rs, p.activation);
-                float o1 = act_mul(__uint_as_float(g[i + 1]) * rs, __uint_as_float(u[i + 1]) * rs, p.activation);
+                float o0 = act_mul_fast(__uint_as_float(g[i]) * rs, __uint_as_float(u[i]) * rs, p.activation);
+                float o1 = act_mul_fast(__uint_as_float(g[i + 1]) * rs, __uint_as_float(u[i + 1]) * rs, p.activation);
                 w[j] = pack_bf16x2(o0, o1);
               }
               dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -281,6 +324,11 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       // accumulator may be overwritten by the MMA warp from here on
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&acc_empty[acc]);
+      if (p.profile) prof_busy += clock64() - te1;
+    }
+    if (p.profile && threadIdx.x == 0 && blockIdx.x < 256) {
+      g_wait_prof[blockIdx.x * 8 + 4] = prof_wait;
+      g_wait_prof[blockIdx.x * 8 + 5] = prof_busy;
     }
   }
 
@@ -323,18 +371,18 @@ int device_sm_count() {
   return sm_count;
 }
 
-// 2-D row-major [rows, cols] tensor of `elem_bytes` elements; box = 128 bytes x box_rows, 128-byte swizzle.
+// 2-D row-major [rows, cols] tensor of `elem_bytes` elements; box = kbytes (128 or 64) x box_rows, swizzle of the same width.
 int make_tensor_map_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int elem_bytes, int box_rows,
-                       bool weights) {
+                       bool weights, int kbytes) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)cols * elem_bytes};
-  cuuint32_t box[2] = {(cuuint32_t)(KBYTES / elem_bytes), (cuuint32_t)box_rows};
+  cuuint32_t box[2] = {(cuuint32_t)(kbytes / elem_bytes), (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B,
+                  kbytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                   weights ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
@@ -343,13 +391,14 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t
 
 namespace {
 
-template <bool GATED>
+template <bool GATED, int KB>
 int launch(const GemmParams& g, cudaStream_t st) {
+  constexpr int SMEM_BYTES = Ring<KB>::SMEM_BYTES, KBYTES = KB;
   const int sm_count = device_sm_count();
   static cudaError_t attr_err = cudaSuccess;
   static std::once_flag once_attr;
   std::call_once(once_attr, [] {
-    attr_err = cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err = cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     SMEM_BYTES);
   });
   if (attr_err != cudaSuccess)
@@ -357,9 +406,9 @@ int launch(const GemmParams& g, cudaStream_t st) {
 
   const int64_t w_rows = GATED ? 2 * g.n : g.n;
   CUtensorMap map_a, map_b;
-  int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 2, BM, false);
+  int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 2, BM, false, KB);
   if (rc) return rc;
-  rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 2, 128, true);
+  rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 2, 128, true, KB);
   if (rc) return rc;
 
   TcParams p;
@@ -380,8 +429,9 @@ int launch(const GemmParams& g, cudaStream_t st) {
 
   const int64_t max_tiles = g.max_blocks * p.n_tiles;
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sm_count > 0 ? sm_count : 148, max_tiles));
-  p.group_m = pick_group_m(g, BM, g.k * 2, p.n_tiles, (int)grid);
-  grouped_gemm_tcgen05_kernel<GATED><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
+  p.group_m = pick_group_m(BM, g.k * 2);
+  p.profile = getenv("FMOE_TC_PROFILE") != nullptr;
+  grouped_gemm_tcgen05_kernel<GATED, KB><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_kernel");
 }
 
@@ -405,14 +455,28 @@ int gemm_tcgen05(const GemmParams& p, bool gated, cudaStream_t st) {
                 "n %% %d == 0, 16-byte aligned pointers (got dtype=%d block=%d a_gather=%d n=%lld k=%lld)",
                 gated ? 128 : 32, p.dtype, p.block_size, p.a_gather, (long long)p.n, (long long)p.k);
   if (p.max_blocks <= 0) return FMOE_OK;
-  return gated ? launch<true>(p, st) : launch<false>(p, st);
+  return gated ? launch<true, 128>(p, st) : launch<false, 128>(p, st);
 }
 
+int read_wait_profile(long long* host_out, int n) {
+  FMOE_CUDA_OK(cudaMemcpyFromSymbol(host_out, g_wait_prof, sizeof(long long) * (size_t)n));
+  return FMOE_OK;
+}
+
+int status_word_fp8(int* out, bool clear);
+int status_word_pair(int* out, bool clear);
+
+// First non-zero status word of the three tcgen05 translation units (each keeps its own); all are cleared.
 int read_and_clear_device_status(cudaStream_t st, int* status_out) {
-  int zero = 0;
+  int zero = 0, a = 0, b = 0, c = 0;
   FMOE_CUDA_OK(cudaStreamSynchronize(st));
-  FMOE_CUDA_OK(cudaMemcpyFromSymbol(status_out, g_device_status, sizeof(int)));
-  if (*status_out != 0) FMOE_CUDA_OK(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+  FMOE_CUDA_OK(cudaMemcpyFromSymbol(&a, g_device_status, sizeof(int)));
+  if (a != 0) FMOE_CUDA_OK(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
+  int rc = status_word_fp8(&b, true);
+  if (rc) return rc;
+  rc = status_word_pair(&c, true);
+  if (rc) return rc;
+  *status_out = a ? a : (b ? b : c);
   return FMOE_OK;
 }
 

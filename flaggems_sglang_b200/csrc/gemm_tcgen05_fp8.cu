@@ -19,7 +19,8 @@
 
 namespace fmoe {
 
-extern __device__ int g_device_status;
+// This translation unit's status word (device code is not linked across files); read by status_word_fp8().
+__device__ int g_device_status_fp8 = 0;
 
 namespace {
 
@@ -55,7 +56,7 @@ struct Fp8Params {
   int32_t group_m;
 };
 
-__device__ __forceinline__ void report(int code) { atomicCAS(&g_device_status, 0, code); }
+__device__ __forceinline__ void report(int code) { atomicCAS(&g_device_status_fp8, 0, code); }
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
   return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity));
 }
@@ -101,6 +102,7 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
 
   const int used_blocks = min((int)(*p.num_tokens_post_padded / BM), p.max_blocks);
   const int64_t total_tiles = (int64_t)used_blocks * p.n_tiles;
+  TileCursor cursor;
   const int kblocks = p.kblocks;
 
   if (warp == kEpiWarps) {
@@ -108,14 +110,19 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
-    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+    // coordinates of a tile; looked up one tile ahead so that the index loads never stall the ring
+    auto tile_rows = [&](int64_t tile, int32_t* row_a, int32_t* row_b0, int32_t* row_b1) {
       int m_blk, n_tile;
-      tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile);
-      const int e = p.expert_ids[m_blk];
-      if (e < 0 || e >= p.num_experts) continue;
-      const int32_t row_a = m_blk * BM;
-      const int32_t row_b0 = (int32_t)((int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256));
-      const int32_t row_b1 = GATED ? (int32_t)(row_b0 + p.n) : row_b0 + 128;
+      cursor.locate(tile, used_blocks, p.n_tiles, p.group_m, p.expert_ids, &m_blk, &n_tile);
+      const int e = min(max(p.expert_ids[m_blk], 0), p.num_experts - 1);
+      *row_a = m_blk * BM;
+      *row_b0 = (int32_t)((int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256));
+      *row_b1 = GATED ? (int32_t)(*row_b0 + p.n) : *row_b0 + 128;
+    };
+    int32_t row_a = 0, row_b0 = 0, row_b1 = 0, nrow_a = 0, nrow_b0 = 0, nrow_b1 = 0;
+    if ((int64_t)blockIdx.x < total_tiles) tile_rows(blockIdx.x, &row_a, &row_b0, &row_b1);
+    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+      const bool has_next = tile + gridDim.x < total_tiles;
       for (int kb = 0; kb < kblocks; ++kb) {
         if (!warp_wait(&empty_bar[stage], phase ^ 1)) {
           report(0x500 | stage);
@@ -132,11 +139,15 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
           ptx::tma_load_2d(sb + B_BYTES / 2, &map_b, x, row_b1, &full_bar[stage]);
         }
         __syncwarp();
+        if (kb == 0 && has_next) tile_rows(tile + gridDim.x, &nrow_a, &nrow_b0, &nrow_b1);
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1;
         }
       }
+      row_a = nrow_a;
+      row_b0 = nrow_b0;
+      row_b1 = nrow_b1;
     }
     if (alive) {  // drain our own bulk copies before leaving
       for (int s = 0; s < STAGES; ++s) {
@@ -158,10 +169,6 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     uint32_t step = 0;  // K blocks issued so far by this CTA (selects the partial and its phase)
     bool alive = true;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-      int m_blk, n_tile_unused;
-        tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile_unused);
-      const int e = p.expert_ids[m_blk];
-      if (e < 0 || e >= p.num_experts) continue;
       for (int kb = 0; kb < kblocks; ++kb, ++step) {
         const int buf = step & 1;
         const uint32_t buf_phase = (step >> 1) & 1;
@@ -203,9 +210,8 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     bool alive = true;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
       int m_blk, n_tile;
-      tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile);
-      const int e = p.expert_ids[m_blk];
-      if (e < 0 || e >= p.num_experts) continue;
+      cursor.locate(tile, used_blocks, p.n_tiles, p.group_m, p.expert_ids, &m_blk, &n_tile);
+      const int e = min(max(p.expert_ids[m_blk], 0), p.num_experts - 1);
       const int64_t pos = (int64_t)m_blk * BM + row;
       const bool in_cap = pos < p.sorted_cap;
       const int32_t slot = in_cap ? p.sorted_token_ids[pos] : -1;
@@ -267,8 +273,8 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const int i = v * 8 + j * 2;
-              w[j] = pack_bf16x2(act_mul(acc[i] * rs, acc[32 + i] * rs, p.activation),
-                                 act_mul(acc[i + 1] * rs, acc[32 + i + 1] * rs, p.activation));
+              w[j] = pack_bf16x2(act_mul_fast(acc[i] * rs, acc[32 + i] * rs, p.activation),
+                                 act_mul_fast(acc[i + 1] * rs, acc[32 + i + 1] * rs, p.activation));
             }
             dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
           }
@@ -309,7 +315,7 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 
 // defined in gemm_tcgen05.cu
 int make_tensor_map_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int elem_bytes, int box_rows,
-                       bool weights);
+                       bool weights, int kbytes);
 int device_sm_count();
 
 namespace {
@@ -326,9 +332,9 @@ int launch(const GemmParams& g, cudaStream_t st) {
     return fail(FMOE_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", SMEM_BYTES, cudaGetErrorString(attr_err));
   const int64_t w_rows = GATED ? 2 * g.n : g.n;
   CUtensorMap map_a, map_b;
-  int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 1, BM, false);
+  int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 1, BM, false, 128);
   if (rc) return rc;
-  rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 1, 128, true);
+  rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 1, 128, true, 128);
   if (rc) return rc;
   Fp8Params p;
   p.sorted_token_ids = g.sorted_token_ids;
@@ -351,7 +357,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
   const int64_t max_tiles = g.max_blocks * p.n_tiles;
   const int sms = device_sm_count();
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sms > 0 ? sms : 148, max_tiles));
-  p.group_m = pick_group_m(g, BM, g.k, p.n_tiles, (int)grid);
+  p.group_m = pick_group_m(BM, g.k);
   grouped_gemm_tcgen05_fp8_kernel<GATED><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_fp8_kernel");
 }
@@ -367,6 +373,13 @@ bool gemm_tcgen05_fp8_supports(const GemmParams& p, bool gated) {
   if ((int64_t)p.num_experts * (gated ? 2 * p.n : p.n) >= (1ll << 31) || p.a_rows >= (1ll << 31)) return false;
   if (p.max_blocks >= (1ll << 24)) return false;
   return true;
+}
+
+int status_word_fp8(int* out, bool clear) {
+  int zero = 0;
+  FMOE_CUDA_OK(cudaMemcpyFromSymbol(out, g_device_status_fp8, sizeof(int)));
+  if (clear && *out != 0) FMOE_CUDA_OK(cudaMemcpyToSymbol(g_device_status_fp8, &zero, sizeof(int)));
+  return FMOE_OK;
 }
 
 int gemm_tcgen05_fp8(const GemmParams& p, bool gated, cudaStream_t st) {

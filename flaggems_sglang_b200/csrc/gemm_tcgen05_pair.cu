@@ -24,9 +24,10 @@
 
 namespace fmoe {
 
-extern __device__ int g_device_status;
+// This translation unit's status word (device code is not linked across files); read by status_word_pair().
+__device__ int g_device_status_pair = 0;
 int make_tensor_map_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int elem_bytes, int box_rows,
-                       bool weights);
+                       bool weights, int kbytes);
 int device_sm_count();
 
 namespace {
@@ -61,9 +62,13 @@ struct PairParams {
   int32_t group_m;
 };
 
-__device__ __forceinline__ void report(int code) { atomicCAS(&g_device_status, 0, code); }
+__device__ __forceinline__ void report(int code) { atomicCAS(&g_device_status_pair, 0, code); }
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
   return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity));
+}
+
+__device__ __forceinline__ bool warp_wait_relaxed(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, ptx::mbar_wait_relaxed(bar, parity));
 }
 
 template <bool GATED>
@@ -111,6 +116,7 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
 
   const int used_blocks = min((int)(*p.num_tokens_post_padded / PAIR_M), p.max_blocks);
   const int64_t total_tiles = (int64_t)used_blocks * p.n_tiles;
+  TileCursor cursor;
   const int k_steps = p.k_steps;
 
   if (warp == 4) {
@@ -118,14 +124,18 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
-    for (int64_t tile = cluster_id; tile < total_tiles && alive; tile += num_clusters) {
+    auto tile_rows = [&](int64_t tile, int32_t* row_a, int32_t* row_b) {
       int m_blk, n_tile;
-      tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile);
-      const int e = p.expert_ids[m_blk];
-      if (e < 0 || e >= p.num_experts) continue;
-      const int32_t row_a = m_blk * PAIR_M + (int)rank * BM;
+      cursor.locate(tile, used_blocks, p.n_tiles, p.group_m, p.expert_ids, &m_blk, &n_tile);
+      const int e = min(max(p.expert_ids[m_blk], 0), p.num_experts - 1);
+      *row_a = m_blk * PAIR_M + (int)rank * BM;
       const int64_t b0 = (int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256);
-      const int32_t row_b = (int32_t)(leader ? b0 : (GATED ? b0 + p.n : b0 + 128));
+      *row_b = (int32_t)(leader ? b0 : (GATED ? b0 + p.n : b0 + 128));
+    };
+    int32_t row_a = 0, row_b = 0, nrow_a = 0, nrow_b = 0;
+    if ((int64_t)cluster_id < total_tiles) tile_rows(cluster_id, &row_a, &row_b);
+    for (int64_t tile = cluster_id; tile < total_tiles && alive; tile += num_clusters) {
+      const bool has_next = tile + num_clusters < total_tiles;
       for (int ks = 0; ks < k_steps; ++ks) {
         if (!warp_wait(&empty_bar[stage], phase ^ 1)) {
           report(0x900 | stage);
@@ -142,11 +152,14 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
           ptx::tma_load_2d_pair(sa + A_BYTES, &map_b, x, row_b, bar0);
         }
         __syncwarp();
+        if (ks == 0 && has_next) tile_rows(tile + num_clusters, &nrow_a, &nrow_b);
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1;
         }
       }
+      row_a = nrow_a;
+      row_b = nrow_b;
     }
     if (alive) {  // drain: every stage this CTA filled has been consumed
       for (int s = 0; s < STAGES; ++s) {
@@ -169,10 +182,6 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
       int local = 0;
       bool alive = true;
       for (int64_t tile = cluster_id; tile < total_tiles && alive; tile += num_clusters) {
-        int m_blk, n_tile_unused;
-        tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile_unused);
-        const int e = p.expert_ids[m_blk];
-        if (e < 0 || e >= p.num_experts) continue;
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         ++local;
@@ -223,9 +232,7 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
     const int row = warp * 32 + lane;
     for (int64_t tile = cluster_id; tile < total_tiles && alive; tile += num_clusters) {
       int m_blk, n_tile;
-      tile_to_mn(tile, used_blocks, p.n_tiles, p.group_m, &m_blk, &n_tile);
-      const int e = p.expert_ids[m_blk];
-      if (e < 0 || e >= p.num_experts) continue;
+      cursor.locate(tile, used_blocks, p.n_tiles, p.group_m, p.expert_ids, &m_blk, &n_tile);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ++local;
@@ -233,7 +240,7 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
       const int32_t slot = (pos < p.sorted_cap) ? p.sorted_token_ids[pos] : -1;
       const bool valid = slot >= 0 && slot < p.numel;
       const float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
-      if (!warp_wait(&acc_full[acc], acc_phase)) {
+      if (!warp_wait_relaxed(&acc_full[acc], acc_phase)) {
         report(0xB00 | acc);
         alive = false;
         break;
@@ -256,8 +263,8 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int i = v * 8 + j * 2;
-                float o0 = act_mul(__uint_as_float(g[i]) * rs, __uint_as_float(u[i]) * rs, p.activation);
-                float o1 = act_mul(__uint_as_float(g[i + 1]) * rs, __uint_as_float(u[i + 1]) * rs, p.activation);
+                float o0 = act_mul_fast(__uint_as_float(g[i]) * rs, __uint_as_float(u[i]) * rs, p.activation);
+                float o1 = act_mul_fast(__uint_as_float(g[i + 1]) * rs, __uint_as_float(u[i + 1]) * rs, p.activation);
                 w[j] = pack_bf16x2(o0, o1);
               }
               dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -314,9 +321,9 @@ int launch(const GemmParams& g, cudaStream_t st) {
     return fail(FMOE_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", SMEM_BYTES, cudaGetErrorString(attr_err));
   const int64_t w_rows = GATED ? 2 * g.n : g.n;
   CUtensorMap map_a, map_b;
-  int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 2, BM, false);
+  int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 2, BM, false, 128);
   if (rc) return rc;
-  rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 2, 128, true);
+  rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 2, 128, true, 128);
   if (rc) return rc;
   PairParams p;
   p.sorted_token_ids = g.sorted_token_ids;
@@ -337,7 +344,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
   const int64_t max_tiles = g.max_blocks * p.n_tiles;
   const int sms = device_sm_count();
   const int64_t pairs = std::max<int64_t>(1, std::min<int64_t>((sms > 0 ? sms : 148) / 2, max_tiles));
-  p.group_m = pick_group_m(g, PAIR_M, g.k * 2, p.n_tiles, (int)pairs);
+  p.group_m = pick_group_m(PAIR_M, g.k * 2);
   grouped_gemm_tcgen05_pair_kernel<GATED><<<(unsigned)(2 * pairs), kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_pair_kernel");
 }
@@ -353,6 +360,13 @@ bool gemm_tcgen05_pair_supports(const GemmParams& p, bool gated) {
   if ((int64_t)p.num_experts * (gated ? 2 * p.n : p.n) >= (1ll << 31) || p.a_rows >= (1ll << 31)) return false;
   if (p.max_blocks >= (1ll << 23)) return false;
   return true;
+}
+
+int status_word_pair(int* out, bool clear) {
+  int zero = 0;
+  FMOE_CUDA_OK(cudaMemcpyFromSymbol(out, g_device_status_pair, sizeof(int)));
+  if (clear && *out != 0) FMOE_CUDA_OK(cudaMemcpyToSymbol(g_device_status_pair, &zero, sizeof(int)));
+  return FMOE_OK;
 }
 
 int gemm_tcgen05_pair(const GemmParams& p, bool gated, cudaStream_t st) {

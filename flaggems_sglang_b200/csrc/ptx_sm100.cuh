@@ -50,6 +50,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   }
 }
 
+// Same, for waits that are expected to last long (an epilogue warp waiting for a whole main loop): sleeps
+// between polls so that the barrier word is not hammered while the MMA and TMA units use shared memory.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    __nanosleep(256);
+    if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > kWaitCycles) return false;
+  }
+}
+
 // 2-D tiled TMA load into this CTA's shared memory, completion on an mbarrier.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
                                             uint64_t* bar) {

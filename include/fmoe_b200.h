@@ -250,6 +250,14 @@ int fmoe_fused_experts_static(const fmoe_fused_args* args, void* stream);
  */
 int fmoe_check_device_status(void* stream);
 
+/*
+ * Diagnostic: with the environment variable FMOE_TC_PROFILE set, the bf16 tcgen05 kernel records, per
+ * CTA, clock cycles spent waiting {tiles, MMA on accumulator, MMA on data, producer on free stage,
+ * epilogue on accumulator, epilogue busy, -, -}.  Copies the last launch's n values (8 per CTA, at most
+ * 256 CTAs) to HOST memory.  No counterpart in the reference.
+ */
+int fmoe_debug_tcgen05_wait_profile(int64_t* host_out, int n);
+
 #ifdef __cplusplus
 }
 #endif

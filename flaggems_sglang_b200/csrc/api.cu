@@ -91,7 +91,15 @@ extern "C" int fmoe_gemm2(const fmoe_gemm_args* args, void* stream) {
   return fmoe::dispatch_gemm(args, false, stream, "gemm2");
 }
 
-namespace fmoe { int read_wait_profile(long long* host_out, int n); }
+namespace fmoe {
+int read_wait_profile(long long* host_out, int n);
+int launch_bounded_wait_selftest(long long limit_cycles, cudaStream_t st);
+}  // namespace fmoe
+
+extern "C" int fmoe_selftest_bounded_wait(int64_t limit_cycles, void* stream) {
+  if (limit_cycles < 1 || limit_cycles > 2000000000ll) return fmoe::fail(FMOE_ERR_INVALID_ARG, "selftest: limit out of range");
+  return fmoe::launch_bounded_wait_selftest(limit_cycles, (cudaStream_t)stream);
+}
 
 extern "C" int fmoe_debug_tcgen05_wait_profile(int64_t* host_out, int n) {
   if (!host_out || n < 0 || n > 256 * 8) return fmoe::fail(FMOE_ERR_INVALID_ARG, "wait profile: bad buffer");

@@ -230,8 +230,9 @@ int pick_ksplit(int64_t items, int64_t kblocks, int elem_bytes) {
     if (w == 1 || w == 2 || w == 4 || w == 8) return w;
   }
   // Measured on B200: with 2-byte elements a warp touches 256 contiguous bytes of a row per step and
-  // HBM streams best when the warps of a CTA walk one row range together (W = 8 gives 2 KB runs);
-  // with 1-byte elements the runs are short either way and fewer, longer-lived warps win.
+  // HBM streams best when the warps of a CTA walk one row range together (W = 8 gives 2 KB runs).
+  // With 1-byte elements W = 1 measured fastest at every size tried (also with 256-byte chunks), so only
+  // the work-item rule below raises it.
   int W = 1;
   if (elem_bytes == 2) W = kblocks >= 16 ? 8 : (kblocks >= 8 ? 4 : (kblocks >= 4 ? 2 : 1));
   const int64_t target = 148 * 16;

@@ -458,6 +458,24 @@ int gemm_tcgen05(const GemmParams& p, bool gated, cudaStream_t st) {
   return gated ? launch<true, 128>(p, st) : launch<false, 128>(p, st);
 }
 
+namespace {
+// Self-test of the time-out path: waits on a barrier that nobody signals, with a short limit.
+__global__ void bounded_wait_selftest_kernel(long long limit_cycles) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bar, 1);
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  if (!ptx::mbar_wait_limit(&bar, 0, limit_cycles) && threadIdx.x == 0) report(0xE00);
+}
+}  // namespace
+
+int launch_bounded_wait_selftest(long long limit_cycles, cudaStream_t st) {
+  bounded_wait_selftest_kernel<<<1, 32, 0, st>>>(limit_cycles);
+  return launch_status("bounded_wait_selftest_kernel");
+}
+
 int read_wait_profile(long long* host_out, int n) {
   FMOE_CUDA_OK(cudaMemcpyFromSymbol(host_out, g_wait_prof, sizeof(long long) * (size_t)n));
   return FMOE_OK;

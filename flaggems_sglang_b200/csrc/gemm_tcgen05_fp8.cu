@@ -83,7 +83,7 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&part_full[a], 1);
-      ptx::mbar_init(&part_empty[a], kEpiWarps * 32);
+      ptx::mbar_init(&part_empty[a], kEpiWarps);  // one arrival per fold warp
     }
     ptx::fence_barrier_init();
   }
@@ -249,7 +249,8 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
         const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          // 16 columns at a time keeps the staging registers small (64 accumulators stay live)
+          // 16 columns at a time keeps the staging registers small (64 accumulators stay live); two loads in
+          // flight per wait were measured no faster: the fold is bound by TMEM read-out, 128 KB per K block
           uint32_t v[16];
           ptx::tmem_ld_32x32b_x16(taddr + ((c < 2) ? col0 + 16 * c : col1 + 16 * (c - 2)), v);
           ptx::tmem_ld_wait();
@@ -257,8 +258,11 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
 #pragma unroll
           for (int i = 0; i < 16; ++i) acc[16 * c + i] = fmaf(__uint_as_float(v[i]), f, acc[16 * c + i]);
         }
+        // 512 separate arrivals on one barrier word would serialise for longer than the fold itself:
+        // the warp's lanes order their TMEM reads, then one lane arrives for all of them
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(&part_empty[buf]);
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&part_empty[buf]);
       }
       if (!alive) break;
 

@@ -41,13 +41,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait for the phase with the given parity.  Returns false on time-out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > kWaitCycles) return false;
+    if (clock64() - t0 > limit_cycles) return false;
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  return mbar_wait_limit(bar, parity, kWaitCycles);
 }
 
 // Same, for waits that are expected to last long (an epilogue warp waiting for a whole main loop): sleeps

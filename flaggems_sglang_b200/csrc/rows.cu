@@ -14,67 +14,67 @@ __device__ __forceinline__ int64_t mapped_row(const int32_t* row_map, int map_di
   return s / map_div;
 }
 
-// 16 lanes per (output row, 128-channel group): each lane owns 8 consecutive channels (one 16-byte load
-// of bf16, two of fp32) and writes 8 bytes; a thread keeps kIlp independent groups in flight.
+// One CTA walks output rows (grid-stride); inside a row, 16 lanes own one 128-channel group: each lane loads
+// 8 consecutive channels (16 bytes of bf16, 32 of fp32) and writes 8 bytes.  Up to kIlp groups per thread are
+// loaded before any is reduced, and no index arithmetic needs a division.
 template <typename InT>
 __global__ void __launch_bounds__(256)
 quant_group128_kernel(const InT* __restrict__ x, int64_t rows_out, int64_t K, const int32_t* __restrict__ row_map,
                       int map_div, int64_t sentinel, const int32_t* __restrict__ num_rows_dev,
                       uint8_t* __restrict__ q, float* __restrict__ scale) {
   constexpr int kIlp = 4;
-  const int sub = threadIdx.x & 15;  // lane inside the 16-lane group
-  const unsigned hmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;  // the two halves of a warp loop independently
-  const int64_t groups = K / 128;
+  const int sub = threadIdx.x & 15;       // lane inside the 16-lane group
+  const int grp0 = threadIdx.x >> 4;      // first group of this thread; the next ones are 16 apart
+  const unsigned hmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+  const int groups = (int)(K / 128);
   const int64_t limit = num_rows_dev ? min((int64_t)*num_rows_dev, rows_out) : rows_out;
-  const int64_t total = limit * groups;
-  const int64_t halfwarps = (int64_t)gridDim.x * (blockDim.x >> 4);
-  const int64_t hw = (int64_t)blockIdx.x * (blockDim.x >> 4) + (threadIdx.x >> 4);
-  for (int64_t base = hw; base < total; base += halfwarps * kIlp) {
-    float v[kIlp][8];
-    int64_t r[kIlp], p[kIlp], g[kIlp];
+  for (int64_t p = blockIdx.x; p < limit; p += gridDim.x) {
+    const int64_t r = mapped_row(row_map, map_div, sentinel, p);
+    const InT* src_row = x + (r >= 0 ? r : 0) * K;
+    for (int gbase = grp0; gbase < groups; gbase += 16 * kIlp) {
+      float v[kIlp][8];
 #pragma unroll
-    for (int u = 0; u < kIlp; ++u) {
-      const int64_t w = base + (int64_t)u * halfwarps;
-      p[u] = w < total ? w / groups : -1;
-      g[u] = w < total ? w % groups : 0;
-      r[u] = p[u] >= 0 ? mapped_row(row_map, map_div, sentinel, p[u]) : -1;
+      for (int u = 0; u < kIlp; ++u) {
+        const int g = gbase + 16 * u;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
-      if (r[u] >= 0) {
-        const InT* src = x + r[u] * K + g[u] * 128 + sub * 8;
-        if constexpr (sizeof(InT) == 4) {
-          float4 f0 = __ldg(reinterpret_cast<const float4*>(src));
-          float4 f1 = __ldg(reinterpret_cast<const float4*>(src) + 1);
-          v[u][0] = f0.x; v[u][1] = f0.y; v[u][2] = f0.z; v[u][3] = f0.w;
-          v[u][4] = f1.x; v[u][5] = f1.y; v[u][6] = f1.z; v[u][7] = f1.w;
-        } else {
-          uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
-          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
+        if (g < groups && r >= 0) {
+          const InT* src = src_row + g * 128 + sub * 8;
+          if constexpr (sizeof(InT) == 4) {
+            float4 f0 = __ldg(reinterpret_cast<const float4*>(src));
+            float4 f1 = __ldg(reinterpret_cast<const float4*>(src) + 1);
+            v[u][0] = f0.x; v[u][1] = f0.y; v[u][2] = f0.z; v[u][3] = f0.w;
+            v[u][4] = f1.x; v[u][5] = f1.y; v[u][6] = f1.z; v[u][7] = f1.w;
+          } else {
+            uint4 raw = __ldg(reinterpret_cast<const uint4*>(src));
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            v[u][2 * i] = __low2float(h[i]);
-            v[u][2 * i + 1] = __high2float(h[i]);
+            for (int i = 0; i < 4; ++i) {
+              v[u][2 * i] = __low2float(h[i]);
+              v[u][2 * i + 1] = __high2float(h[i]);
+            }
           }
         }
       }
-    }
 #pragma unroll
-    for (int u = 0; u < kIlp; ++u) {
-      float amax = 0.f;
+      for (int u = 0; u < kIlp; ++u) {
+        const int g = gbase + 16 * u;
+        float amax = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[u][i]));
+        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[u][i]));
 #pragma unroll
-      for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hmask, amax, off));
-      if (p[u] < 0) continue;  // this 16-lane group is past the end
-      const float s = (r[u] >= 0) ? __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f) : 1.0f;
-      uint32_t lo = 0, hi = 0;
+        for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hmask, amax, off));
+        if (g >= groups) continue;  // uniform over the 16 lanes of the group
+        const float s = (r >= 0) ? __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f) : 1.0f;
+        uint32_t lo = 0, hi = 0;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        lo |= (uint32_t)f32_to_e4m3_bits(__fdiv_rn(v[u][i], s)) << (8 * i);
-        hi |= (uint32_t)f32_to_e4m3_bits(__fdiv_rn(v[u][4 + i], s)) << (8 * i);
+        for (int i = 0; i < 4; ++i) {
+          lo |= (uint32_t)f32_to_e4m3_bits(__fdiv_rn(v[u][i], s)) << (8 * i);
+          hi |= (uint32_t)f32_to_e4m3_bits(__fdiv_rn(v[u][4 + i], s)) << (8 * i);
+        }
+        *reinterpret_cast<uint2*>(q + p * K + (int64_t)g * 128 + sub * 8) = make_uint2(lo, hi);
+        if (sub == 0) scale[p * groups + g] = s;
       }
-      *reinterpret_cast<uint2*>(q + p[u] * K + g[u] * 128 + sub * 8) = make_uint2(lo, hi);
-      if (sub == 0) scale[p[u] * groups + g[u]] = s;
     }
   }
 }
@@ -134,8 +134,7 @@ extern "C" int fmoe_quant_fp8_group128(const void* x, int in_dtype, int64_t rows
   if (rows_out <= 0) return FMOE_OK;
   FMOE_REQUIRE(x && q && scale, "quant_fp8_group128: null pointer");
   FMOE_REQUIRE(aligned16(x) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0, "quant_fp8_group128: misaligned pointer");
-  int64_t halfwarps = rows_out * (K / 128);
-  unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div<int64_t>(halfwarps, 16 * 4), 148 * 8));
+  unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(rows_out, 148 * 8));
   auto st = (cudaStream_t)stream;
   if (in_dtype == FMOE_BF16)
     quant_group128_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, rows_out, K, row_map, map_div,

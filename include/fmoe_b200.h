@@ -251,6 +251,14 @@ int fmoe_fused_experts_static(const fmoe_fused_args* args, void* stream);
 int fmoe_check_device_status(void* stream);
 
 /*
+ * Self-test of the time-out reporting: launches a one-warp kernel that waits, for at most `limit_cycles`
+ * clock cycles, on a barrier nobody signals; it gives up, records a status code and returns, so the next
+ * fmoe_check_device_status returns FMOE_ERR_DEVICE_TIMEOUT and the context stays usable.  No counterpart in
+ * the reference (it has no device-side waits).
+ */
+int fmoe_selftest_bounded_wait(int64_t limit_cycles, void* stream);
+
+/*
  * Diagnostic: with the environment variable FMOE_TC_PROFILE set, the bf16 tcgen05 kernel records, per
  * CTA, clock cycles spent waiting {tiles, MMA on accumulator, MMA on data, producer on free stage,
  * epilogue on accumulator, epilogue busy, -, -}.  Copies the last launch's n values (8 per CTA, at most

@@ -169,6 +169,23 @@ def test_gelu_activation(fg, variant):
         _run(fg, x, w1, w2, tw, ti, activation="relu")
 
 
+def test_bounded_wait_reports_and_context_survives(fg):
+    """A wait that can never be satisfied gives up after its cycle limit, the status word reports it, and
+    the same context keeps computing (no trap, no hang)."""
+    from flaggems_sglang_b200 import _C
+
+    lib = _C.lib()
+    _C.check(lib.fmoe_selftest_bounded_wait(2_000_000, _C.stream_ptr()))  # ~1 ms
+    with pytest.raises(_C.FmoeError) as ei:
+        _C.check_device_status()
+    assert ei.value.code == _C.ERR_DEVICE_TIMEOUT and "0xe00" in str(ei.value)
+    _C.check_device_status()  # cleared by the read above
+    x, w1, w2, logits = _layer(9, 128, 128, 4, 2, torch.bfloat16, 3)
+    tw, ti = OR.softmax_topk(logits, 2, True)
+    out = _run(fg, x, w1, w2, tw, ti, variant="tcgen05")
+    assert_close_moe(out, OE.fused_experts(x, w1, w2, tw, ti), "bf16", "after time-out")
+
+
 def test_empty_batch(fg):
     x, w1, w2, logits = _layer(4, 128, 128, 4, 2, torch.bfloat16, 1)
     out = fg.fused_experts(x[:0].cuda(), w1.cuda(), w2.cuda(), torch.zeros(0, 2).cuda(),

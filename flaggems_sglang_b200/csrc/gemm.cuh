@@ -38,13 +38,26 @@ struct TileCursor {
     const int q = (int)(tile / n_tiles);
     if (q < first || q >= last) {
       const int e = expert_ids[q];
-      int lo = 0, hi = q;  // first index with expert_ids[i] >= e
+      // tiles only move forward, so the new expert starts at or after the cached range's end
+      int lo = (q >= last) ? last : 0, hi = q;  // first index in [lo, q] with expert_ids[i] >= e
       while (lo < hi) {
         const int mid = (lo + hi) >> 1;
         if (expert_ids[mid] < e) lo = mid + 1; else hi = mid;
       }
       first = lo;
-      lo = q + 1, hi = used_blocks;  // first index past q with expert_ids[i] != e
+      // first index past q whose expert differs: gallop, then bisect the last interval
+      int step = 1, known = q;  // expert_ids[known] == e
+      hi = used_blocks;
+      while (known + step < used_blocks) {
+        if (expert_ids[known + step] == e) {
+          known += step;
+          step <<= 1;
+        } else {
+          hi = known + step;
+          break;
+        }
+      }
+      lo = known + 1;
       while (lo < hi) {
         const int mid = (lo + hi) >> 1;
         if (expert_ids[mid] == e) lo = mid + 1; else hi = mid;

@@ -81,6 +81,29 @@ class CudaBackend:
         return moe_sum(z, out, scale)
 
 
+# Optional phase timing for benchmarks: set to a list and every ep_fused_experts call on CUDA tensors appends
+# (phase name, start event, end event) recorded on the current stream.
+PHASE_EVENTS: Optional[list] = None
+
+
+class _phase:
+    def __init__(self, name: str, enabled: bool):
+        self.name, self.enabled = name, enabled and PHASE_EVENTS is not None
+
+    def __enter__(self):
+        if self.enabled:
+            self.t0 = torch.cuda.Event(enable_timing=True)
+            self.t0.record()
+        return self
+
+    def __exit__(self, *exc):
+        if self.enabled:
+            t1 = torch.cuda.Event(enable_timing=True)
+            t1.record()
+            PHASE_EVENTS.append((self.name, self.t0, t1))
+        return False
+
+
 def _all_to_all_rows(send: torch.Tensor, plan: DispatchPlan, group, reverse: bool = False) -> torch.Tensor:
     s, r = (plan.recv_counts, plan.send_counts) if reverse else (plan.send_counts, plan.recv_counts)
     out = send.new_empty((int(sum(r)),) + tuple(send.shape[1:]))
@@ -112,35 +135,41 @@ def ep_fused_experts(
         raise ValueError(f"this rank holds {w1_local.shape[0]} experts, expected {e_local}")
     T, H = hidden_states.shape
     k = topk_ids.shape[1]
-    ids = topk_ids.to(torch.int32).reshape(-1)
-    dest = torch.div(ids, e_local, rounding_mode="floor").to(torch.int32)
-    perm, counts = backend.sort_by_rank(dest, world)
-
-    # count exchange: one [N,N] matrix, one host read per layer call
-    matrix = torch.empty(world * world, dtype=counts.dtype, device=counts.device)
-    dist.all_gather_into_tensor(matrix, counts.contiguous(), group=group)
-    plan = plan_from_count_matrix(matrix.view(world, world).cpu(), rank)
+    timed = hidden_states.is_cuda
+    with _phase("plan", timed):
+        ids = topk_ids.to(torch.int32).reshape(-1)
+        dest = torch.div(ids, e_local, rounding_mode="floor").to(torch.int32)
+        perm, counts = backend.sort_by_rank(dest, world)
+        # count exchange: one [N,N] matrix, one host read per layer call
+        matrix = torch.empty(world * world, dtype=counts.dtype, device=counts.device)
+        dist.all_gather_into_tensor(matrix, counts.contiguous(), group=group)
+        plan = plan_from_count_matrix(matrix.view(world, world).cpu(), rank)
     if sum(plan.send_counts) != T * k:
         raise RuntimeError("dispatch counts do not add up to T*k (expert id out of range?)")
 
-    lperm = perm.long()
-    send_rows = backend.gather_rows(hidden_states.contiguous(), perm, k)
-    meta = torch.stack(((ids - dest * e_local)[lperm].to(torch.int32),
-                        topk_weights.reshape(-1).float()[lperm].view(torch.int32)), dim=1)
-    recv_rows = _all_to_all_rows(send_rows, plan, group)
-    recv_meta = _all_to_all_rows(meta, plan, group)
+    with _phase("pack", timed):
+        lperm = perm.long()
+        send_rows = backend.gather_rows(hidden_states.contiguous(), perm, k)
+        meta = torch.stack(((ids - dest * e_local)[lperm].to(torch.int32),
+                            topk_weights.reshape(-1).float()[lperm].view(torch.int32)), dim=1)
+    with _phase("dispatch", timed):
+        recv_rows = _all_to_all_rows(send_rows, plan, group)
+        recv_meta = _all_to_all_rows(meta, plan, group)
 
-    local_ids = recv_meta[:, 0].contiguous()
-    local_w = recv_meta[:, 1].contiguous().view(torch.float32)
-    if plan.total_recv > 0:
-        z_recv = backend.local_experts(recv_rows, w1_local, w2_local, local_w, local_ids, **expert_kwargs)
-    else:
-        z_recv = recv_rows.new_empty((0, H))
-    back = _all_to_all_rows(z_recv, plan, group, reverse=True)
-
-    z = torch.empty(T * k, H, dtype=back.dtype, device=back.device)
-    z.index_copy_(0, lperm, back)
-    return backend.combine(z.view(T, k, H), routed_scaling_factor)
+    with _phase("experts", timed):
+        local_ids = recv_meta[:, 0].contiguous()
+        local_w = recv_meta[:, 1].contiguous().view(torch.float32)
+        if plan.total_recv > 0:
+            z_recv = backend.local_experts(recv_rows, w1_local, w2_local, local_w, local_ids, **expert_kwargs)
+        else:
+            z_recv = recv_rows.new_empty((0, H))
+    with _phase("combine_a2a", timed):
+        back = _all_to_all_rows(z_recv, plan, group, reverse=True)
+    with _phase("unpermute_sum", timed):
+        z = torch.empty(T * k, H, dtype=back.dtype, device=back.device)
+        z.index_copy_(0, lperm, back)
+        out = backend.combine(z.view(T, k, H), routed_scaling_factor)
+    return out
 
 
 def ep_fused_moe(hidden_states, w1_local, w2_local, gating_output, topk: int, num_global_experts: int,

@@ -1,0 +1,91 @@
+"""Property tests of the oracle's routing stages (CPU, hypothesis): invariants that hold for every input."""
+import numpy as np
+import torch
+from hypothesis import given, settings, strategies as st
+
+from oracle import routing as OR
+
+
+@settings(max_examples=60, deadline=None)
+@given(T=st.integers(0, 70), k=st.integers(1, 4), E=st.integers(1, 40), block=st.sampled_from([1, 4, 16, 32, 64, 128]),
+       seed=st.integers(0, 10_000), hot=st.booleans())
+def test_align_invariants(T, k, E, block, seed, hot):
+    rng = np.random.default_rng(seed)
+    ids = rng.integers(0, E, size=(T, k)).astype(np.int32)
+    if hot and T:
+        ids[: T // 2] = ids[0, 0]  # a hot expert, many empty ones
+    ids[rng.random((T, k)) < 0.05] = -1  # dropped slots
+    n = ids.size
+    s, e, npp = OR.moe_align_block_size(ids, block, E)
+    total = int(npp[0])
+    assert s.shape[0] == n + E * (block - 1) and total % block == 0 and total <= s.shape[0]
+    used = s[:total]
+    real = used[used < n]
+    flat = ids.reshape(-1)
+    assert sorted(real.tolist()) == np.nonzero((flat >= 0) & (flat < E))[0].tolist()  # every kept slot exactly once
+    assert (s[total:] == n).all() and (e[total // block:] == -1).all()
+    for b in range(total // block):
+        blk = used[b * block:(b + 1) * block]
+        valid = blk[blk < n]
+        assert valid.size >= 1 and (flat[valid] == e[b]).all()       # one expert per block, no empty block
+        assert (np.diff(valid) > 0).all()                             # ascending slots
+        assert (blk[valid.size:] == n).all()                          # padding only at the end of the block
+    assert (np.diff(e[: total // block]) >= 0).all()                  # experts ascending
+
+
+@settings(max_examples=60, deadline=None)
+@given(T=st.integers(1, 40), E=st.integers(2, 64), seed=st.integers(0, 10_000), ties=st.booleans())
+def test_softmax_topk_invariants(T, E, seed, ties):
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(T, E, generator=g)
+    if ties:
+        logits = (logits * 2).round() / 2
+    k = min(4, E)
+    w, ids = OR.softmax_topk(logits, k, True)
+    assert torch.allclose(w.sum(-1), torch.ones(T), atol=1e-5)
+    assert (w[:, :-1] >= w[:, 1:] - 1e-7).all()
+    for t in range(T):
+        row = logits[t]
+        chosen = ids[t].tolist()
+        assert len(set(chosen)) == k
+        worst = min(row[c].item() for c in chosen)
+        rest = [row[i].item() for i in range(E) if i not in chosen]
+        assert not rest or max(rest) <= worst
+        # among equal logits the lower index is taken first
+        for a, b in zip(chosen, chosen[1:]):
+            assert row[a] > row[b] or (row[a] == row[b] and a < b)
+
+
+@settings(max_examples=40, deadline=None)
+@given(T=st.integers(1, 30), seed=st.integers(0, 10_000), ng=st.sampled_from([1, 2, 4, 8]), tg=st.integers(1, 8))
+def test_grouped_topk_invariants(T, seed, ng, tg):
+    E, k = 64, 4
+    tg = min(tg, ng)
+    if tg * (E // ng) < k:
+        tg = ng
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(T, E, generator=g)
+    bias = torch.randn(E, generator=g) * 0.1
+    w, ids = OR.grouped_topk(logits, bias, k, ng, tg, True, 2.5)
+    assert torch.allclose(w.sum(-1), torch.full((T,), 2.5), atol=1e-4)
+    groups = ids // (E // ng)
+    assert all(len(set(r.tolist())) <= tg for r in groups)
+    assert all(len(set(r.tolist())) == k for r in ids)
+
+
+@settings(max_examples=30, deadline=None)
+@given(T=st.integers(1, 50), k=st.integers(1, 4), E=st.integers(4, 32), seed=st.integers(0, 10_000))
+def test_reference_routing_tables_are_inverse_permutations(T, k, E, seed):
+    g = torch.Generator().manual_seed(seed)
+    k = min(k, E)
+    logits = torch.randn(T, E, generator=g)
+    w, ids = OR.softmax_topk(logits, k, True)
+    r = OR.standard_topk_to_routing(w, ids, E)
+    M = T * k
+    assert sorted(r["topk_indx"].tolist()) == list(range(M))
+    assert (r["gate_indx"][r["topk_indx"]] == np.arange(M)).all()
+    assert r["hist"].sum() == M and r["token_offs_raw"][-1] == M
+    for bm in OR.BLOCK_MS:
+        pm = r["block_pid_map"][bm]
+        tiles = int(r["token_offs_pad"][bm][-1])
+        assert (pm[:tiles] >= 0).all() and (pm[tiles:] == -1).all()

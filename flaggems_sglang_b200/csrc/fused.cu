@@ -48,6 +48,16 @@ int pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forc
 
 namespace {
 inline int64_t up256(int64_t v) { return (v + 255) & ~int64_t(255); }
+
+// The single-CTA bf16 tcgen05 gate/up kernel can fetch its input rows by TMA gather4 instead of reading a
+// sorted copy of the hidden states.  Measured on B200 the gather costs more than the copy saves (32 four-row
+// TMA instructions per 16 KB stage against one tiled load: gate/up 4.07 ms against 1.67 ms at Mixtral
+// T=4096, 1.03 against 0.39 ms at Qwen3 T=8192), so the copy is the default and FMOE_TC_GATHER4=1 selects
+// the gather (it saves the cap x H workspace).
+inline bool tc_gathers_input(int variant, int dtype) {
+  static const bool gather4 = getenv("FMOE_TC_GATHER4") != nullptr;
+  return variant == FMOE_VARIANT_TCGEN05 && dtype == FMOE_BF16 && gather4;
+}
 }
 
 int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
@@ -79,17 +89,21 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
   p.off_npp = take(16);
   p.align_ws_bytes = fmoe_moe_align_workspace_bytes(p.numel, a.num_experts);
   p.off_align_ws = take(p.align_ws_bytes);
-  p.off_xs = p.off_xs_scale = p.off_actq = p.off_actq_scale = -1;
+  p.off_xs = p.off_xs_scale = p.off_xt = p.off_xt_scale = p.off_actq = p.off_actq_scale = -1;
   if (fp8) {
     const int64_t xrows = tc ? p.cap : a.T;
     p.off_xs = take(xrows * a.H);
     p.off_xs_scale = take(xrows * (a.H / 128) * 4);
+    if (tc && fp8_quant_once(a.top_k, a.H)) {
+      p.off_xt = take(a.T * a.H);
+      p.off_xt_scale = take(a.T * (a.H / 128) * 4);
+    }
     p.act_elem = tc ? 2 : 4;  // bf16 from the tcgen05 epilogue, fp32 from the streaming kernel
     p.off_act = take(p.cap * a.I * p.act_elem);
     p.off_actq = take(p.cap * a.I);
     p.off_actq_scale = take(p.cap * (a.I / 128) * 4);
   } else {
-    if (tc) p.off_xs = take(p.cap * a.H * eb);
+    if (tc && !tc_gathers_input(p.variant, a.dtype)) p.off_xs = take(p.cap * a.H * eb);
     p.act_elem = (int)eb;
     p.off_act = take(p.cap * a.I * eb);
   }
@@ -148,7 +162,7 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
 
   if (!fp8) {
     g1.dtype = g1.out_dtype = g2.dtype = a.dtype;
-    if (tc) {
+    if (tc && !tc_gathers_input(p.variant, a.dtype)) {
       void* xs = ws + p.off_xs;
       rc = fmoe_gather_rows(a.hidden, (int)eb, p.cap, a.H, sorted, a.top_k, p.numel, npp, xs, stream);
       if (rc) return rc;
@@ -164,7 +178,15 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
   } else {
     void* xq = ws + p.off_xs;
     float* xsc = reinterpret_cast<float*>(ws + p.off_xs_scale);
-    if (tc)
+    if (tc && p.off_xt >= 0) {
+      void* xt = ws + p.off_xt;
+      float* xtsc = reinterpret_cast<float*>(ws + p.off_xt_scale);
+      rc = fmoe_quant_fp8_group128(a.hidden, FMOE_BF16, a.T, a.H, nullptr, 1, 0, nullptr, xt, xtsc, stream);
+      if (rc) return rc;
+      rc = fmoe_gather_rows(xt, 1, p.cap, a.H, sorted, a.top_k, p.numel, npp, xq, stream);
+      if (rc) return rc;
+      rc = fmoe_gather_rows(xtsc, 4, p.cap, a.H / 128, sorted, a.top_k, p.numel, npp, xsc, stream);
+    } else if (tc)
       rc = fmoe_quant_fp8_group128(a.hidden, FMOE_BF16, p.cap, a.H, sorted, a.top_k, p.numel, npp, xq, xsc, stream);
     else
       rc = fmoe_quant_fp8_group128(a.hidden, FMOE_BF16, a.T, a.H, nullptr, 1, 0, nullptr, xq, xsc, stream);
@@ -183,7 +205,8 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
   rc = fmoe_gemm1_silu(&g1, stream);
   if (rc) return rc;
   if (fp8) {
-    rc = fmoe_quant_fp8_group128(act, g1.out_dtype, p.cap, a.I, nullptr, 1, 0, npp, ws + p.off_actq,
+    // padding positions of the sorted order (most of the rows at small T) are zero-filled, not quantised
+    rc = fmoe_quant_fp8_group128(act, g1.out_dtype, p.cap, a.I, sorted, 0, p.numel, npp, ws + p.off_actq,
                                  reinterpret_cast<float*>(ws + p.off_actq_scale), stream);
     if (rc) return rc;
   }

@@ -66,6 +66,8 @@ struct TcParams {
   int32_t activation;
   int32_t group_m;
   int32_t profile;
+  int32_t top_k;       // gather mode: input row of slot s is s / top_k
+  int32_t a_rows;      // gather mode: rows of the input tensor (a row index >= a_rows reads zeros)
 };
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_device_status, 0, code); }
@@ -80,7 +82,10 @@ __device__ __forceinline__ bool warp_wait_relaxed(uint64_t* bar, uint32_t parity
   return __all_sync(0xffffffffu, ptx::mbar_wait_relaxed(bar, parity));
 }
 
-template <bool GATED, int KB>
+// GATHER: the A operand is the un-permuted [a_rows, K] input; the producer warp fetches row
+// sorted_token_ids[p] / top_k for sorted position p with TMA gather4 (32 lanes x 4 rows = one 128-row stage),
+// padding positions read row a_rows, which is outside the tensor and arrives as zeros.
+template <bool GATED, int KB, bool GATHER>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                             const TcParams p) {
@@ -141,8 +146,18 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       *row_b0 = (int32_t)((int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256));
       *row_b1 = GATED ? (int32_t)(*row_b0 + p.n) : *row_b0 + 128;
     };
+    // gather mode: the four input rows this lane fetches for sorted positions row_a + 4*lane .. +3
+    auto lane_rows = [&](int32_t row_a) {
+      int4 s = *reinterpret_cast<const int4*>(p.sorted_token_ids + row_a + 4 * lane);
+      auto src = [&](int32_t slot) { return (slot >= 0 && slot < p.numel) ? slot / p.top_k : p.a_rows; };
+      return make_int4(src(s.x), src(s.y), src(s.z), src(s.w));
+    };
     int32_t row_a = 0, row_b0 = 0, row_b1 = 0, nrow_a = 0, nrow_b0 = 0, nrow_b1 = 0;
-    if ((int64_t)blockIdx.x < total_tiles) tile_rows(blockIdx.x, &row_a, &row_b0, &row_b1);
+    int4 src_rows = make_int4(0, 0, 0, 0), nsrc_rows = src_rows;
+    if ((int64_t)blockIdx.x < total_tiles) {
+      tile_rows(blockIdx.x, &row_a, &row_b0, &row_b1);
+      if constexpr (GATHER) src_rows = lane_rows(row_a);
+    }
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
       const bool has_next = tile + gridDim.x < total_tiles;
       for (int ks = 0; ks < k_steps; ++ks) {
@@ -159,12 +174,20 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           uint8_t* sb = sa + A_BYTES;
           ptx::mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
           const int32_t x = ks * (KBYTES / 2);  // element coordinate (bf16)
-          ptx::tma_load_2d(sa, &map_a, x, row_a, &full_bar[stage]);
+          if constexpr (!GATHER) ptx::tma_load_2d(sa, &map_a, x, row_a, &full_bar[stage]);
           ptx::tma_load_2d(sb, &map_b, x, row_b0, &full_bar[stage]);
           ptx::tma_load_2d(sb + B_BYTES / 2, &map_b, x, row_b1, &full_bar[stage]);
         }
         __syncwarp();
-        if (ks == 0 && has_next) tile_rows(tile + gridDim.x, &nrow_a, &nrow_b0, &nrow_b1);
+        if constexpr (GATHER) {
+          // after lane 0 armed the barrier: every lane brings its 4 rows (4 x 128 B) of the stage
+          ptx::tma_gather4_2d(smem + stage * STAGE_BYTES + lane * (4 * KBYTES), &map_a, ks * (KBYTES / 2), src_rows.x,
+                              src_rows.y, src_rows.z, src_rows.w, &full_bar[stage]);
+        }
+        if (ks == 0 && has_next) {
+          tile_rows(tile + gridDim.x, &nrow_a, &nrow_b0, &nrow_b1);
+          if constexpr (GATHER) nsrc_rows = lane_rows(nrow_a);
+        }
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1;
@@ -173,6 +196,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       row_a = nrow_a;
       row_b0 = nrow_b0;
       row_b1 = nrow_b1;
+      src_rows = nsrc_rows;
     }
     if (p.profile && lane == 0 && blockIdx.x < 256) g_wait_prof[blockIdx.x * 8 + 3] = prof_a;
     // drain: do not leave while our own bulk copies may still be landing in shared memory
@@ -391,14 +415,14 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t
 
 namespace {
 
-template <bool GATED, int KB>
+template <bool GATED, int KB, bool GATHER>
 int launch(const GemmParams& g, cudaStream_t st) {
   constexpr int SMEM_BYTES = Ring<KB>::SMEM_BYTES, KBYTES = KB;
   const int sm_count = device_sm_count();
   static cudaError_t attr_err = cudaSuccess;
   static std::once_flag once_attr;
   std::call_once(once_attr, [] {
-    attr_err = cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err = cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED, KB, GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     SMEM_BYTES);
   });
   if (attr_err != cudaSuccess)
@@ -406,7 +430,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
 
   const int64_t w_rows = GATED ? 2 * g.n : g.n;
   CUtensorMap map_a, map_b;
-  int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 2, BM, false, KB);
+  int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 2, GATHER ? 1 : BM, false, KB);
   if (rc) return rc;
   rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 2, 128, true, KB);
   if (rc) return rc;
@@ -426,12 +450,14 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.n_tiles = (int)ceil_div<int64_t>(g.n, GATED ? 128 : 256);
   p.max_blocks = (int)g.max_blocks;
   p.activation = g.activation;
+  p.top_k = g.top_k;
+  p.a_rows = (int32_t)g.a_rows;
 
   const int64_t max_tiles = g.max_blocks * p.n_tiles;
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sm_count > 0 ? sm_count : 148, max_tiles));
   p.group_m = pick_group_m(BM, g.k * 2);
   p.profile = getenv("FMOE_TC_PROFILE") != nullptr;
-  grouped_gemm_tcgen05_kernel<GATED, KB><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
+  grouped_gemm_tcgen05_kernel<GATED, KB, GATHER><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_kernel");
 }
 
@@ -439,7 +465,9 @@ int launch(const GemmParams& g, cudaStream_t st) {
 
 bool gemm_tcgen05_supports(const GemmParams& p, bool gated) {
   if (p.dtype != FMOE_BF16 || p.out_dtype != FMOE_BF16) return false;
-  if (p.block_size != BM || p.a_gather) return false;
+  if (p.block_size != BM) return false;
+  // gather mode: gate/up GEMM only; one int4 of sorted ids per lane
+  if (p.a_gather && (!gated || p.top_k < 1 || !aligned16(p.sorted_token_ids))) return false;
   if (p.k <= 0 || (p.k * 2) % 16 != 0) return false;            // TMA row stride must be a multiple of 16 bytes
   if (p.n <= 0 || p.n % (gated ? 128 : 32) != 0) return false;  // gate/up pairing; 64-byte epilogue stores
   if (!aligned16(p.a) || !aligned16(p.w) || !aligned16(p.out)) return false;
@@ -451,11 +479,12 @@ bool gemm_tcgen05_supports(const GemmParams& p, bool gated) {
 int gemm_tcgen05(const GemmParams& p, bool gated, cudaStream_t st) {
   if (!gemm_tcgen05_supports(p, gated))
     return fail(FMOE_ERR_UNSUPPORTED,
-                "tcgen05 gemm: needs bf16 in/out, block_size 128, input rows already in sorted order, "
+                "tcgen05 gemm: needs bf16 in/out, block_size 128, input-row gather only for the gate/up gemm, "
                 "n %% %d == 0, 16-byte aligned pointers (got dtype=%d block=%d a_gather=%d n=%lld k=%lld)",
                 gated ? 128 : 32, p.dtype, p.block_size, p.a_gather, (long long)p.n, (long long)p.k);
   if (p.max_blocks <= 0) return FMOE_OK;
-  return gated ? launch<true, 128>(p, st) : launch<false, 128>(p, st);
+  if (p.a_gather) return launch<true, 128, true>(p, st);
+  return gated ? launch<true, 128, false>(p, st) : launch<false, 128, false>(p, st);
 }
 
 namespace {

@@ -73,6 +73,18 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// TMA gather: four rows (y0..y3, any order, repeats allowed) of a 2-D tensor whose map has a one-row box
+// land as four consecutive box rows at smem_dst; a row index outside the tensor reads the fill value.
+// Completion credits 4 x the box bytes to the mbarrier.
+__device__ __forceinline__ void tma_gather4_2d(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y0, int32_t y1,
+                                               int32_t y2, int32_t y3, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y0), "r"(y1),
+      "r"(y2), "r"(y3)
+      : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

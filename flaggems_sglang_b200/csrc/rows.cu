@@ -7,39 +7,63 @@
 namespace fmoe {
 namespace {
 
+// Source row of output position p: p itself without a map; with a map, the map's entry divided by map_div,
+// or p when map_div is 0 (the map then only marks padding).  -1 = padding position.
 __device__ __forceinline__ int64_t mapped_row(const int32_t* row_map, int map_div, int64_t sentinel, int64_t p) {
   if (!row_map) return p;
   int32_t s = row_map[p];
   if (s < 0 || (int64_t)s >= sentinel) return -1;
-  return s / map_div;
+  return map_div ? s / map_div : p;
 }
 
-// One CTA walks output rows (grid-stride); inside a row, 16 lanes own one 128-channel group: each lane loads
-// 8 consecutive channels (16 bytes of bf16, 32 of fp32) and writes 8 bytes.  Up to kIlp groups per thread are
-// loaded before any is reduced, and no index arithmetic needs a division.
+// RN(v / s) for many v and one s: with r = RN(1/s), two residual corrections of v*r give the correctly rounded
+// quotient (Markstein), the same bits as an IEEE division, in 5 instructions per element.  The caller falls back to
+// __fdiv_rn when the group holds an infinity (the residual would be inf - inf).
+__device__ __forceinline__ float div_by_shared(float v, float s, float r) {
+  float q = v * r;
+  q = fmaf(fmaf(-q, s, v), r, q);
+  q = fmaf(fmaf(-q, s, v), r, q);
+  return q;
+}
+
+// The work is the flat list of (output row, 128-channel group) items; 16 lanes own one item: each lane loads
+// 8 consecutive channels (16 bytes of bf16, 32 of fp32) and writes 8 bytes.  A 16-lane team walks the list with
+// the grid's team count as stride and loads kIlp items before it reduces any, so that short rows (few groups)
+// keep as many loads in flight as long ones.  Row and group of an item advance by a fixed step: no division
+// inside the loop.
 template <typename InT>
 __global__ void __launch_bounds__(256)
 quant_group128_kernel(const InT* __restrict__ x, int64_t rows_out, int64_t K, const int32_t* __restrict__ row_map,
                       int map_div, int64_t sentinel, const int32_t* __restrict__ num_rows_dev,
                       uint8_t* __restrict__ q, float* __restrict__ scale) {
   constexpr int kIlp = 4;
-  const int sub = threadIdx.x & 15;       // lane inside the 16-lane group
-  const int grp0 = threadIdx.x >> 4;      // first group of this thread; the next ones are 16 apart
+  const int sub = threadIdx.x & 15;  // lane inside the 16-lane team
   const unsigned hmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
   const int groups = (int)(K / 128);
   const int64_t limit = num_rows_dev ? min((int64_t)*num_rows_dev, rows_out) : rows_out;
-  for (int64_t p = blockIdx.x; p < limit; p += gridDim.x) {
-    const int64_t r = mapped_row(row_map, map_div, sentinel, p);
-    const InT* src_row = x + (r >= 0 ? r : 0) * K;
-    for (int gbase = grp0; gbase < groups; gbase += 16 * kIlp) {
-      float v[kIlp][8];
+  const int64_t teams = (int64_t)gridDim.x * 16;
+  const int64_t team = (int64_t)blockIdx.x * 16 + (threadIdx.x >> 4);
+  const int64_t step_p = teams / groups;
+  const int step_g = (int)(teams % groups);
+  int64_t p = team / groups;  // item of this team: (row p, group g); the next one is `teams` items further
+  int g = (int)(team % groups);
+  while (p < limit) {
+    float v[kIlp][8];
+    int64_t pu[kIlp];
+    int gu[kIlp];
+    bool real[kIlp];
 #pragma unroll
-      for (int u = 0; u < kIlp; ++u) {
-        const int g = gbase + 16 * u;
+    for (int u = 0; u < kIlp; ++u) {
+      pu[u] = p;
+      gu[u] = g;
+      real[u] = false;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
-        if (g < groups && r >= 0) {
-          const InT* src = src_row + g * 128 + sub * 8;
+      for (int i = 0; i < 8; ++i) v[u][i] = 0.f;
+      if (p < limit) {
+        const int64_t r = mapped_row(row_map, map_div, sentinel, p);
+        real[u] = r >= 0;
+        if (r >= 0) {
+          const InT* src = x + r * K + g * 128 + sub * 8;
           if constexpr (sizeof(InT) == 4) {
             float4 f0 = __ldg(reinterpret_cast<const float4*>(src));
             float4 f1 = __ldg(reinterpret_cast<const float4*>(src) + 1);
@@ -56,25 +80,45 @@ quant_group128_kernel(const InT* __restrict__ x, int64_t rows_out, int64_t K, co
           }
         }
       }
+      p += step_p;
+      g += step_g;
+      if (g >= groups) {
+        g -= groups;
+        ++p;
+      }
+    }
 #pragma unroll
-      for (int u = 0; u < kIlp; ++u) {
-        const int g = gbase + 16 * u;
-        float amax = 0.f;
+    for (int u = 0; u < kIlp; ++u) {
+      float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[u][i]));
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[u][i]));
 #pragma unroll
-        for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hmask, amax, off));
-        if (g >= groups) continue;  // uniform over the 16 lanes of the group
-        const float s = (r >= 0) ? __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f) : 1.0f;
-        uint32_t lo = 0, hi = 0;
+      for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(hmask, amax, off));
+      if (pu[u] >= limit) continue;  // uniform over the 16 lanes of the team
+      uint2* dst = reinterpret_cast<uint2*>(q + pu[u] * K + (int64_t)gu[u] * 128 + sub * 8);
+      if (!real[u]) {  // padding position: zeros with a unit scale
+        *dst = make_uint2(0, 0);
+        if (sub == 0) scale[pu[u] * groups + gu[u]] = 1.0f;
+        continue;
+      }
+      const float s = __fdiv_rn(fmaxf(amax, 1e-10f), 448.0f);
+      uint32_t lo = 0, hi = 0;
+      if (amax <= 3.0e38f) {
+        const float r = __frcp_rn(s);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          lo |= (uint32_t)f32_to_e4m3_bits(div_by_shared(v[u][i], s, r)) << (8 * i);
+          hi |= (uint32_t)f32_to_e4m3_bits(div_by_shared(v[u][4 + i], s, r)) << (8 * i);
+        }
+      } else {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           lo |= (uint32_t)f32_to_e4m3_bits(__fdiv_rn(v[u][i], s)) << (8 * i);
           hi |= (uint32_t)f32_to_e4m3_bits(__fdiv_rn(v[u][4 + i], s)) << (8 * i);
         }
-        *reinterpret_cast<uint2*>(q + p * K + (int64_t)g * 128 + sub * 8) = make_uint2(lo, hi);
-        if (sub == 0) scale[p * groups + g] = s;
       }
+      *dst = make_uint2(lo, hi);
+      if (sub == 0) scale[pu[u] * groups + gu[u]] = s;
     }
   }
 }
@@ -130,11 +174,12 @@ extern "C" int fmoe_quant_fp8_group128(const void* x, int in_dtype, int64_t rows
   using namespace fmoe;
   FMOE_REQUIRE(K > 0 && K % 128 == 0, "quant_fp8_group128: K must be a positive multiple of 128 (got %lld)", (long long)K);
   FMOE_REQUIRE(in_dtype == FMOE_BF16 || in_dtype == FMOE_F32, "quant_fp8_group128: in_dtype must be bf16 or f32");
-  FMOE_REQUIRE(!row_map || map_div >= 1, "quant_fp8_group128: map_div must be >= 1");
+  FMOE_REQUIRE(!row_map || map_div >= 0, "quant_fp8_group128: map_div must be >= 0");
   if (rows_out <= 0) return FMOE_OK;
   FMOE_REQUIRE(x && q && scale, "quant_fp8_group128: null pointer");
   FMOE_REQUIRE(aligned16(x) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0, "quant_fp8_group128: misaligned pointer");
-  unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(rows_out, 148 * 8));
+  // 16 teams per CTA, 4 items per team and pass
+  unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div<int64_t>(rows_out * (K / 128), 64), 148 * 8));
   auto st = (cudaStream_t)stream;
   if (in_dtype == FMOE_BF16)
     quant_group128_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, rows_out, K, row_map, map_div,

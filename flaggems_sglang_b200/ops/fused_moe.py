@@ -229,11 +229,12 @@ def fused_experts(
         _C.check(lib.fmoe_fused_experts(fa, st))
         return out
 
-    # profiling path (STAGE_EVENTS set): the same kernels launched one by one with events around the GEMMs
+    # profiling path (STAGE_EVENTS set): the same kernels launched one by one with events around each launch
     name, block = _pick_variant(w1.dtype if not use_fp8_w8a8 else torch.float8_e4m3fn, numel, E, I, H, variant)
     vcode = _C.VARIANTS[name]
 
-    sorted_ids, expert_ids, num_post = moe_align_block_size(ids, block, E)
+    with _stage("align"):
+        sorted_ids, expert_ids, num_post = moe_align_block_size(ids, block, E)
     cap = sorted_ids.numel()
     max_blocks = min(cap // block, numel)
     row_w = wts.data_ptr()
@@ -247,10 +248,12 @@ def fused_experts(
     z = z_alloc((numel, H), dtype=out_dtype, device=dev)
 
     if not use_fp8_w8a8:
-        if name in ("tcgen05", "tcgen05_pair"):
+        if name == "tcgen05_pair" or (name == "tcgen05" and not os.environ.get("FMOE_TC_GATHER4")):
+            # sorted copy of the input rows (FMOE_TC_GATHER4=1: the single-CTA kernel gathers them by TMA instead)
             xs = torch.empty((cap, H), dtype=out_dtype, device=dev)
-            _C.check(lib.fmoe_gather_rows(x.data_ptr(), x.element_size(), cap, H, sorted_ids.data_ptr(), k, numel,
-                                          num_post.data_ptr(), xs.data_ptr(), st))
+            with _stage("gather_rows"):
+                _C.check(lib.fmoe_gather_rows(x.data_ptr(), x.element_size(), cap, H, sorted_ids.data_ptr(), k, numel,
+                                              num_post.data_ptr(), xs.data_ptr(), st))
             a_ptr, a_rows, gather = xs.data_ptr(), cap, 0
         else:
             a_ptr, a_rows, gather = x.data_ptr(), T, 1
@@ -270,14 +273,28 @@ def fused_experts(
             # rows quantised straight into the padded expert-sorted order (gather fused into the quantiser)
             xq = torch.empty((cap, H), dtype=torch.float8_e4m3fn, device=dev)
             xsc = torch.empty((cap, H // 128), dtype=torch.float32, device=dev)
-            _C.check(lib.fmoe_quant_fp8_group128(x.data_ptr(), _C.BF16, cap, H, sorted_ids.data_ptr(), k, numel,
-                                                 num_post.data_ptr(), xq.data_ptr(), xsc.data_ptr(), st))
+            if k >= 2 and H % 512 == 0:
+                # each token row quantised once, then bytes and scales copied into the sorted order
+                xt = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=dev)
+                xtsc = torch.empty((T, H // 128), dtype=torch.float32, device=dev)
+                with _stage("quant_input"):
+                    _C.check(lib.fmoe_quant_fp8_group128(x.data_ptr(), _C.BF16, T, H, None, 1, 0, None, xt.data_ptr(),
+                                                         xtsc.data_ptr(), st))
+                with _stage("gather_rows"):
+                    for src, dst, eb, cols in ((xt, xq, 1, H), (xtsc, xsc, 4, H // 128)):
+                        _C.check(lib.fmoe_gather_rows(src.data_ptr(), eb, cap, cols, sorted_ids.data_ptr(), k, numel,
+                                                      num_post.data_ptr(), dst.data_ptr(), st))
+            else:
+                with _stage("quant_input"):
+                    _C.check(lib.fmoe_quant_fp8_group128(x.data_ptr(), _C.BF16, cap, H, sorted_ids.data_ptr(), k, numel,
+                                                         num_post.data_ptr(), xq.data_ptr(), xsc.data_ptr(), st))
             a_rows, gather, act_dtype, act_code = cap, 0, torch.bfloat16, _C.BF16
         else:
             xq = torch.empty((T, H), dtype=torch.float8_e4m3fn, device=dev)
             xsc = torch.empty((T, H // 128), dtype=torch.float32, device=dev)
-            _C.check(lib.fmoe_quant_fp8_group128(x.data_ptr(), _C.BF16, T, H, None, 1, 0, None, xq.data_ptr(),
-                                                 xsc.data_ptr(), st))
+            with _stage("quant_input"):
+                _C.check(lib.fmoe_quant_fp8_group128(x.data_ptr(), _C.BF16, T, H, None, 1, 0, None, xq.data_ptr(),
+                                                     xsc.data_ptr(), st))
             a_rows, gather, act_dtype, act_code = T, 1, torch.float32, _C.F32
         act = torch.empty((cap, I), dtype=act_dtype, device=dev)
         g1 = _gemm_args(dtype=_C.E4M3, out_dtype=act_code, a_gather=gather, n=I, k=H, a_rows=a_rows, a=xq.data_ptr(),
@@ -287,8 +304,9 @@ def fused_experts(
             _C.check(lib.fmoe_gemm1_silu(g1, st))
         aq = torch.empty((cap, I), dtype=torch.float8_e4m3fn, device=dev)
         asc = torch.empty((cap, I // 128), dtype=torch.float32, device=dev)
-        _C.check(lib.fmoe_quant_fp8_group128(act.data_ptr(), act_code, cap, I, None, 1, 0, num_post.data_ptr(),
-                                             aq.data_ptr(), asc.data_ptr(), st))
+        with _stage("quant_act"):
+            _C.check(lib.fmoe_quant_fp8_group128(act.data_ptr(), act_code, cap, I, sorted_ids.data_ptr(), 0, numel, num_post.data_ptr(),
+                                                 aq.data_ptr(), asc.data_ptr(), st))
         g2 = _gemm_args(dtype=_C.E4M3, out_dtype=_C.BF16, a_gather=0, n=H, k=I, a_rows=cap, a=aq.data_ptr(),
                         a_scale=asc.data_ptr(), w=w2.data_ptr(), w_scale=w2_scale.data_ptr(),
                         row_scale=None if apply_router_weight_on_input else row_w, out=z.data_ptr(), **common)
@@ -299,7 +317,8 @@ def fused_experts(
         return z.view(T, k, H)
     out = torch.empty((T, H), dtype=out_dtype, device=dev)
     scale = 1.0 if routed_scaling_factor is None else float(routed_scaling_factor)
-    _C.check(lib.fmoe_moe_sum(z.data_ptr(), _C.DTYPE_CODE[out_dtype], T, k, H, scale, out.data_ptr(), st))
+    with _stage("moe_sum"):
+        _C.check(lib.fmoe_moe_sum(z.data_ptr(), _C.DTYPE_CODE[out_dtype], T, k, H, scale, out.data_ptr(), st))
     return out
 
 

@@ -114,8 +114,10 @@ int fmoe_moe_align_block_size_ws(const int32_t* topk_ids, int64_t numel, int E, 
  *   q [rows_out, K] e4m3, scale [rows_out, K/128] f32,
  *   scale = max(amax,1e-10)/448, q = rne(x/scale) saturated to +-448.
  * With row_map == NULL rows_out == rows_in and row r reads row r.  With a
- * row_map (sorted_token_ids) output row p reads input row row_map[p]/map_div,
- * and rows whose map entry is >= map_sentinel are written as zeros (scale 1).
+ * row_map (sorted_token_ids) output row p reads input row row_map[p]/map_div
+ * (map_div >= 1) or input row p itself (map_div == 0: the map only marks the
+ * padding), and rows whose map entry is >= map_sentinel are written as zeros
+ * (scale 1) without reading x.
  * Only rows p < *num_rows_dev are produced when num_rows_dev != NULL.
  */
 int fmoe_quant_fp8_group128(const void* x, int in_dtype, int64_t rows_out, int64_t K,

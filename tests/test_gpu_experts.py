@@ -151,10 +151,54 @@ def test_one_call_entry_equals_kernel_by_kernel_path(fg, variant, fp8):
     FM.STAGE_EVENTS = []
     try:
         b = _run(fg, x, w1, w2, tw, ti, **kw)
-        assert len(FM.STAGE_EVENTS) == 2
+        assert sum(name.startswith("gemm") for name, _, _ in FM.STAGE_EVENTS) == 2
     finally:
         FM.STAGE_EVENTS = None
     assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("T,H,I,E,k", [(70, 512, 256, 16, 4), (1, 128, 128, 4, 2), (300, 1032, 384, 8, 2),
+                                       (2048, 2048, 768, 32, 8)])
+@pytest.mark.parametrize("on_input", [False, True])
+def test_tcgen05_gate_up_row_gather_equals_sorted_copy(fg, T, H, I, E, k, on_input):
+    """The tcgen05 gate/up kernel either reads a sorted copy of the input rows (a_gather = 0) or fetches
+    row slot/top_k of the [T,H] input itself with TMA gather (a_gather = 1); padding rows read as zeros in
+    both.  The two must agree bit for bit, and rows past num_tokens_post_padded stay untouched."""
+    import importlib
+
+    from flaggems_sglang_b200 import _C
+
+    FM = importlib.import_module("flaggems_sglang_b200.ops.fused_moe")
+    kk = 1 if on_input else k
+    x, w1, _, logits = _layer(T, H, I, E, kk, torch.bfloat16, 23)
+    tw, ti = OR.softmax_topk(logits, kk, True)
+    x, w1, tw, ti = x.cuda(), w1.cuda(), tw.cuda().float().contiguous(), ti.cuda().int().contiguous()
+    lib, st = _C.lib(), _C.stream_ptr(x.device)
+    numel = T * kk
+    sorted_ids, expert_ids, num_post = fg.moe_align_block_size(ti, 128, E)
+    cap = sorted_ids.numel()
+    common = dict(variant=_C.VARIANTS["tcgen05"], activation=_C.ACTIVATIONS["silu"], num_experts=E, top_k=kk,
+                  block_size=128, numel=numel, sorted_cap=cap, max_blocks=min(cap // 128, numel),
+                  sorted_token_ids=sorted_ids.data_ptr(), expert_ids=expert_ids.data_ptr(),
+                  num_tokens_post_padded=num_post.data_ptr(), dtype=_C.BF16, out_dtype=_C.BF16, n=I, k=H,
+                  w=w1.data_ptr(), row_scale=tw.data_ptr() if on_input else None)
+    xs = torch.empty((cap, H), dtype=torch.bfloat16, device="cuda")
+    _C.check(lib.fmoe_gather_rows(x.data_ptr(), 2, cap, H, sorted_ids.data_ptr(), kk, numel, num_post.data_ptr(),
+                                  xs.data_ptr(), st))
+    outs = []
+    for gather in (0, 1):
+        act = torch.full((cap, I), -7.0, dtype=torch.bfloat16, device="cuda")
+        a, rows = (x, T) if gather else (xs, cap)
+        g1 = FM._gemm_args(a_gather=gather, a_rows=rows, a=a.data_ptr(), out=act.data_ptr(), **common)
+        _C.check(lib.fmoe_gemm1_silu(g1, st))
+        outs.append(act)
+    torch.cuda.synchronize()
+    _C.check_device_status()
+    used = int(num_post.item())
+    assert torch.equal(outs[0], outs[1])
+    assert (outs[1][used:] == -7.0).all()
+    pad = (sorted_ids[:used] >= numel)
+    assert (outs[1][:used][pad] == 0).all()
 
 
 @pytest.mark.parametrize("variant", ["simt", "stream", "tcgen05"])
@@ -264,6 +308,49 @@ def test_fp8_block_quant(fg, T, variant):
                            routed_scaling_factor=2.5, variant=variant)
     ref = OE.fused_experts_fp8(x, w1q, w1s, w2q, w2s, tw, ti, routed_scaling_factor=2.5)
     assert_close_moe(out, ref, "fp8", f"fp8 T={T} {variant}")
+
+
+@pytest.mark.parametrize("H", [512, 640])
+def test_fp8_tcgen05_both_input_quant_routes(fg, H):
+    """H % 512 == 0: token rows are quantised once and copied into the sorted order; otherwise every sorted
+    row is quantised.  Both feed the same GEMM and must match the oracle."""
+    T, I, E, k = 300, 256, 8, 2
+    x, w1, w2, logits = _layer(T, H, I, E, k, torch.bfloat16, 77)
+    w1q, w1s = OQ.quant_weight_block128(w1)
+    w2q, w2s = OQ.quant_weight_block128(w2)
+    tw, ti = OR.softmax_topk(logits, k, True)
+    out = fg.fused_experts(x.cuda(), w1q.cuda(), w2q.cuda(), tw.cuda(), ti.cuda(), use_fp8_w8a8=True,
+                           w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), block_shape=[128, 128], variant="tcgen05")
+    ref = OE.fused_experts_fp8(x, w1q, w1s, w2q, w2s, tw, ti)
+    assert_close_moe(out, ref, "fp8", f"fp8 H={H}")
+
+
+def test_fp8_quantise_once_then_copy_equals_quantising_sorted_rows(fg):
+    from flaggems_sglang_b200 import _C
+
+    T, H, E, k = 130, 1024, 8, 4
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16).cuda()
+    ti = torch.randint(0, E, (T, k), generator=g).int().cuda()
+    sorted_ids, _, num_post = fg.moe_align_block_size(ti, 128, E)
+    cap, numel, used = sorted_ids.numel(), T * k, int(num_post.item())
+    lib, st = _C.lib(), _C.stream_ptr(x.device)
+    qa = torch.empty((cap, H), dtype=torch.uint8, device="cuda")
+    sa = torch.empty((cap, H // 128), dtype=torch.float32, device="cuda")
+    _C.check(lib.fmoe_quant_fp8_group128(x.data_ptr(), _C.BF16, cap, H, sorted_ids.data_ptr(), k, numel,
+                                         num_post.data_ptr(), qa.data_ptr(), sa.data_ptr(), st))
+    qt = torch.empty((T, H), dtype=torch.uint8, device="cuda")
+    stt = torch.empty((T, H // 128), dtype=torch.float32, device="cuda")
+    _C.check(lib.fmoe_quant_fp8_group128(x.data_ptr(), _C.BF16, T, H, None, 1, 0, None, qt.data_ptr(), stt.data_ptr(), st))
+    qb, sb = torch.empty_like(qa), torch.empty_like(sa)
+    for src, dst, eb, cols in ((qt, qb, 1, H), (stt, sb, 4, H // 128)):
+        _C.check(lib.fmoe_gather_rows(src.data_ptr(), eb, cap, cols, sorted_ids.data_ptr(), k, numel,
+                                      num_post.data_ptr(), dst.data_ptr(), st))
+    torch.cuda.synchronize()
+    real = sorted_ids[:used] < numel
+    assert torch.equal(qa[:used][real], qb[:used][real])
+    assert torch.equal(sa[:used][real], sb[:used][real])
+    assert (qb[:used][~real] == 0).all() and (qa[:used][~real] == 0).all()
 
 
 # ------------------------------------------------------------------ full benchmark sizes

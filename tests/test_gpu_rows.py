@@ -27,6 +27,51 @@ def test_quant_group128_bit_exact(fg, rows, K, dtype):
     assert torch.equal(q.cpu().view(torch.uint8), oq.view(torch.uint8))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_quant_group128_division_bit_exact_over_wide_range(fg, dtype):
+    """The kernel divides by the group scale through a shared reciprocal with two exact-residual corrections;
+    8M quotients with group magnitudes from 2^-60 to 2^60 and exact ties must give the bits of the oracle's
+    IEEE division."""
+    g = torch.Generator().manual_seed(99)
+    rows, K = 4096, 2048
+    x = torch.randn(rows, K, generator=g)
+    expo = torch.randint(-60, 61, (rows, K // 128), generator=g).float()
+    x = (x.view(rows, K // 128, 128) * torch.exp2(expo).unsqueeze(-1)).view(rows, K)
+    # exact e4m3 grid points and midpoints relative to a group maximum of 448 * 2^e
+    grid = torch.tensor([448.0, 13.0, 13.5, 14.0, 0.001953125, 0.0009765625, 240.0, 232.0, -17.0, -18.0])
+    x[5, :10] = grid
+    x[6, 128:138] = grid * 2.0 ** -20
+    x = x.to(dtype)
+    q, s = fg.per_token_group_quant_fp8(x.cuda())
+    oq, os_ = OQ.quant_act_group128(x)
+    assert torch.equal(s.cpu(), os_)
+    assert torch.equal(q.cpu().view(torch.uint8), oq.view(torch.uint8))
+
+
+def test_quant_in_place_rows_with_padding_marks(fg):
+    """map_div = 0: output row p reads input row p, and the map only says which positions are padding."""
+    from flaggems_sglang_b200 import _C
+
+    torch.manual_seed(3)
+    T, k, K, E, block = 21, 2, 256, 8, 16
+    ids = torch.randint(0, E, (T, k), dtype=torch.int32)
+    s, _, n = fg.moe_align_block_size(ids.cuda(), block, E)
+    cap, used = s.numel(), int(n.item())
+    x = torch.randn(cap, K).bfloat16()
+    q = torch.full((cap, K), 0x55, dtype=torch.uint8, device="cuda")
+    qs = torch.full((cap, K // 128), -1.0, dtype=torch.float32, device="cuda")
+    _C.check(_C.lib().fmoe_quant_fp8_group128(x.cuda().data_ptr(), _C.BF16, cap, K, s.data_ptr(), 0, T * k,
+                                              n.data_ptr(), q.data_ptr(), qs.data_ptr(), _C.stream_ptr()))
+    oq, os_ = OQ.quant_act_group128(x)
+    real = torch.zeros(cap, dtype=torch.bool)
+    real[:used] = s.cpu()[:used] < T * k
+    pad = ~real
+    pad[used:] = False
+    assert torch.equal(q.cpu()[real], oq.view(torch.uint8)[real]) and torch.equal(qs.cpu()[real], os_[real])
+    assert (q.cpu()[pad] == 0).all() and (qs.cpu()[pad] == 1.0).all()
+    assert (q.cpu()[used:] == 0x55).all() and (qs.cpu()[used:] == -1.0).all()
+
+
 def test_weight_quant_matches_oracle(fg):
     torch.manual_seed(0)
     w = (torch.randn(3, 256, 384) / 16).bfloat16()

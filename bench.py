@@ -325,6 +325,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-T sweep of the configuration")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="N>1: token exchange by this package's P2P-store kernels (default) or by NCCL all-to-all")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -339,7 +341,7 @@ def main():
     if world > 1:
         from flaggems_sglang_b200 import ep_bench
 
-        ep_bench.run(args, cfg, rank, world, local)
+        ep_bench.run(args, cfg, rank, world, local, clock_sampler=ClockSampler(local))
         return
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (no CPU fallback)"

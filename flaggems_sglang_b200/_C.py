@@ -84,6 +84,16 @@ SIGNATURES = {
     "fmoe_fused_experts": (c_int, [POINTER(FusedArgs), c_void_p]),
     "fmoe_static_scratch_bytes": (c_int64, []),
     "fmoe_fused_experts_static": (c_int, [POINTER(FusedArgs), c_void_p]),
+    "fmoe_ep_buffer_create": (c_int, [c_int64, POINTER(c_void_p), c_void_p]),
+    "fmoe_ep_buffer_open": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "fmoe_ep_buffer_close": (c_int, [c_void_p]),
+    "fmoe_ep_buffer_destroy": (c_int, [c_void_p]),
+    "fmoe_ep_route": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "fmoe_ep_dispatch": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "fmoe_ep_mask_tail": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p]),
+    "fmoe_ep_combine": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
+                                c_void_p, c_void_p]),
     "fmoe_selftest_bounded_wait": (c_int, [c_int64, c_void_p]),
     "fmoe_debug_tcgen05_wait_profile": (c_int, [c_void_p, c_int]),
     "fmoe_check_device_status": (c_int, [c_void_p]),

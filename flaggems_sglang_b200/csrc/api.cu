@@ -110,6 +110,10 @@ extern "C" int fmoe_check_device_status(void* stream) {
   int status = 0;
   int rc = fmoe::read_and_clear_device_status((cudaStream_t)stream, &status);
   if (rc) return rc;
+  if ((status & 0xF00) == 0xA00)
+    return fmoe::fail(FMOE_ERR_INVALID_ARG,
+                      "expert-parallel exchange skipped rows (site code 0x%x: 0xA00 expert id out of range, "
+                      "0xA01 receive capacity exceeded, 0xA02 bad return address)", status);
   if (status != 0)
     return fmoe::fail(FMOE_ERR_DEVICE_TIMEOUT, "a bounded wait inside a tcgen05 kernel gave up (site code 0x%x)", status);
   return FMOE_OK;

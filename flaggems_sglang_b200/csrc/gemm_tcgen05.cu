@@ -512,10 +512,12 @@ int read_wait_profile(long long* host_out, int n) {
 
 int status_word_fp8(int* out, bool clear);
 int status_word_pair(int* out, bool clear);
+int status_word_ep(int* out, bool clear);
 
-// First non-zero status word of the three tcgen05 translation units (each keeps its own); all are cleared.
+// First non-zero status word of the translation units that keep one (tcgen05 kernels, expert-parallel
+// exchange); all are cleared.
 int read_and_clear_device_status(cudaStream_t st, int* status_out) {
-  int zero = 0, a = 0, b = 0, c = 0;
+  int zero = 0, a = 0, b = 0, c = 0, d = 0;
   FMOE_CUDA_OK(cudaStreamSynchronize(st));
   FMOE_CUDA_OK(cudaMemcpyFromSymbol(&a, g_device_status, sizeof(int)));
   if (a != 0) FMOE_CUDA_OK(cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int)));
@@ -523,7 +525,9 @@ int read_and_clear_device_status(cudaStream_t st, int* status_out) {
   if (rc) return rc;
   rc = status_word_pair(&c, true);
   if (rc) return rc;
-  *status_out = a ? a : (b ? b : c);
+  rc = status_word_ep(&d, true);
+  if (rc) return rc;
+  *status_out = a ? a : (b ? b : (c ? c : d));
   return FMOE_OK;
 }
 

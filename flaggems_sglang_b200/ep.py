@@ -12,7 +12,12 @@ Per layer call, every rank
   4. runs the grouped GEMMs over the rows it received, with top_k = 1 and the weight applied in
      the down-projection epilogue exactly as on one GPU;
   5. combine: all-to-all of the result rows back, un-permute to slot order, sum the k slots.
-Payloads land in local HBM through NCCL before any kernel reads them; no kernel touches peer memory.
+Two exchanges are built.  The default one is NCCL all-to-all (steps 3 and 5 as library calls; it needs the split
+sizes on the host, i.e. one device-to-host read per call).  With a `PeerExchange` (receive areas that the peers
+map through CUDA IPC) steps 2-5 run without any host read: this package's kernels store the rows straight into
+the destination rank's receive area and the expert outputs straight into the source rank's slot buffer over
+NVLink, and the only library calls left are a tiny count all-gather and two barriers that order the phases.
+Those kernels never wait on a peer and never read peer memory.
 
 The data movement is written against a small backend interface so that the exchange logic runs
 unchanged on CPU ranks (gloo) in the tests, where the backend is the CPU oracle.
@@ -111,6 +116,214 @@ def _all_to_all_rows(send: torch.Tensor, plan: DispatchPlan, group, reverse: boo
     return out
 
 
+# --------------------------------------------------------------------------
+# exchange over peer memory
+# --------------------------------------------------------------------------
+class _DeviceBytes:
+    """Exposes a raw device allocation to torch (zero copy) through __cuda_array_interface__."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+def _up256(n: int) -> int:
+    return (n + 255) & ~255
+
+
+class PeerExchange:
+    """Receive areas of one process group for the P2P exchange (see fmoe_ep_* in include/fmoe_b200.h).
+
+    Created collectively (every rank of `group`, same arguments).  `capacity` = rows this rank can receive per
+    call; the default world * max_tokens * top_k can never overflow, a smaller value saves memory and an
+    overflow is then reported by `_C.check_device_status` (rows beyond it are dropped, nothing is overwritten).
+    One instance serves one layer call at a time (calls on it must be stream-ordered).
+    """
+
+    def __init__(self, group, max_tokens: int, top_k: int, hidden_size: int, dtype=torch.bfloat16,
+                 capacity: Optional[int] = None, device=None):
+        import ctypes
+
+        from . import _C
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self._layout(max_tokens, top_k, hidden_size, dtype, capacity)
+        lib = _C.lib()
+        base = ctypes.c_void_p()
+        handle = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(self.device):
+            _C.check(lib.fmoe_ep_buffer_create(self.nbytes, ctypes.byref(base), handle))
+            mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
+            every = torch.empty(self.world * 64, dtype=torch.uint8, device=self.device)
+            dist.all_gather_into_tensor(every, mine, group=group)
+            every = every.cpu().view(self.world, 64)
+            self._own_base = base.value
+            self._opened = []
+            bases = []
+            for j in range(self.world):
+                if j == self.rank:
+                    bases.append(base.value)
+                    continue
+                peer = ctypes.c_void_p()
+                raw = (ctypes.c_ubyte * 64)(*every[j].tolist())
+                _C.check(lib.fmoe_ep_buffer_open(raw, ctypes.byref(peer)))
+                self._opened.append(peer.value)
+                bases.append(peer.value)
+        self._bind(bases, torch.as_tensor(_DeviceBytes(base.value, self.nbytes), device=self.device))
+        self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.ids.fill_(-1)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)
+
+    # -- shared with the single-process emulation used by the tests -------------------------------------
+    def _layout(self, max_tokens, top_k, hidden_size, dtype, capacity):
+        self.max_tokens, self.top_k, self.H, self.dtype = int(max_tokens), int(top_k), int(hidden_size), dtype
+        eb = torch.empty(0, dtype=dtype).element_size()
+        if (self.H * eb) % 16:
+            raise ValueError("hidden rows must be a multiple of 16 bytes")
+        self.z_slots = self.max_tokens * self.top_k
+        self.capacity = int(capacity) if capacity is not None else self.world * self.z_slots
+        off = 0
+        self._off = {}
+        for name, nbytes in (("rows", self.capacity * self.H * eb), ("ids", self.capacity * 4),
+                             ("weights", self.capacity * 4), ("src", self.capacity * 8),
+                             ("z", self.z_slots * self.H * eb)):
+            self._off[name] = (off, nbytes)
+            off += _up256(nbytes)
+        self.nbytes = max(off, 256)
+
+    def _bind(self, bases, own_bytes: torch.Tensor):
+        self._bytes = own_bytes
+
+        def own(name, dt, shape):
+            o, n = self._off[name]
+            return own_bytes[o:o + n].view(dt).view(shape)
+
+        self.rows = own("rows", self.dtype, (self.capacity, self.H))
+        self.ids = own("ids", torch.int32, (self.capacity,))
+        self.weights = own("weights", torch.float32, (self.capacity,))
+        self.src = own("src", torch.int32, (self.capacity, 2))
+        self.z = own("z", self.dtype, (self.z_slots, self.H))
+        self.ptrs = {name: torch.tensor([b + self._off[name][0] for b in bases], dtype=torch.int64, device=self.device)
+                     for name in self._off}
+
+    @classmethod
+    def emulated(cls, world: int, max_tokens: int, top_k: int, hidden_size: int, dtype=torch.bfloat16,
+                 capacity: Optional[int] = None, device="cuda"):
+        """`world` exchanges living in ONE process and on one GPU, the "peers" being plain local tensors: the
+        same kernels and pointer tables without IPC.  The caller runs every phase for all ranks before the next
+        phase (there are no barriers to wait on)."""
+        out, stores = [], []
+        for r in range(world):
+            xc = cls.__new__(cls)
+            xc.group, xc.world, xc.rank, xc.device = None, world, r, torch.device(device)
+            xc._layout(max_tokens, top_k, hidden_size, dtype, capacity)
+            stores.append(torch.zeros(xc.nbytes, dtype=torch.uint8, device=xc.device))
+            out.append(xc)
+        bases = [st.data_ptr() for st in stores]
+        for xc, st in zip(out, stores):
+            xc._bind(bases, st)
+            xc.ids.fill_(-1)
+            xc._opened, xc._own_base, xc._flag = [], None, None
+        return out
+
+    def barrier(self):
+        """Stream-ordered barrier over the group: every kernel a rank enqueued before it has completed (its
+        peer stores included) before any rank's later kernels start."""
+        dist.all_reduce(self._flag, group=self.group)
+
+    def close(self):
+        from . import _C
+
+        lib = _C.lib()
+        torch.cuda.synchronize(self.device)
+        if self.group is not None:
+            dist.barrier(group=self.group)
+        for p in self._opened:
+            _C.check(lib.fmoe_ep_buffer_close(p))
+        self._opened = []
+        if self._own_base:
+            if self.group is not None:
+                dist.barrier(group=self.group)
+            _C.check(lib.fmoe_ep_buffer_destroy(self._own_base))
+            self._own_base = None
+
+
+def p2p_route(xc: PeerExchange, hidden_states, topk_weights, topk_ids, experts_per_rank: int) -> dict:
+    """Phase 1 (local): destination rank per (token, slot), rows per destination, destination-sorted order."""
+    from . import _C
+    from .ops.moe_align_block_size import moe_align_block_size
+
+    T, H = hidden_states.shape
+    k = topk_ids.shape[1]
+    if T > xc.max_tokens or k != xc.top_k or H != xc.H or hidden_states.dtype != xc.dtype:
+        raise ValueError(f"this PeerExchange was sized for <= {xc.max_tokens} tokens, top_k {xc.top_k}, H {xc.H}, {xc.dtype}")
+    dev = hidden_states.device
+    x = hidden_states.contiguous()
+    ids = topk_ids.to(torch.int32).contiguous().view(-1)
+    wts = topk_weights.to(torch.float32).contiguous().view(-1)
+    dest = torch.empty(T * k, dtype=torch.int32, device=dev)
+    counts = torch.empty(xc.world, dtype=torch.int32, device=dev)
+    _C.check(_C.lib().fmoe_ep_route(ids.data_ptr(), T * k, experts_per_rank, xc.world, dest.data_ptr(),
+                                    counts.data_ptr(), _C.stream_ptr(dev)))
+    perm, _, _ = moe_align_block_size(dest, 1, xc.world) if T > 0 else (dest, None, None)
+    return dict(x=x, ids=ids, wts=wts, perm=perm, counts=counts, T=T, k=k, e_local=experts_per_rank)
+
+
+def p2p_send(xc: PeerExchange, state: dict, matrix: torch.Tensor) -> None:
+    """Phase 2: store this rank's rows and their metadata into the destination ranks' receive areas."""
+    from . import _C
+
+    state["matrix"] = matrix
+    x = state["x"]
+    _C.check(_C.lib().fmoe_ep_dispatch(
+        x.data_ptr(), x.element_size(), state["T"], xc.H, state["k"], state["ids"].data_ptr(), state["wts"].data_ptr(),
+        state["perm"].data_ptr(), matrix.data_ptr(), xc.rank, xc.world, state["e_local"], xc.ptrs["rows"].data_ptr(),
+        xc.ptrs["ids"].data_ptr(), xc.ptrs["weights"].data_ptr(), xc.ptrs["src"].data_ptr(), xc.capacity,
+        _C.stream_ptr(x.device)))
+
+
+def p2p_experts(xc: PeerExchange, state: dict, w1_local, w2_local, **expert_kwargs) -> torch.Tensor:
+    """Phase 3 (after the barrier): grouped GEMMs over the receive area; rows past the received count carry
+    id -1 and are skipped by moe_align_block_size."""
+    from . import _C
+    from .ops.fused_moe import _pick_variant, fused_experts
+
+    dev = xc.rows.device
+    _C.check(_C.lib().fmoe_ep_mask_tail(xc.ids.data_ptr(), state["matrix"].data_ptr(), xc.rank, xc.world, xc.capacity,
+                                        _C.stream_ptr(dev)))
+    if "variant" not in expert_kwargs:
+        # kernel family for the rows a balanced routing would bring (this rank's own count), not for the capacity
+        fp8 = expert_kwargs.get("use_fp8_w8a8", False)
+        name, _ = _pick_variant(torch.float8_e4m3fn if fp8 else w1_local.dtype, max(state["T"] * state["k"], 1),
+                                w1_local.shape[0], w2_local.shape[2], xc.H, None)
+        expert_kwargs = dict(expert_kwargs, variant=name)
+    return fused_experts(xc.rows, w1_local, w2_local, xc.weights.view(-1, 1), xc.ids.view(-1, 1), no_combine=True,
+                         **expert_kwargs).view(xc.capacity, xc.H)
+
+
+def p2p_return(xc: PeerExchange, state: dict, z_rows: torch.Tensor) -> None:
+    """Phase 4: store every expert output row into the slot buffer of the rank it came from."""
+    from . import _C
+
+    _C.check(_C.lib().fmoe_ep_combine(z_rows.data_ptr(), z_rows.element_size(), xc.H, xc.src.data_ptr(),
+                                      state["matrix"].data_ptr(), xc.rank, xc.world, xc.capacity, xc.z_slots,
+                                      xc.ptrs["z"].data_ptr(), _C.stream_ptr(z_rows.device)))
+
+
+def p2p_finish(xc: PeerExchange, state: dict, routed_scaling_factor: Optional[float]) -> torch.Tensor:
+    """Phase 5 (after the barrier): sum the top_k slots of every token."""
+    from .ops.moe_sum import moe_sum
+
+    T, k = state["T"], state["k"]
+    out = torch.empty(T, xc.H, dtype=xc.dtype, device=xc.rows.device)
+    if T == 0:
+        return out
+    return moe_sum(xc.z[:T * k].view(T, k, xc.H), out, routed_scaling_factor)
+
+
 def ep_fused_experts(
     hidden_states: torch.Tensor,
     w1_local: torch.Tensor,
@@ -121,10 +334,13 @@ def ep_fused_experts(
     group=None,
     backend=None,
     routed_scaling_factor: Optional[float] = None,
+    exchange: Optional["PeerExchange"] = None,
     **expert_kwargs,
 ) -> torch.Tensor:
     """Expert-parallel `fused_experts`: `w1_local`/`w2_local` hold experts
-    [rank*E/N, (rank+1)*E/N) of the global layer; `topk_ids` are global ids of this rank's tokens."""
+    [rank*E/N, (rank+1)*E/N) of the global layer; `topk_ids` are global ids of this rank's tokens.
+    `exchange`: a PeerExchange of the same group -> rows travel by P2P stores of this package's kernels
+    instead of NCCL all-to-all, with no host read on the way."""
     backend = backend or CudaBackend()
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
@@ -133,6 +349,24 @@ def ep_fused_experts(
     e_local = num_global_experts // world
     if w1_local.shape[0] != e_local:
         raise ValueError(f"this rank holds {w1_local.shape[0]} experts, expected {e_local}")
+    if exchange is not None:
+        if exchange.world != world or exchange.rank != rank:
+            raise ValueError("the PeerExchange belongs to another group")
+        with _phase("route", True):
+            state = p2p_route(exchange, hidden_states, topk_weights, topk_ids, e_local)
+        with _phase("counts", True):
+            matrix = torch.empty(world * world, dtype=torch.int32, device=hidden_states.device)
+            dist.all_gather_into_tensor(matrix, state["counts"], group=group)
+        with _phase("dispatch", True):
+            p2p_send(exchange, state, matrix)
+            exchange.barrier()
+        with _phase("experts", True):
+            z_rows = p2p_experts(exchange, state, w1_local, w2_local, **expert_kwargs)
+        with _phase("combine", True):
+            p2p_return(exchange, state, z_rows)
+            exchange.barrier()
+        with _phase("sum", True):
+            return p2p_finish(exchange, state, routed_scaling_factor)
     T, H = hidden_states.shape
     k = topk_ids.shape[1]
     timed = hidden_states.is_cuda
@@ -175,14 +409,15 @@ def ep_fused_experts(
 def ep_fused_moe(hidden_states, w1_local, w2_local, gating_output, topk: int, num_global_experts: int,
                  renormalize: bool = True, use_grouped_topk: bool = False, num_expert_group=None, topk_group=None,
                  correction_bias=None, routed_scaling_factor=None, group=None, backend=None, router=None,
-                 **expert_kwargs):
+                 exchange=None, **expert_kwargs):
     """Router on this rank's tokens, then `ep_fused_experts`."""
     if router is None:
         from .ops.topk import topk as router
     tw, ti = router(hidden_states, gating_output, topk, renormalize, use_grouped_topk, num_expert_group, topk_group,
                     correction_bias, None)
     return ep_fused_experts(hidden_states, w1_local, w2_local, tw, ti, num_global_experts, group=group,
-                            backend=backend, routed_scaling_factor=routed_scaling_factor, **expert_kwargs)
+                            backend=backend, routed_scaling_factor=routed_scaling_factor, exchange=exchange,
+                            **expert_kwargs)
 
 
-__all__ = ["ep_fused_experts", "ep_fused_moe", "plan_from_count_matrix", "DispatchPlan", "CudaBackend"]
+__all__ = ["ep_fused_experts", "ep_fused_moe", "plan_from_count_matrix", "DispatchPlan", "CudaBackend", "PeerExchange"]

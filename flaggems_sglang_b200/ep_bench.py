@@ -14,7 +14,9 @@ import torch
 import torch.distributed as dist
 
 
-def run(args, cfg, rank: int, world: int, local: int) -> None:
+def run(args, cfg, rank: int, world: int, local: int, clock_sampler=None) -> None:
+    """`clock_sampler`: object with start()/stop() -> dict; rank 0 samples its GPU's clocks from the warm-up to
+    the end of the timed regions (they are tens of milliseconds, shorter than one nvidia-smi sample)."""
     from . import ep, workloads as W
     from . import _C
 
@@ -31,12 +33,19 @@ def run(args, cfg, rank: int, world: int, local: int) -> None:
         if cfg.dtype == "fp8":
             kw = dict(use_fp8_w8a8=True, w1_scale=wts["w1_scale"], w2_scale=wts["w2_scale"], block_shape=[128, 128])
 
+        # rows travel by P2P stores of this package's kernels into IPC-mapped receive areas ("p2p"), or by
+        # NCCL all-to-all ("nccl")
+        mode = getattr(args, "ep_exchange", "p2p")
+        xc = ep.PeerExchange(None, args.tokens, cfg.top_k, cfg.H, tok["hidden"].dtype) if mode == "p2p" else None
+
         def step():
             return ep.ep_fused_moe(tok["hidden"], wts["w1"], wts["w2"], tok["logits"], cfg.top_k, cfg.E, True,
                                    use_grouped_topk=cfg.router == "grouped", num_expert_group=cfg.n_group,
                                    topk_group=cfg.topk_group, correction_bias=tok.get("correction_bias"),
-                                   routed_scaling_factor=cfg.routed_scaling_factor, **kw)
+                                   routed_scaling_factor=cfg.routed_scaling_factor, exchange=xc, **kw)
 
+        if clock_sampler is not None and rank == 0:
+            clock_sampler.start()
         for _ in range(max(args.warmup, 3)):
             step()
         torch.cuda.synchronize()
@@ -76,6 +85,7 @@ def run(args, cfg, rank: int, world: int, local: int) -> None:
         dist.barrier()
         ms2 = torch.tensor([e0.elapsed_time(e1) / args.steps], device=dev)
         dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
+        clocks = clock_sampler.stop() if clock_sampler is not None and rank == 0 else None
 
         if rank == 0:
             T_all = args.tokens * world
@@ -86,17 +96,21 @@ def run(args, cfg, rank: int, world: int, local: int) -> None:
                 "scaling": "weak", "vs_baseline": None, "dtype": cfg.dtype, "data": "synthetic",
                 "config": {"workload": f"{cfg.name} MoE layer H={cfg.H} I={cfg.I} E={cfg.E} top_k={cfg.top_k}, "
                                        f"T={args.tokens} tokens per rank, experts sharded {e_local} per GPU, "
-                                       f"NCCL all-to-all dispatch/combine",
+                                       + ("dispatch/combine by P2P stores into IPC-mapped receive areas"
+                                          if mode == "p2p" else "NCCL all-to-all dispatch/combine"),
                            "tokens_per_step": T_all, "parallelism": f"ep{world}",
                            "l2": "weights re-read every step exceed L2 (no flush needed)"},
                 "roofline": None, "cpu_baseline": None,
                 "e2e": {"value": T_all / (ms2_v * 1e-3), "unit": "tokens/s", "ms_per_step": ms2_v,
                         "h2d_bytes_per_step": (h_host.numel() * h_host.element_size() + l_host.numel() * 4) * world,
                         "d2h_bytes_per_step": out_host.numel() * out_host.element_size() * world},
-                "gpu_launches": 9 * args.steps * world,
+                # router, route, sort, dispatch, mask, align, row copy, 2 GEMMs, combine, sum (NCCL's not counted)
+                "gpu_launches": (11 if mode == "p2p" else 9) * args.steps * world,
                 "wall_ms_per_step": t_wall * 1e3 / args.steps,
-                "clocks": None,
+                "clocks": clocks,
             }
             print(json.dumps(line), flush=True)
+        if xc is not None:
+            xc.close()
     finally:
         dist.destroy_process_group()

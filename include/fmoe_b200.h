@@ -246,9 +246,55 @@ int64_t fmoe_static_scratch_bytes(void);
 int fmoe_fused_experts_static(const fmoe_fused_args* args, void* stream);
 
 /*
+ * Expert-parallel token exchange over peer memory (one process per GPU, NVLink P2P stores).  No counterpart in
+ * the reference, which has no expert parallelism (expert_map is asserted None,
+ * src/flaggems_sglang/ops/fused_moe.py:176-178); the contract is "same numbers as the single-GPU op on the same
+ * global batch".  Experts are sharded contiguously: rank j owns global experts [j*experts_per_rank,
+ * (j+1)*experts_per_rank).
+ *
+ * Every rank owns a receive area that its peers write: rows [capacity, H], ids [capacity] (int32, local expert
+ * id), weights [capacity] (f32), src [capacity] (two int32: source rank, source slot) and a result area
+ * z [z_slots, H].  `peer_*` arguments are DEVICE arrays of `world` pointers, entry j = that area on rank j
+ * (entry `rank` = this rank's own).  The kernels only store to peer memory and never wait on a peer; the caller
+ * orders the phases across ranks with stream-ordered collectives:
+ *
+ *   fmoe_ep_route -> sort by dest (fmoe_moe_align_block_size, block 1, E = world) -> all-gather of `counts` into
+ *   matrix[world*world] (matrix[i*world+j] = rows i sends to j) -> fmoe_ep_dispatch -> barrier ->
+ *   fmoe_ep_mask_tail -> expert computation over the receive area (top_k = 1, ids = -1 rows are skipped) ->
+ *   fmoe_ep_combine -> barrier -> fmoe_moe_sum over this rank's z.
+ *
+ * Misuse that only the device can see (an expert id outside [0, world*experts_per_rank), a row beyond
+ * `capacity`, a corrupt return address) is skipped, recorded, and returned by fmoe_check_device_status as
+ * FMOE_ERR_INVALID_ARG.
+ */
+#define FMOE_EP_IPC_HANDLE_BYTES 64
+/* cudaMalloc + IPC handle of a receive area / open and close a peer's / free the own one. */
+int fmoe_ep_buffer_create(int64_t bytes, void** ptr, void* ipc_handle /* FMOE_EP_IPC_HANDLE_BYTES, host */);
+int fmoe_ep_buffer_open(const void* ipc_handle, void** ptr);
+int fmoe_ep_buffer_close(void* ptr);
+int fmoe_ep_buffer_destroy(void* ptr);
+/* dest[i] = topk_ids[i] / experts_per_rank (world for an id out of range), counts[j] = rows for rank j. */
+int fmoe_ep_route(const int32_t* topk_ids, int64_t numel, int experts_per_rank, int world, int32_t* dest,
+                  int32_t* counts, void* stream);
+/* perm: the numel (token, slot) positions sorted by dest (stable).  Sends hidden[perm[p] / top_k] and its metadata. */
+int fmoe_ep_dispatch(const void* hidden, int elem_bytes, int64_t T, int64_t H, int top_k,
+                     const int32_t* topk_ids, const float* topk_weights, const int32_t* perm,
+                     const int32_t* matrix, int rank, int world, int experts_per_rank,
+                     void* const* peer_rows, int32_t* const* peer_ids, float* const* peer_weights,
+                     void* const* peer_src, int64_t capacity, void* stream);
+/* recv_ids[r] = -1 for r >= rows received (sum of column `rank` of the matrix). */
+int fmoe_ep_mask_tail(int32_t* recv_ids, const int32_t* matrix, int rank, int world, int64_t capacity,
+                      void* stream);
+/* z_rows[r] (expert output of received row r) -> peer_z[src[r].rank] + src[r].slot * H. */
+int fmoe_ep_combine(const void* z_rows, int elem_bytes, int64_t H, const void* recv_src,
+                    const int32_t* matrix, int rank, int world, int64_t capacity, int64_t z_slots,
+                    void* const* peer_z, void* stream);
+
+/*
  * Reads and clears the device-side status word that bounded waits inside the
- * tcgen05 kernels set when they give up.  Synchronises `stream`.
- * Returns FMOE_OK or FMOE_ERR_DEVICE_TIMEOUT.
+ * tcgen05 kernels set when they give up, and the one of the expert-parallel
+ * exchange kernels.  Synchronises `stream`.
+ * Returns FMOE_OK, FMOE_ERR_DEVICE_TIMEOUT or FMOE_ERR_INVALID_ARG.
  */
 int fmoe_check_device_status(void* stream);
 

@@ -19,7 +19,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, fp8, q):
+def _worker(rank, world, port, fp8, p2p, q):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -47,24 +47,32 @@ def _worker(rank, world, port, fp8, q):
         T = 300 if rank == 0 else 77
         x = torch.randn(T, H, generator=g2).bfloat16().to(dev)
         logits = torch.randn(T, E, generator=g2).to(dev)
-        out = ep.ep_fused_moe(x, w1[lo:hi].contiguous(), w2[lo:hi].contiguous(), logits, k, E, True, **kw_loc)
+        # p2p: rows stored into the peers' IPC-mapped receive areas by this package's kernels; else NCCL all-to-all
+        xc = ep.PeerExchange(None, 300, k, H) if p2p else None
         ref = fg.fused_moe(x, w1, w2, logits, k, True, **kw_full)
-        torch.cuda.synchronize()
-        _C.check_device_status(dev)
-        err = float((out.float() - ref.float()).norm() / ref.float().norm())
+        err = 0.0
+        for _ in range(3 if p2p else 1):  # repeated calls reuse the receive areas
+            out = ep.ep_fused_moe(x, w1[lo:hi].contiguous(), w2[lo:hi].contiguous(), logits, k, E, True, exchange=xc,
+                                  **kw_loc)
+            torch.cuda.synchronize()
+            _C.check_device_status(dev)
+            err = max(err, float((out.float() - ref.float()).norm() / ref.float().norm()))
+        if xc is not None:
+            xc.close()
         q.put((rank, err))
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("p2p", [False, True])
 @pytest.mark.parametrize("fp8", [False, True])
-def test_ep_two_gpus_matches_single_gpu(fp8):
+def test_ep_two_gpus_matches_single_gpu(fp8, p2p):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, fp8, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, fp8, p2p, q)) for r in range(2)]
     for p in procs:
         p.start()
     res = sorted(q.get(timeout=300) for _ in range(2))

@@ -40,7 +40,7 @@ class GemmArgs(Structure):
         ("sorted_cap", c_int64), ("max_blocks", c_int64),
         ("a", c_void_p), ("a_scale", c_void_p), ("w", c_void_p), ("w_scale", c_void_p),
         ("sorted_token_ids", c_void_p), ("expert_ids", c_void_p), ("num_tokens_post_padded", c_void_p),
-        ("row_scale", c_void_p), ("out", c_void_p), ("out_scale", c_void_p),
+        ("row_scale", c_void_p), ("out", c_void_p), ("out_scale", c_void_p), ("out_rows", c_void_p),
     ]
 
 
@@ -55,7 +55,7 @@ class FusedArgs(Structure):
         ("routed_scaling_factor", c_float), ("reserved_f", c_float),
         ("hidden", c_void_p), ("w1", c_void_p), ("w2", c_void_p), ("w1_scale", c_void_p), ("w2_scale", c_void_p),
         ("topk_weights", c_void_p), ("topk_ids", c_void_p), ("out", c_void_p), ("workspace", c_void_p),
-        ("workspace_bytes", c_int64),
+        ("workspace_bytes", c_int64), ("out_rows", c_void_p),
     ]
 
 
@@ -91,7 +91,8 @@ SIGNATURES = {
     "fmoe_ep_route": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "fmoe_ep_dispatch": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
-    "fmoe_ep_mask_tail": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p]),
+    "fmoe_ep_mask_tail": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64,
+                                  c_void_p, c_void_p]),
     "fmoe_ep_combine": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
                                 c_void_p, c_void_p]),
     "fmoe_selftest_bounded_wait": (c_int, [c_int64, c_void_p]),

@@ -21,8 +21,12 @@ int validate_gemm(const GemmParams& a, bool gated, const char* who) {
                "%s: max_blocks*block_size (%lld) exceeds sorted_cap (%lld)", who,
                (long long)(a.max_blocks * a.block_size), (long long)a.sorted_cap);
   if (a.max_blocks == 0 || a.numel == 0) return FMOE_OK;
-  FMOE_REQUIRE(a.a && a.w && a.out && a.sorted_token_ids && a.expert_ids && a.num_tokens_post_padded,
+  FMOE_REQUIRE(a.a && a.w && (a.out || (!gated && a.out_rows)) && a.sorted_token_ids && a.expert_ids &&
+                   a.num_tokens_post_padded,
                "%s: null pointer", who);
+  if (a.out_rows)
+    FMOE_REQUIRE(!gated && (a.variant == FMOE_VARIANT_STREAM || a.variant == FMOE_VARIANT_TCGEN05),
+                 "%s: out_rows is taken by gemm2 with the STREAM or TCGEN05 variant only", who);
   if (a.dtype == FMOE_E4M3) {
     FMOE_REQUIRE(a.a_scale && a.w_scale, "%s: e4m3 needs a_scale and w_scale", who);
     FMOE_REQUIRE(a.k % 128 == 0 && a.n % 128 == 0, "%s: e4m3 needs k and n to be multiples of 128", who);
@@ -33,7 +37,6 @@ int validate_gemm(const GemmParams& a, bool gated, const char* who) {
   else
     FMOE_REQUIRE(a.a_rows * a.top_k >= a.numel, "%s: a has %lld rows but numel/top_k needs more", who,
                  (long long)a.a_rows);
-  (void)gated;
   return FMOE_OK;
 }
 

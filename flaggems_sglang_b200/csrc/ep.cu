@@ -9,8 +9,10 @@
 //
 //   fmoe_ep_route      dest rank of every (token, slot) pair + rows per destination
 //   fmoe_ep_dispatch   row p of the destination-sorted order -> peer dest, at the offset the count matrix gives
-//   fmoe_ep_mask_tail  receive-area ids past the received rows := -1 (ignored by moe_align_block_size)
-//   fmoe_ep_combine    expert output row r -> z[slot] of the rank that sent row r
+//   fmoe_ep_mask_tail  receive-area ids past the received rows := -1 (ignored by moe_align_block_size); optionally
+//                      the table of return addresses that lets the down-projection epilogue store its rows
+//                      straight into the source ranks' z (fmoe_gemm_args.out_rows)
+//   fmoe_ep_combine    expert output row r -> z[slot] of the rank that sent row r (when the GEMM did not)
 //
 // The reference has no expert parallelism (expert_map is asserted None,
 // FlagGems-sglang src/flaggems_sglang/ops/fused_moe.py:176-178).
@@ -104,11 +106,20 @@ __device__ __forceinline__ int64_t rows_received(const int32_t* matrix, int rank
 
 __global__ void __launch_bounds__(256)
 ep_mask_tail_kernel(int32_t* __restrict__ recv_ids, const int32_t* __restrict__ matrix, int rank, int world,
-                    int64_t capacity) {
+                    int64_t capacity, const int2* __restrict__ recv_src, int64_t z_slots,
+                    uint8_t* const* __restrict__ peer_z, int64_t row_bytes, void** __restrict__ out_rows) {
   const int64_t total = min(rows_received(matrix, rank, world), capacity);
-  for (int64_t r = total + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < capacity;
-       r += (int64_t)gridDim.x * blockDim.x)
-    recv_ids[r] = -1;
+  for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < capacity; r += (int64_t)gridDim.x * blockDim.x) {
+    if (r >= total) {
+      recv_ids[r] = -1;
+      if (out_rows) out_rows[r] = nullptr;
+    } else if (out_rows) {
+      const int2 s = recv_src[r];
+      const bool ok = s.x >= 0 && s.x < world && s.y >= 0 && s.y < z_slots;
+      if (!ok) report_ep(0xA02);
+      out_rows[r] = ok ? peer_z[s.x] + (int64_t)s.y * row_bytes : nullptr;
+    }
+  }
 }
 
 __global__ void __launch_bounds__(256)
@@ -212,13 +223,19 @@ extern "C" int fmoe_ep_dispatch(const void* hidden, int elem_bytes, int64_t T, i
 }
 
 extern "C" int fmoe_ep_mask_tail(int32_t* recv_ids, const int32_t* matrix, int rank, int world, int64_t capacity,
-                                 void* stream) {
+                                 const void* recv_src, int64_t z_slots, void* const* peer_z, int64_t row_bytes,
+                                 void** out_rows, void* stream) {
   using namespace fmoe;
   FMOE_REQUIRE(world >= 1 && world <= kMaxWorld && rank >= 0 && rank < world, "ep_mask_tail: bad rank %d of %d", rank, world);
   if (capacity <= 0) return FMOE_OK;
   FMOE_REQUIRE(recv_ids && matrix, "ep_mask_tail: null pointer");
+  if (out_rows)
+    FMOE_REQUIRE(recv_src && peer_z && row_bytes > 0 && row_bytes % 16 == 0 && z_slots >= 0,
+                 "ep_mask_tail: out_rows needs recv_src, peer_z and a row size that is a multiple of 16 bytes");
   const unsigned grid = (unsigned)std::min<int64_t>(ceil_div<int64_t>(capacity, 256), 148 * 4);
-  ep_mask_tail_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(recv_ids, matrix, rank, world, capacity);
+  ep_mask_tail_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(recv_ids, matrix, rank, world, capacity,
+                                                              (const int2*)recv_src, z_slots,
+                                                              (uint8_t* const*)peer_z, row_bytes, out_rows);
   return launch_status("ep_mask_tail_kernel");
 }
 

@@ -114,7 +114,12 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
 
 int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* stream) {
   if (a.T == 0) return FMOE_OK;
-  FMOE_REQUIRE(a.hidden && a.w1 && a.w2 && a.topk_weights && a.topk_ids && a.out, "fused_experts: null pointer");
+  FMOE_REQUIRE(a.hidden && a.w1 && a.w2 && a.topk_weights && a.topk_ids && (a.out || a.out_rows), "fused_experts: null pointer");
+  if (a.out_rows) {
+    FMOE_REQUIRE(a.no_combine && !a.zero_dropped, "fused_experts: out_rows needs no_combine = 1 and zero_dropped = 0");
+    if (p.variant != FMOE_VARIANT_STREAM && p.variant != FMOE_VARIANT_TCGEN05)
+      return fail(FMOE_ERR_UNSUPPORTED, "fused_experts: out_rows is taken by the STREAM and TCGEN05 kernels only");
+  }
   const bool fp8 = a.dtype == FMOE_E4M3;
   const bool tc = p.variant == FMOE_VARIANT_TCGEN05 || p.variant == FMOE_VARIANT_TCGEN05_PAIR;
   if (fp8) FMOE_REQUIRE(a.w1_scale && a.w2_scale, "fused_experts: e4m3 needs w1_scale and w2_scale");
@@ -155,6 +160,7 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
   g2.k = a.I;
   g2.w = a.w2;
   g2.out = z;
+  g2.out_rows = a.out_rows;
   g2.a_gather = 0;
   g2.a_rows = p.cap;
   g2.row_scale = a.apply_router_weight_on_input ? nullptr : a.topk_weights;

@@ -1,6 +1,8 @@
 // Internal interface between the C-ABI entry points (api.cu) and the three
 // grouped-GEMM kernel families.
 #pragma once
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace fmoe {
@@ -76,9 +78,13 @@ struct TileCursor {
 };
 // Row blocks per group: the group's A rows should stay around 16 MB.
 inline int pick_group_m(int64_t block_rows, int64_t k_bytes_per_row) {
+  if (const char* env = getenv("FMOE_TC_GROUP_M")) {  // tuning aid
+    const int g = atoi(env);
+    if (g >= 1 && g <= 1024) return g;
+  }
   const int64_t per_block = block_rows * k_bytes_per_row;
   int64_t g = (16ll << 20) / (per_block > 0 ? per_block : 1);
-  return (int)(g < 4 ? 4 : (g > 64 ? 64 : g));
+  return (int)(g < 8 ? 8 : (g > 64 ? 64 : g));
 }
 
 // device status word written by bounded waits (gemm_tcgen05.cu)

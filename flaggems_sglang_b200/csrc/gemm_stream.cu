@@ -43,8 +43,11 @@ __device__ __forceinline__ void mma_e4m3_16832(float (&d)[4], uint32_t a0, uint3
 // A work item is (token block b, slab pair s); W = 1, 2, 4 or 8 warps share an item and split its K
 // range (interleaved 128-k chunks).  W is chosen by the host so that the launch has enough warps to
 // keep HBM busy; with W == 1 a warp owns its item end to end and the CTA never synchronises.
+// CTAs per SM the register allocation must allow: the kernel hides HBM latency with resident warps
+constexpr int min_ctas(int eb, int ntg) { return (ntg == 1 || (ntg == 2 && eb == 2)) ? 2 : 1; }
+
 template <int EB, int NTG, bool GATED, typename OutT>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, min_ctas(EB, NTG))
 grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
   constexpr int BM = 8 * NTG;
   constexpr int U = (EB == 2) ? 4 : 2;      // 64-byte steps per 128-k chunk
@@ -122,16 +125,52 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
         sw_ptr[rt] = p.w_scale + ((int64_t)e * (w_rows / 128) + min(slab_row0[rt], w_rows - 1) / 128) * kblocks;
     }
 
-    for (int64_t chunk = part; chunk < kblocks; chunk += W) {
-      const int64_t boff = chunk * 128 * EB;  // byte offset of the chunk inside a row
-      uint4 wq[RT][U][2];
+    // The W fragments of a chunk live in registers; as soon as the MMAs of one 64-byte step have consumed
+    // theirs, the same registers are reloaded with that step of the warp's NEXT chunk, so loads stay in
+    // flight while the rest of the chunk is computed (a warp that loaded a whole chunk, waited and then
+    // computed kept HBM busy only half of the time).  The block scales of the next chunk travel the same way.
+    uint4 wq[RT][U][2];
+    float sw_c[RT], sa_c[NTG][2];
+    // wptr walks one chunk ahead of xptr: it always points at the chunk whose fragments are loaded next
+    const int64_t step = (int64_t)W * 128 * EB;
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) wptr[rt][h] += (int64_t)part * 128 * EB;
+#pragma unroll
+    for (int q = 0; q < NTG; ++q)
+      if (xptr[q]) xptr[q] += (int64_t)part * 128 * EB;
+    auto load_w_step = [&](int u) {
 #pragma unroll
       for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
-        for (int u = 0; u < U; ++u)
+        for (int h = 0; h < 2; ++h) wq[rt][u][h] = ldg_stream_v4(wptr[rt][h] + u * 64);
+    };
+    auto load_scales = [&](int64_t chunk) {
+      if constexpr (EB == 1) {
 #pragma unroll
-          for (int h = 0; h < 2; ++h) wq[rt][u][h] = ldg_stream_v4(wptr[rt][h] + boff + u * 64);
-
+        for (int rt = 0; rt < RT; ++rt) sw_c[rt] = sw_ptr[rt][chunk];
+#pragma unroll
+        for (int q = 0; q < NTG; ++q)
+#pragma unroll
+          for (int j = 0; j < 2; ++j) sa_c[q][j] = sa_ptr[q][j] ? sa_ptr[q][j][chunk] : 0.f;
+      }
+    };
+    auto bump_w = [&]() {
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) wptr[rt][h] += step;
+    };
+    if (part < kblocks) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) load_w_step(u);
+      load_scales(part);
+      bump_w();
+    }
+#pragma unroll 1
+    for (int64_t chunk = part; chunk < kblocks; chunk += W) {
+      const bool has_next = chunk + W < kblocks;
       float part_acc[RT][NTG][4];
       if constexpr (EB == 1) {
 #pragma unroll
@@ -145,7 +184,7 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
       for (int u = 0; u < U; ++u) {
 #pragma unroll
         for (int q = 0; q < NTG; ++q) {
-          uint4 xq = xptr[q] ? ldg_cached_v4(xptr[q] + boff + u * 64) : make_uint4(0, 0, 0, 0);
+          uint4 xq = xptr[q] ? ldg_cached_v4(xptr[q] + u * 64) : make_uint4(0, 0, 0, 0);
 #pragma unroll
           for (int rt = 0; rt < RT; ++rt) {
             if constexpr (EB == 2) {
@@ -157,22 +196,27 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
             }
           }
         }
+        if (has_next) load_w_step(u);
       }
+      bump_w();
+#pragma unroll
+      for (int q = 0; q < NTG; ++q)
+        if (xptr[q]) xptr[q] += step;
       if constexpr (EB == 1) {
         // acc += partial * (activation scale of the token) * (weight scale of the slab) for this 128-k block
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt) {
-          const float sw = sw_ptr[rt][chunk];
 #pragma unroll
           for (int q = 0; q < NTG; ++q) {
-            const float s0 = sa_ptr[q][0] ? sa_ptr[q][0][chunk] * sw : 0.f;
-            const float s1 = sa_ptr[q][1] ? sa_ptr[q][1][chunk] * sw : 0.f;
+            const float s0 = sa_c[q][0] * sw_c[rt];
+            const float s1 = sa_c[q][1] * sw_c[rt];
             acc[rt][q][0] = fmaf(part_acc[rt][q][0], s0, acc[rt][q][0]);
             acc[rt][q][1] = fmaf(part_acc[rt][q][1], s1, acc[rt][q][1]);
             acc[rt][q][2] = fmaf(part_acc[rt][q][2], s0, acc[rt][q][2]);
             acc[rt][q][3] = fmaf(part_acc[rt][q][3], s1, acc[rt][q][3]);
           }
         }
+        if (has_next) load_scales(chunk + W);
       }
     }
   }
@@ -214,12 +258,14 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
           out[(b * BM + q * 8 + 2 * t + (i & 1)) * p.n + n0 + col] =
               from_f32<OutT>(act_mul(acc[0][q][i] * rs, acc[1][q][i] * rs, p.activation));
       } else {
+        OutT* orow = p.out_rows ? reinterpret_cast<OutT*>(p.out_rows[slot]) : out + (int64_t)slot * p.n;
+        if (!orow) continue;
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt)
-          if (n0 + rt * 16 + col < p.n)
-            out[(int64_t)slot * p.n + n0 + rt * 16 + col] = from_f32<OutT>(acc[rt][q][i] * rs);
+          if (n0 + rt * 16 + col < p.n) orow[n0 + rt * 16 + col] = from_f32<OutT>(acc[rt][q][i] * rs);
       }
     }
+  if (p.out_rows) __threadfence_system();  // rows stored to a peer are complete before the kernel ends
 }
 
 // Warps per item: enough warps in flight to cover HBM latency, but at least two 128-k chunks per warp.

@@ -55,6 +55,7 @@ struct TcParams {
   const int32_t* num_tokens_post_padded;
   const float* row_scale;
   void* out;
+  void* const* out_rows;  // down projection: optional per-slot row addresses (may be peer memory)
   int64_t numel;
   int64_t n;           // gemm1: I, gemm2: H
   int64_t w_rows;      // rows of W per expert
@@ -323,14 +324,16 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           }
         }
       } else {
-        __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)(valid ? slot : 0) * p.n +
-                              (int64_t)n_tile * 256;
+        __nv_bfloat16* obase = !valid ? nullptr
+                               : p.out_rows ? reinterpret_cast<__nv_bfloat16*>(p.out_rows[slot])
+                                            : reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)slot * p.n;
+        __nv_bfloat16* orow = obase + (int64_t)n_tile * 256;
 #pragma unroll 1
         for (int c = 0; c < 8; ++c) {
           uint32_t r[32];
           ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
           ptx::tmem_ld_wait();
-          if (valid && (int64_t)n_tile * 256 + c * 32 < p.n) {
+          if (obase && (int64_t)n_tile * 256 + c * 32 < p.n) {
             uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -350,6 +353,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       ptx::mbar_arrive(&acc_empty[acc]);
       if (p.profile) prof_busy += clock64() - te1;
     }
+    if (p.out_rows) __threadfence_system();  // rows stored to a peer are complete before the kernel ends
     if (p.profile && threadIdx.x == 0 && blockIdx.x < 256) {
       g_wait_prof[blockIdx.x * 8 + 4] = prof_wait;
       g_wait_prof[blockIdx.x * 8 + 5] = prof_busy;
@@ -441,6 +445,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.num_tokens_post_padded = g.num_tokens_post_padded;
   p.row_scale = g.row_scale;
   p.out = g.out;
+  p.out_rows = GATED ? nullptr : g.out_rows;
   p.numel = g.numel;
   p.n = g.n;
   p.w_rows = w_rows;
@@ -470,7 +475,7 @@ bool gemm_tcgen05_supports(const GemmParams& p, bool gated) {
   if (p.a_gather && (!gated || p.top_k < 1 || !aligned16(p.sorted_token_ids))) return false;
   if (p.k <= 0 || (p.k * 2) % 16 != 0) return false;            // TMA row stride must be a multiple of 16 bytes
   if (p.n <= 0 || p.n % (gated ? 128 : 32) != 0) return false;  // gate/up pairing; 64-byte epilogue stores
-  if (!aligned16(p.a) || !aligned16(p.w) || !aligned16(p.out)) return false;
+  if (!aligned16(p.a) || !aligned16(p.w) || !(aligned16(p.out) && (p.out || (!gated && p.out_rows)))) return false;
   if ((int64_t)p.num_experts * (gated ? 2 * p.n : p.n) >= (1ll << 31) || p.a_rows >= (1ll << 31)) return false;
   if (p.max_blocks >= (1ll << 24)) return false;
   return true;

@@ -44,6 +44,7 @@ struct Fp8Params {
   const float* a_scale;  // [a_rows, kblocks]
   const float* w_scale;  // [E, w_rows/128, kblocks]
   void* out;
+  void* const* out_rows;  // down projection: optional per-slot row addresses (may be peer memory)
   int64_t numel;
   int64_t n;
   int64_t w_rows;
@@ -285,9 +286,11 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
         }
       } else {
         const int64_t colg = (int64_t)n_tile * 256 + 64 * cpart;
-        if (valid && colg < p.n) {
-          __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)slot * p.n + colg;
-          uint4* dst = reinterpret_cast<uint4*>(orow);
+        __nv_bfloat16* obase = !valid ? nullptr
+                               : p.out_rows ? reinterpret_cast<__nv_bfloat16*>(p.out_rows[slot])
+                                            : reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)slot * p.n;
+        if (obase && colg < p.n) {
+          uint4* dst = reinterpret_cast<uint4*>(obase + colg);
 #pragma unroll
           for (int v = 0; v < 8; ++v) {
             uint32_t w[4];
@@ -303,6 +306,7 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     }
   }
 
+  if (p.out_rows) __threadfence_system();  // rows stored to a peer are complete before the kernel ends
   ptx::tc_fence_before_sync();
   __syncthreads();
   if (warp == kEpiWarps + 1) {
@@ -348,6 +352,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.a_scale = g.a_scale;
   p.w_scale = g.w_scale;
   p.out = g.out;
+  p.out_rows = GATED ? nullptr : g.out_rows;
   p.numel = g.numel;
   p.n = g.n;
   p.w_rows = w_rows;
@@ -373,7 +378,7 @@ bool gemm_tcgen05_fp8_supports(const GemmParams& p, bool gated) {
   if (p.block_size != BM || p.a_gather) return false;
   if (p.k <= 0 || p.k % 128 != 0 || p.n <= 0 || p.n % 128 != 0) return false;
   if (!p.a_scale || !p.w_scale) return false;
-  if (!aligned16(p.a) || !aligned16(p.w) || !aligned16(p.out)) return false;
+  if (!aligned16(p.a) || !aligned16(p.w) || !(aligned16(p.out) && (p.out || (!gated && p.out_rows)))) return false;
   if ((int64_t)p.num_experts * (gated ? 2 * p.n : p.n) >= (1ll << 31) || p.a_rows >= (1ll << 31)) return false;
   if (p.max_blocks >= (1ll << 24)) return false;
   return true;

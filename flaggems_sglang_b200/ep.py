@@ -24,6 +24,7 @@ unchanged on CPU ranks (gloo) in the tests, where the backend is the CPU oracle.
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -180,6 +181,8 @@ class PeerExchange:
     # -- shared with the single-process emulation used by the tests -------------------------------------
     def _layout(self, max_tokens, top_k, hidden_size, dtype, capacity):
         self.max_tokens, self.top_k, self.H, self.dtype = int(max_tokens), int(top_k), int(hidden_size), dtype
+        # result rows go back from inside the down-projection kernel (False: a separate copy kernel, for A/B timing)
+        self.fuse_return = os.environ.get("FMOE_EP_FUSE_RETURN", "1") != "0"
         eb = torch.empty(0, dtype=dtype).element_size()
         if (self.H * eb) % 16:
             raise ValueError("hidden rows must be a multiple of 16 bytes")
@@ -285,28 +288,38 @@ def p2p_send(xc: PeerExchange, state: dict, matrix: torch.Tensor) -> None:
         _C.stream_ptr(x.device)))
 
 
-def p2p_experts(xc: PeerExchange, state: dict, w1_local, w2_local, **expert_kwargs) -> torch.Tensor:
+def p2p_experts(xc: PeerExchange, state: dict, w1_local, w2_local, fuse_return: bool = True,
+                **expert_kwargs) -> Optional[torch.Tensor]:
     """Phase 3 (after the barrier): grouped GEMMs over the receive area; rows past the received count carry
-    id -1 and are skipped by moe_align_block_size."""
+    id -1 and are skipped by moe_align_block_size.  With `fuse_return` (and a kernel family that takes row
+    addresses) the down-projection epilogue stores every result row straight into the slot buffer of the
+    rank the row came from, and None is returned; otherwise the rows come back for `p2p_return`."""
     from . import _C
     from .ops.fused_moe import _pick_variant, fused_experts
 
     dev = xc.rows.device
+    fp8 = expert_kwargs.get("use_fp8_w8a8", False)
+    # kernel family for the rows a balanced routing would bring (this rank's own count), not for the capacity
+    name, _ = _pick_variant(torch.float8_e4m3fn if fp8 else w1_local.dtype, max(state["T"] * state["k"], 1),
+                            w1_local.shape[0], w2_local.shape[2], xc.H, expert_kwargs.get("variant"))
+    expert_kwargs = dict(expert_kwargs, variant=name)
+    fuse_return = fuse_return and name in ("stream", "tcgen05")
+    out_rows = torch.empty(xc.capacity, dtype=torch.int64, device=dev) if fuse_return else None
     _C.check(_C.lib().fmoe_ep_mask_tail(xc.ids.data_ptr(), state["matrix"].data_ptr(), xc.rank, xc.world, xc.capacity,
-                                        _C.stream_ptr(dev)))
-    if "variant" not in expert_kwargs:
-        # kernel family for the rows a balanced routing would bring (this rank's own count), not for the capacity
-        fp8 = expert_kwargs.get("use_fp8_w8a8", False)
-        name, _ = _pick_variant(torch.float8_e4m3fn if fp8 else w1_local.dtype, max(state["T"] * state["k"], 1),
-                                w1_local.shape[0], w2_local.shape[2], xc.H, None)
-        expert_kwargs = dict(expert_kwargs, variant=name)
-    return fused_experts(xc.rows, w1_local, w2_local, xc.weights.view(-1, 1), xc.ids.view(-1, 1), no_combine=True,
-                         **expert_kwargs).view(xc.capacity, xc.H)
+                                        xc.src.data_ptr(), xc.z_slots, xc.ptrs["z"].data_ptr(),
+                                        xc.H * xc.rows.element_size(), _C.ptr(out_rows), _C.stream_ptr(dev)))
+    z = fused_experts(xc.rows, w1_local, w2_local, xc.weights.view(-1, 1), xc.ids.view(-1, 1), no_combine=True,
+                      out_rows=out_rows, **expert_kwargs)
+    return None if fuse_return else z.view(xc.capacity, xc.H)
 
 
-def p2p_return(xc: PeerExchange, state: dict, z_rows: torch.Tensor) -> None:
-    """Phase 4: store every expert output row into the slot buffer of the rank it came from."""
+def p2p_return(xc: PeerExchange, state: dict, z_rows: Optional[torch.Tensor]) -> None:
+    """Phase 4: store every expert output row into the slot buffer of the rank it came from (nothing to do
+    when the down projection already did)."""
     from . import _C
+
+    if z_rows is None:
+        return
 
     _C.check(_C.lib().fmoe_ep_combine(z_rows.data_ptr(), z_rows.element_size(), xc.H, xc.src.data_ptr(),
                                       state["matrix"].data_ptr(), xc.rank, xc.world, xc.capacity, xc.z_slots,
@@ -361,7 +374,8 @@ def ep_fused_experts(
             p2p_send(exchange, state, matrix)
             exchange.barrier()
         with _phase("experts", True):
-            z_rows = p2p_experts(exchange, state, w1_local, w2_local, **expert_kwargs)
+            z_rows = p2p_experts(exchange, state, w1_local, w2_local, fuse_return=exchange.fuse_return,
+                                 **expert_kwargs)
         with _phase("combine", True):
             p2p_return(exchange, state, z_rows)
             exchange.barrier()

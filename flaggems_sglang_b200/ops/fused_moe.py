@@ -150,6 +150,7 @@ def fused_experts(
     expert_map: Optional[torch.Tensor] = None,
     global_num_experts: int = -1,
     variant: Optional[str] = None,
+    out_rows: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """Expert computation for already-routed tokens.
 
@@ -160,6 +161,9 @@ def fused_experts(
     (activations are quantised per token per 128 channels on the fly).
     Returns [T,H] (or [T,k,H] with `no_combine`).  `expert_map` maps global to
     local expert ids (-1 = not on this rank; such slots contribute zeros).
+    `out_rows` (with `no_combine`): int64 [T*k] device addresses; the result row of every slot is stored
+    there by the down-projection kernel instead of into a [T,k,H] tensor (0 = skip), and None is returned.
+    Used by the expert-parallel path, whose addresses are slot rows in the source ranks' memory.
     """
     logger.debug("FLAGGEMS_SGLANG_B200 FUSED_EXPERTS")
     assert inplace is False, "Inplace is not supported"
@@ -203,8 +207,11 @@ def fused_experts(
         ids = expert_map.to(torch.int32)[topk_ids.long()]
     ids = ids.to(torch.int32).contiguous()
 
+    if out_rows is not None:
+        assert no_combine and expert_map is None, "out_rows needs no_combine and no expert_map"
+        assert out_rows.dtype == torch.int64 and out_rows.numel() >= numel and out_rows.is_contiguous()
     if T == 0:
-        return x.new_empty((0, k, H) if no_combine else (0, H))
+        return None if out_rows is not None else x.new_empty((0, k, H) if no_combine else (0, H))
 
     lib = _C.lib()
     st = _C.stream_ptr(dev)
@@ -213,14 +220,16 @@ def fused_experts(
         forced = variant or os.environ.get("FMOE_VARIANT") or "auto"
         if forced not in _C.VARIANTS:
             raise ValueError(f"unknown variant {forced!r}")
-        out = torch.empty((T, k, H) if no_combine else (T, H), dtype=out_dtype, device=dev)
+        out = None if out_rows is not None else torch.empty((T, k, H) if no_combine else (T, H), dtype=out_dtype,
+                                                            device=dev)
         fa = _C.FusedArgs(
             dtype=_C.E4M3 if use_fp8_w8a8 else _C.DTYPE_CODE[out_dtype], variant=_C.VARIANTS[forced], num_experts=E,
             top_k=k, apply_router_weight_on_input=int(apply_router_weight_on_input), no_combine=int(no_combine),
             zero_dropped=int(expert_map is not None), activation=_C.ACTIVATIONS[activation], T=T, H=H, I=I,
             routed_scaling_factor=1.0 if routed_scaling_factor is None else float(routed_scaling_factor),
             hidden=x.data_ptr(), w1=w1.data_ptr(), w2=w2.data_ptr(), w1_scale=_C.ptr(w1_scale),
-            w2_scale=_C.ptr(w2_scale), topk_weights=wts.data_ptr(), topk_ids=ids.data_ptr(), out=out.data_ptr())
+            w2_scale=_C.ptr(w2_scale), topk_weights=wts.data_ptr(), topk_ids=ids.data_ptr(), out=_C.ptr(out),
+            out_rows=_C.ptr(out_rows))
         need = lib.fmoe_fused_experts_workspace_bytes(fa)
         if need < 0:
             _C.check(_C.ERR_INVALID_ARG)
@@ -245,7 +254,8 @@ def fused_experts(
 
     # Z holds one output row per flat slot; slots that no kernel writes (dropped ids) must read as zero
     z_alloc = torch.zeros if expert_map is not None else torch.empty
-    z = z_alloc((numel, H), dtype=out_dtype, device=dev)
+    z = None if out_rows is not None else z_alloc((numel, H), dtype=out_dtype, device=dev)
+    z_args = dict(out=_C.ptr(z), out_rows=_C.ptr(out_rows))
 
     if not use_fp8_w8a8:
         if name == "tcgen05_pair" or (name == "tcgen05" and not os.environ.get("FMOE_TC_GATHER4")):
@@ -265,7 +275,7 @@ def fused_experts(
             _C.check(lib.fmoe_gemm1_silu(g1, st))
         g2 = _gemm_args(dtype=code, out_dtype=code, a_gather=0, n=H, k=I, a_rows=cap, a=act.data_ptr(),
                         w=w2.data_ptr(), row_scale=None if apply_router_weight_on_input else row_w,
-                        out=z.data_ptr(), **common)
+                        **z_args, **common)
         with _stage("gemm2_" + name):
             _C.check(lib.fmoe_gemm2(g2, st))
     else:
@@ -309,10 +319,12 @@ def fused_experts(
                                                  aq.data_ptr(), asc.data_ptr(), st))
         g2 = _gemm_args(dtype=_C.E4M3, out_dtype=_C.BF16, a_gather=0, n=H, k=I, a_rows=cap, a=aq.data_ptr(),
                         a_scale=asc.data_ptr(), w=w2.data_ptr(), w_scale=w2_scale.data_ptr(),
-                        row_scale=None if apply_router_weight_on_input else row_w, out=z.data_ptr(), **common)
+                        row_scale=None if apply_router_weight_on_input else row_w, **z_args, **common)
         with _stage("gemm2_fp8_" + name):
             _C.check(lib.fmoe_gemm2(g2, st))
 
+    if out_rows is not None:
+        return None
     if no_combine:
         return z.view(T, k, H)
     out = torch.empty((T, H), dtype=out_dtype, device=dev)

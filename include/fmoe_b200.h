@@ -164,6 +164,10 @@ typedef struct fmoe_gemm_args {
   const float* row_scale; /* [numel] top-k weights by flat slot, or NULL                 */
   void* out;           /* gemm1: [sorted_cap, I] in sorted order; gemm2: [numel, H] by slot */
   float* out_scale;    /* gemm1 with out_dtype e4m3: [sorted_cap, I/128]                 */
+  void* const* out_rows; /* gemm2, optional: DEVICE array [numel] of row addresses; row `slot` is written
+                            at out_rows[slot] instead of out + slot*H (NULL entry: row skipped).  The
+                            addresses may be peer memory (expert-parallel combine fused into the
+                            epilogue).  STREAM and TCGEN05 variants only.                          */
 } fmoe_gemm_args;
 
 /* gemm1: out[p, c] = act(acc[p, c]) * acc[p, I + c], acc = (a_row(p) . w[e(p)]^T) * row_scale. */
@@ -211,6 +215,8 @@ typedef struct fmoe_fused_args {
   void* out;            /* [T,H] or [T,k,H]                                                               */
   void* workspace;      /* 256-byte aligned                                                               */
   int64_t workspace_bytes;
+  void* const* out_rows; /* with no_combine: optional DEVICE array [T*k] of row addresses that replace
+                            out + slot*H (see fmoe_gemm_args.out_rows); `out` may then be NULL            */
 } fmoe_fused_args;
 
 /* Kernel family and moe_align block the AUTO choice takes for a shape.  forced_variant may be AUTO. */
@@ -261,7 +267,7 @@ int fmoe_fused_experts_static(const fmoe_fused_args* args, void* stream);
  *   fmoe_ep_route -> sort by dest (fmoe_moe_align_block_size, block 1, E = world) -> all-gather of `counts` into
  *   matrix[world*world] (matrix[i*world+j] = rows i sends to j) -> fmoe_ep_dispatch -> barrier ->
  *   fmoe_ep_mask_tail -> expert computation over the receive area (top_k = 1, ids = -1 rows are skipped) ->
- *   fmoe_ep_combine -> barrier -> fmoe_moe_sum over this rank's z.
+ *   fmoe_ep_combine (or none: out_rows of fmoe_ep_mask_tail) -> barrier -> fmoe_moe_sum over this rank's z.
  *
  * Misuse that only the device can see (an expert id outside [0, world*experts_per_rank), a row beyond
  * `capacity`, a corrupt return address) is skipped, recorded, and returned by fmoe_check_device_status as
@@ -282,9 +288,13 @@ int fmoe_ep_dispatch(const void* hidden, int elem_bytes, int64_t T, int64_t H, i
                      const int32_t* matrix, int rank, int world, int experts_per_rank,
                      void* const* peer_rows, int32_t* const* peer_ids, float* const* peer_weights,
                      void* const* peer_src, int64_t capacity, void* stream);
-/* recv_ids[r] = -1 for r >= rows received (sum of column `rank` of the matrix). */
+/* recv_ids[r] = -1 for r >= rows received (sum of column `rank` of the matrix).  With out_rows != NULL also
+ * out_rows[r] = peer_z[src[r].rank] + src[r].slot * row_bytes for the received rows (NULL past them): the
+ * table fmoe_gemm_args.out_rows takes, which makes the down-projection epilogue store every result row
+ * straight into the slot buffer of the rank it came from (no fmoe_ep_combine pass). */
 int fmoe_ep_mask_tail(int32_t* recv_ids, const int32_t* matrix, int rank, int world, int64_t capacity,
-                      void* stream);
+                      const void* recv_src, int64_t z_slots, void* const* peer_z, int64_t row_bytes,
+                      void** out_rows, void* stream);
 /* z_rows[r] (expert output of received row r) -> peer_z[src[r].rank] + src[r].slot * H. */
 int fmoe_ep_combine(const void* z_rows, int elem_bytes, int64_t H, const void* recv_src,
                     const int32_t* matrix, int rank, int world, int64_t capacity, int64_t z_slots,

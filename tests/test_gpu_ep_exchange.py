@@ -18,7 +18,8 @@ def _layer(E, H, I, seed):
     return w1, w2
 
 
-def _run_emulated(fg, ep, world, tokens, E, H, k, w1, w2, kw_of_rank, capacity=None, rsf=None, bad_id=False):
+def _run_emulated(fg, ep, world, tokens, E, H, k, w1, w2, kw_of_rank, capacity=None, rsf=None, bad_id=False,
+                  fuse=True):
     el = E // world
     xcs = ep.PeerExchange.emulated(world, max(max(tokens), 1), k, H, torch.bfloat16, capacity=capacity)
     xs, states = [], []
@@ -34,7 +35,8 @@ def _run_emulated(fg, ep, world, tokens, E, H, k, w1, w2, kw_of_rank, capacity=N
     for r in range(world):
         ep.p2p_send(xcs[r], states[r], matrix)
     zs = [ep.p2p_experts(xcs[r], states[r], w1[r * el:(r + 1) * el].contiguous(), w2[r * el:(r + 1) * el].contiguous(),
-                         **kw_of_rank(r)) for r in range(world)]
+                         fuse_return=fuse, **kw_of_rank(r)) for r in range(world)]
+    assert all((z is None) == fuse for z in zs)
     for r in range(world):
         ep.p2p_return(xcs[r], states[r], zs[r])
     outs = [ep.p2p_finish(xcs[r], states[r], rsf) for r in range(world)]
@@ -42,14 +44,15 @@ def _run_emulated(fg, ep, world, tokens, E, H, k, w1, w2, kw_of_rank, capacity=N
     return xs, outs, matrix, xcs
 
 
+@pytest.mark.parametrize("fuse", [True, False], ids=["gemm2_stores_to_peer", "separate_combine"])
 @pytest.mark.parametrize("world,tokens", [(4, [300, 77, 1, 0]), (2, [64, 64]), (8, [40, 3, 0, 129, 7, 1, 55, 20])])
-def test_emulated_ranks_match_single_gpu_bf16(world, tokens):
+def test_emulated_ranks_match_single_gpu_bf16(world, tokens, fuse):
     import flaggems_sglang_b200 as fg
     from flaggems_sglang_b200 import _C, ep
 
     E, H, I, k = 16, 512, 256, 4
     w1, w2 = _layer(E, H, I, 0)
-    xs, outs, matrix, xcs = _run_emulated(fg, ep, world, tokens, E, H, k, w1, w2, lambda r: {}, rsf=1.5)
+    xs, outs, matrix, xcs = _run_emulated(fg, ep, world, tokens, E, H, k, w1, w2, lambda r: {}, rsf=1.5, fuse=fuse)
     _C.check_device_status()
     m = matrix.view(world, world).cpu()
     assert m.sum(1).tolist() == [t * k for t in tokens]
@@ -82,7 +85,8 @@ def test_emulated_ranks_forced_same_kernel_family_is_bit_exact():
         assert torch.equal(outs[r], ref)
 
 
-def test_emulated_ranks_fp8():
+@pytest.mark.parametrize("fuse", [True, False], ids=["gemm2_stores_to_peer", "separate_combine"])
+def test_emulated_ranks_fp8(fuse):
     import flaggems_sglang_b200 as fg
     from flaggems_sglang_b200 import _C, ep
 
@@ -96,7 +100,7 @@ def test_emulated_ranks_fp8():
         return dict(use_fp8_w8a8=True, w1_scale=s1[r * el:(r + 1) * el].contiguous(),
                     w2_scale=s2[r * el:(r + 1) * el].contiguous(), block_shape=[128, 128])
 
-    xs, outs, _, _ = _run_emulated(fg, ep, world, tokens, E, H, k, w1q, w2q, kw)
+    xs, outs, _, _ = _run_emulated(fg, ep, world, tokens, E, H, k, w1q, w2q, kw, fuse=fuse)
     _C.check_device_status()
     for r in range(world):
         x, tw, ti = xs[r]

@@ -307,9 +307,12 @@ def launches_per_step(cfg, T):
 
     dt = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn}[cfg.dtype]
     name, _ = _pick_variant(dt, T * cfg.top_k, cfg.E, cfg.I, cfg.H, None)
-    n = 1 + 1 + 2 + 1  # router, align, two GEMMs, sum
+    numel = T * cfg.top_k
+    n = 1 + (3 if numel >= 8192 else 1) + 2 + 1  # router, align (count/scan/scatter above 8192 slots), two GEMMs, sum
     if cfg.dtype == "fp8":
         n += 2  # activation quantisation before each GEMM
+        if name == "tcgen05" and cfg.top_k >= 2 and cfg.H % 512 == 0:
+            n += 2  # token rows quantised once, then bytes and scales copied into the sorted order
     elif name == "tcgen05":
         n += 1  # row gather into sorted order
     return n

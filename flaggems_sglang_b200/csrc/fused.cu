@@ -19,7 +19,10 @@ int pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forc
   const bool tc_ok = dtype == FMOE_BF16 ? (I % 128 == 0 && H % 32 == 0) : (I % 128 == 0 && H % 128 == 0);
   int v = forced;
   if (v == FMOE_VARIANT_AUTO) {
-    if (stream_ok && (rows <= 8.0 || !tc_ok)) v = FMOE_VARIANT_STREAM;
+    // measured on B200: up to 4 rows per expert the two families tie (both stream the weights once at ~90 % of
+    // HBM bandwidth) and the streaming kernel wins on tile quantisation for a handful of experts; above that the
+    // 128-row tensor-core tiles win (DeepSeek-V3 T=256: 1.49 against 2.11 ms)
+    if (stream_ok && (rows <= 4.0 || !tc_ok)) v = FMOE_VARIANT_STREAM;
     else if (tc_ok) v = FMOE_VARIANT_TCGEN05;
     else v = FMOE_VARIANT_SIMT;
   }
@@ -34,7 +37,7 @@ int pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forc
       break;
     case FMOE_VARIANT_STREAM:
       if (!stream_ok) return fail(FMOE_ERR_UNSUPPORTED, "stream kernels need H %% 128 == 0 and I %% 128 == 0");
-      *block = rows <= 6.0 ? 8 : (rows <= 12.0 ? 16 : 32);
+      *block = rows <= 4.0 ? 8 : (rows <= 12.0 ? 16 : 32);
       break;
     case FMOE_VARIANT_SIMT:
       *block = 16;

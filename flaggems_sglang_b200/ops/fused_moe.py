@@ -9,8 +9,8 @@ CUDA kernels behind the C ABI (include/fmoe_b200.h); nothing falls back to
 torch or the CPU.
 
 Kernel selection (per call, from shapes only, no host sync):
-  rows per active expert <= 8    -> "stream": small-M weight-streaming kernel,
-                                    moe_align block 8/16, x gathered on the fly
+  rows per active expert <= 4    -> "stream": small-M weight-streaming kernel,
+                                    moe_align block 8, x gathered on the fly
   larger                         -> "tcgen05": rows copied into expert-sorted order
                                     (block 128), TMA + tcgen05/TMEM persistent kernel
   fp32 inputs                    -> "simt"

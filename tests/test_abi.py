@@ -109,5 +109,6 @@ def test_variant_selection_is_shape_only():
     assert _pick_variant(bf, 128, 8, 14336, 4096, None)[0] == "tcgen05"       # Mixtral T=64 (HBM-bound, 128-row tiles)
     assert _pick_variant(bf, 8192, 8, 14336, 4096, None) == ("tcgen05", 128)  # Mixtral T=4096
     assert _pick_variant(bf, 65536, 128, 768, 2048, None) == ("tcgen05", 128)
-    assert _pick_variant(torch.float8_e4m3fn, 512, 256, 2048, 7168, None)[0] == "stream"   # DSV3 T=64
+    assert _pick_variant(torch.float8_e4m3fn, 512, 256, 2048, 7168, None) == ("stream", 8)   # DSV3 T=64
+    assert _pick_variant(torch.float8_e4m3fn, 2048, 256, 2048, 7168, None)[0] == "tcgen05"   # DSV3 T=256
     assert _pick_variant(torch.float8_e4m3fn, 131072, 256, 2048, 7168, None) == ("tcgen05", 128)

@@ -203,11 +203,35 @@ def graphed(step, warmup=3):
     return g.replay
 
 
-def time_steps(step, steps, warmup):
-    """Device time of `steps` calls (CUDA events on the current stream) -> ms per step."""
+_FLUSH = None
+
+
+def flush_l2():
+    """Overwrite a buffer of twice the L2 size, so that the next step finds none of its inputs in L2."""
+    global _FLUSH
+    if _FLUSH is None:
+        l2 = torch.cuda.get_device_properties(0).L2_cache_size
+        _FLUSH = torch.empty(2 * l2, dtype=torch.uint8, device="cuda")
+    _FLUSH.zero_()
+
+
+def time_steps(step, steps, warmup, flush=False):
+    """Device time of `steps` calls (CUDA events on the current stream) -> ms per step.  With `flush` every step
+    is timed by its own event pair and L2 is flushed before it, outside the timed interval."""
     for _ in range(warmup):
         step()
     torch.cuda.synchronize()
+    if flush:
+        pairs = []
+        for _ in range(steps):
+            flush_l2()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            step()
+            b.record()
+            pairs.append((a, b))
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(b) for a, b in pairs) / steps
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
@@ -241,17 +265,19 @@ def measure_point(cfg, wts, T, steps, warmup, peaks, seed=0):
     tok = W.make_tokens(cfg, T, "cuda", seed=seed)
     step = make_step(cfg, wts, tok)
     use_graph = T <= GRAPH_MAX_TOKENS
-    ms = time_steps(graphed(step) if use_graph else step, steps, warmup)
-    st = stage_times(step, max(3, steps // 2))
     _, ids = W.route(cfg, tok)
     active = int(torch.unique(ids).numel())
     nbytes, flops = W.algorithmic_bytes_flops(cfg, T, active)
+    # inputs smaller than twice the L2 could be served from L2 on the next iteration: flush before every step
+    flush = nbytes < 2 * torch.cuda.get_device_properties(0).L2_cache_size
+    ms = time_steps(graphed(step) if use_graph else step, steps, warmup, flush=flush)
+    st = stage_times(step, max(3, steps // 2))
     p_tensor = peaks["bf16_tflops"] * (2.0 if cfg.dtype == "fp8" else 1.0)
     t_hbm = nbytes / (peaks["hbm_gbs"] * 1e9)
     t_tc = flops / (p_tensor * 1e12)
     bound = "tensor" if t_tc > t_hbm else "hbm"
     t_roof = max(t_hbm, t_tc)
-    return {"T": T, "ms": ms, "cuda_graph": use_graph, "tokens_per_s": T / (ms * 1e-3), "active_experts": active, "bound": bound,
+    return {"T": T, "ms": ms, "cuda_graph": use_graph, "l2_flush": flush, "tokens_per_s": T / (ms * 1e-3), "active_experts": active, "bound": bound,
             "roofline_ms": t_roof * 1e3, "roofline_frac": t_roof / (ms * 1e-3),
             "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "achieved_tflops": flops / (ms * 1e-3) / 1e12,
             "stages_ms": st, "alg_bytes": nbytes, "alg_flops": flops}
@@ -365,7 +391,7 @@ def main():
             pt = point if Ts == T else measure_point(cfg, wts, Ts, max(5, args.steps // 2), 3, peaks)
             dom = dominant_kernel_roofline(cfg, Ts, pt, peaks)
             sweep.append({"T": Ts, "ms": round(pt["ms"], 4), "tokens_per_s": round(pt["tokens_per_s"], 1),
-                          "cuda_graph": pt["cuda_graph"], "bound": pt["bound"], "roofline_frac": round(pt["roofline_frac"], 4),
+                          "cuda_graph": pt["cuda_graph"], "l2_flush": pt["l2_flush"], "bound": pt["bound"], "roofline_frac": round(pt["roofline_frac"], 4),
                           "gemm1_frac": None if dom is None else round(dom["frac"], 4),
                           "active_experts": pt["active_experts"],
                           "stages_ms": {k: round(v, 4) for k, v in pt["stages_ms"].items()}})
@@ -385,7 +411,8 @@ def main():
         "config": {"workload": f"{cfg.name} MoE layer H={cfg.H} I={cfg.I} E={cfg.E} top_k={cfg.top_k}, T={T}, "
                                f"softmax top-k renormalised" if cfg.router == "softmax" else
                                f"{cfg.name} MoE layer H={cfg.H} I={cfg.I} E={cfg.E} top_k={cfg.top_k}, T={T}, grouped top-k",
-                   "tokens_per_step": T, "l2": "weights re-read every step exceed L2 (no flush needed)",
+                   "tokens_per_step": T, "l2": ("flushed before every step" if point["l2_flush"]
+                          else "weights re-read every step exceed L2 (no flush needed)"),
                    "active_experts": point["active_experts"]},
         "roofline": dominant_kernel_roofline(cfg, T, point, peaks),
         "layer_roofline": {"bound": point["bound"], "frac": point["roofline_frac"], "roofline_ms": point["roofline_ms"],

@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(kThreads)
 moe_align_kernel(const int32_t* __restrict__ topk_ids, int numel, int E, int block,
                  int32_t* __restrict__ sorted_ids, int sorted_cap, int32_t* __restrict__ expert_ids,
                  int expert_cap, int32_t* __restrict__ num_post_pad) {
+  pdl_entry();
   extern __shared__ int s_mem[];
   int* s_cnt = s_mem;                  // [kWarps][E] counts, then running output positions
   int* s_total = s_mem + kWarps * E;   // [E] per-expert count
@@ -279,8 +280,7 @@ extern "C" int fmoe_moe_align_block_size(const int32_t* topk_ids, int64_t numel,
   size_t smem = ((size_t)kWarps * E + 2 * (size_t)E + 1) * sizeof(int);
   if (smem > 48 * 1024)
     FMOE_CUDA_OK(cudaFuncSetAttribute(moe_align_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  moe_align_kernel<<<1, kThreads, smem, (cudaStream_t)stream>>>(
-      topk_ids, (int)numel, E, block, sorted_token_ids, (int)sorted_cap, expert_ids, (int)expert_cap,
-      num_tokens_post_padded);
+  launch_pdl(moe_align_kernel, dim3(1), dim3(kThreads), smem, (cudaStream_t)stream, topk_ids, (int)numel, E, block,
+             sorted_token_ids, (int)sorted_cap, expert_ids, (int)expert_cap, num_tokens_post_padded);
   return launch_status("moe_align_kernel");
 }

@@ -1,8 +1,18 @@
 // extern "C" entry points that are not tied to a single kernel file: error
 // reporting, device queries and the grouped-GEMM dispatcher.
+#include <cstdlib>
+
 #include "gemm.cuh"
 
 namespace fmoe {
+
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* env = getenv("FMOE_PDL");
+    return !(env && env[0] == '0');
+  }();
+  return on;
+}
 
 char* last_error_buffer() {
   static thread_local char buf[kErrBufSize] = {0};

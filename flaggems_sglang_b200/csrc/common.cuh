@@ -43,6 +43,37 @@ inline int launch_status(const char* what) {
   return FMOE_OK;
 }
 
+// ---- programmatic dependent launch ------------------------------------------------------------
+// The kernels of a decode-sized layer call run for a few microseconds each, so the gap between two launches
+// is a visible share of the call.  Kernels launched through launch_pdl() may be scheduled while their
+// predecessor on the stream is still running; each of them starts with pdl_entry(), which first lets its own
+// successor be scheduled and then waits until the predecessor grid has completed and its writes are visible.
+// Nothing is read or written before that wait, so the data flow is the one of ordinary stream order.
+// FMOE_PDL=0 turns the launch attribute off (plain stream serialisation).
+bool pdl_enabled();
+
+#if defined(__CUDACC__)
+__device__ __forceinline__ void pdl_entry() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // the error is picked up by launch_status()
+}
+#endif
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <typename T>

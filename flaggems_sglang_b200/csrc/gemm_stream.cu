@@ -49,6 +49,7 @@ constexpr int min_ctas(int eb, int ntg) { return (ntg == 1 || (ntg == 2 && eb ==
 template <int EB, int NTG, bool GATED, typename OutT>
 __global__ void __launch_bounds__(kThreads, min_ctas(EB, NTG))
 grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
+  pdl_entry();
   constexpr int BM = 8 * NTG;
   constexpr int U = (EB == 2) ? 4 : 2;      // 64-byte steps per 128-k chunk
   constexpr int FRAG = RT * NTG * 4 * 32;   // accumulator words per warp
@@ -296,9 +297,9 @@ int launch(const GemmParams& p, cudaStream_t st) {
   const size_t smem = W > 1 ? sizeof(float) * kWarps * RT * NTG * 4 * 32 : 0;
   dim3 grid((unsigned)ctas);
   if (p.out_dtype == FMOE_F32)
-    grouped_gemm_stream_kernel<EB, NTG, GATED, float><<<grid, kThreads, smem, st>>>(p, W, n_slabs);
+    launch_pdl(grouped_gemm_stream_kernel<EB, NTG, GATED, float>, grid, dim3(kThreads), smem, st, p, W, n_slabs);
   else
-    grouped_gemm_stream_kernel<EB, NTG, GATED, __nv_bfloat16><<<grid, kThreads, smem, st>>>(p, W, n_slabs);
+    launch_pdl(grouped_gemm_stream_kernel<EB, NTG, GATED, __nv_bfloat16>, grid, dim3(kThreads), smem, st, p, W, n_slabs);
   return launch_status("grouped_gemm_stream_kernel");
 }
 

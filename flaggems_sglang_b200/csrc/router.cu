@@ -73,6 +73,7 @@ template <int VPT>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 topk_softmax_kernel(const float* __restrict__ logits, int64_t T, int E, int k, int renorm,
                     float* __restrict__ out_w, int32_t* __restrict__ out_ids) {
+  pdl_entry();
   __shared__ int s_ids[kWarpsPerBlock][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t t = (int64_t)blockIdx.x * kWarpsPerBlock + warp;
@@ -115,6 +116,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 topk_grouped_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int64_t T, int E,
                     int k, int n_group, int topk_group, int renorm, float scale,
                     float* __restrict__ out_w, int32_t* __restrict__ out_ids) {
+  pdl_entry();
   extern __shared__ float s_dyn[];  // per warp: score[E], choice[E]
   __shared__ int s_ids[kWarpsPerBlock][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -204,7 +206,7 @@ struct SoftmaxLauncher {
   static int run(const float* logits, int64_t T, int E, int k, int renorm, float* w, int32_t* ids,
                  cudaStream_t st) {
     dim3 grid((unsigned)ceil_div<int64_t>(T, kWarpsPerBlock));
-    topk_softmax_kernel<VPT><<<grid, kWarpsPerBlock * 32, 0, st>>>(logits, T, E, k, renorm, w, ids);
+    launch_pdl(topk_softmax_kernel<VPT>, grid, dim3(kWarpsPerBlock * 32), 0, st, logits, T, E, k, renorm, w, ids);
     return launch_status("topk_softmax_kernel");
   }
 };
@@ -215,8 +217,8 @@ struct GroupedLauncher {
                  int topk_group, int renorm, float scale, float* w, int32_t* ids, cudaStream_t st) {
     dim3 grid((unsigned)ceil_div<int64_t>(T, kWarpsPerBlock));
     size_t smem = (size_t)kWarpsPerBlock * 2 * E * sizeof(float);
-    topk_grouped_kernel<VPT><<<grid, kWarpsPerBlock * 32, smem, st>>>(
-        logits, bias, T, E, k, n_group, topk_group, renorm, scale, w, ids);
+    launch_pdl(topk_grouped_kernel<VPT>, grid, dim3(kWarpsPerBlock * 32), smem, st, logits, bias, T, E, k, n_group,
+               topk_group, renorm, scale, w, ids);
     return launch_status("topk_grouped_kernel");
   }
 };

@@ -36,6 +36,7 @@ __global__ void __launch_bounds__(256)
 quant_group128_kernel(const InT* __restrict__ x, int64_t rows_out, int64_t K, const int32_t* __restrict__ row_map,
                       int map_div, int64_t sentinel, const int32_t* __restrict__ num_rows_dev,
                       uint8_t* __restrict__ q, float* __restrict__ scale) {
+  pdl_entry();
   constexpr int kIlp = 4;
   const int sub = threadIdx.x & 15;  // lane inside the 16-lane team
   const unsigned hmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
@@ -127,6 +128,7 @@ __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint4* __restrict__ x, int64_t rows_out, int64_t vec_per_row,
                    const int32_t* __restrict__ row_map, int map_div, int64_t sentinel,
                    const int32_t* __restrict__ num_rows_dev, uint4* __restrict__ out) {
+  pdl_entry();
   const int64_t limit = num_rows_dev ? min((int64_t)*num_rows_dev, rows_out) : rows_out;
   for (int64_t p = blockIdx.x; p < limit; p += gridDim.x) {
     const int64_t r = mapped_row(row_map, map_div, sentinel, p);
@@ -139,6 +141,7 @@ gather_rows_kernel(const uint4* __restrict__ x, int64_t rows_out, int64_t vec_pe
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_sum_kernel(const T* __restrict__ z, int64_t Tn, int k, int64_t H, float scale, T* __restrict__ out) {
+  pdl_entry();
   constexpr int V = 16 / sizeof(T);
   const int64_t vec_per_row = H / V;
   const int64_t total = Tn * vec_per_row;
@@ -182,11 +185,11 @@ extern "C" int fmoe_quant_fp8_group128(const void* x, int in_dtype, int64_t rows
   unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div<int64_t>(rows_out * (K / 128), 64), 148 * 8));
   auto st = (cudaStream_t)stream;
   if (in_dtype == FMOE_BF16)
-    quant_group128_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)x, rows_out, K, row_map, map_div,
-                                                               map_sentinel, num_rows_dev, (uint8_t*)q, scale);
+    launch_pdl(quant_group128_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)x, rows_out, K,
+               row_map, map_div, map_sentinel, num_rows_dev, (uint8_t*)q, scale);
   else
-    quant_group128_kernel<float><<<grid, 256, 0, st>>>((const float*)x, rows_out, K, row_map, map_div, map_sentinel,
-                                                       num_rows_dev, (uint8_t*)q, scale);
+    launch_pdl(quant_group128_kernel<float>, dim3(grid), dim3(256), 0, st, (const float*)x, rows_out, K, row_map,
+               map_div, map_sentinel, num_rows_dev, (uint8_t*)q, scale);
   return launch_status("quant_group128_kernel");
 }
 
@@ -200,8 +203,8 @@ extern "C" int fmoe_gather_rows(const void* x, int elem_bytes, int64_t rows_out,
   if (rows_out <= 0) return FMOE_OK;
   FMOE_REQUIRE(x && out && aligned16(x) && aligned16(out), "gather_rows: null or misaligned pointer");
   unsigned grid = (unsigned)std::min<int64_t>(rows_out, 148 * 8);
-  gather_rows_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)x, rows_out, K * elem_bytes / 16, row_map,
-                                                             map_div, map_sentinel, num_rows_dev, (uint4*)out);
+  launch_pdl(gather_rows_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const uint4*)x, rows_out,
+             K * elem_bytes / 16, row_map, map_div, map_sentinel, num_rows_dev, (uint4*)out);
   return launch_status("gather_rows_kernel");
 }
 
@@ -217,8 +220,9 @@ extern "C" int fmoe_moe_sum(const void* z, int dtype, int64_t T, int k, int64_t 
   unsigned grid = (unsigned)std::min<int64_t>(ceil_div<int64_t>(total, 256), 148 * 16);
   auto st = (cudaStream_t)stream;
   if (dtype == FMOE_BF16)
-    moe_sum_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)z, T, k, H, scale, (__nv_bfloat16*)out);
+    launch_pdl(moe_sum_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)z, T, k, H, scale,
+               (__nv_bfloat16*)out);
   else
-    moe_sum_kernel<float><<<grid, 256, 0, st>>>((const float*)z, T, k, H, scale, (float*)out);
+    launch_pdl(moe_sum_kernel<float>, dim3(grid), dim3(256), 0, st, (const float*)z, T, k, H, scale, (float*)out);
   return launch_status("moe_sum_kernel");
 }

@@ -154,24 +154,43 @@ class PeerExchange:
         lib = _C.lib()
         base = ctypes.c_void_p()
         handle = (ctypes.c_ubyte * 64)()
+        self._own_base, self._opened = None, []
+
+        def agree(problem: Optional[str], what: str):
+            # a step that failed on one rank must fail on all of them, or the others would wait in the next collective
+            flag = torch.tensor([0 if problem is None else 1], dtype=torch.int32, device=self.device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+            if int(flag.item()):
+                self._release()
+                raise RuntimeError(f"PeerExchange: {what} failed on " +
+                                   (f"this rank: {problem}" if problem else "another rank"))
+
         with torch.cuda.device(self.device):
-            _C.check(lib.fmoe_ep_buffer_create(self.nbytes, ctypes.byref(base), handle))
+            problem = None
+            try:
+                _C.check(lib.fmoe_ep_buffer_create(self.nbytes, ctypes.byref(base), handle))
+                self._own_base = base.value
+            except Exception as e:  # noqa: BLE001
+                problem = str(e)
+            agree(problem, "allocating the receive area")
             mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
             every = torch.empty(self.world * 64, dtype=torch.uint8, device=self.device)
             dist.all_gather_into_tensor(every, mine, group=group)
             every = every.cpu().view(self.world, 64)
-            self._own_base = base.value
-            self._opened = []
             bases = []
-            for j in range(self.world):
-                if j == self.rank:
-                    bases.append(base.value)
-                    continue
-                peer = ctypes.c_void_p()
-                raw = (ctypes.c_ubyte * 64)(*every[j].tolist())
-                _C.check(lib.fmoe_ep_buffer_open(raw, ctypes.byref(peer)))
-                self._opened.append(peer.value)
-                bases.append(peer.value)
+            try:
+                for j in range(self.world):
+                    if j == self.rank:
+                        bases.append(base.value)
+                        continue
+                    peer = ctypes.c_void_p()
+                    raw = (ctypes.c_ubyte * 64)(*every[j].tolist())
+                    _C.check(lib.fmoe_ep_buffer_open(raw, ctypes.byref(peer)))
+                    self._opened.append(peer.value)
+                    bases.append(peer.value)
+            except Exception as e:  # noqa: BLE001
+                problem = str(e)
+            agree(problem, "mapping the peers' receive areas (CUDA IPC)")
         self._bind(bases, torch.as_tensor(_DeviceBytes(base.value, self.nbytes), device=self.device))
         self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.ids.fill_(-1)
@@ -237,21 +256,32 @@ class PeerExchange:
         peer stores included) before any rank's later kernels start."""
         dist.all_reduce(self._flag, group=self.group)
 
-    def close(self):
+    def _release(self):
         from . import _C
 
         lib = _C.lib()
+        for p in self._opened:
+            lib.fmoe_ep_buffer_close(p)
+        self._opened = []
+        if self._own_base:
+            lib.fmoe_ep_buffer_destroy(self._own_base)
+            self._own_base = None
+
+    def close(self):
+        """Collective: unmaps the peers' areas, then frees the own one once every rank has unmapped it."""
+        from . import _C
+
+        if not self._own_base:  # emulated instance, or closed already
+            return
+        lib = _C.lib()
         torch.cuda.synchronize(self.device)
-        if self.group is not None:
-            dist.barrier(group=self.group)
+        dist.barrier(group=self.group)
         for p in self._opened:
             _C.check(lib.fmoe_ep_buffer_close(p))
         self._opened = []
-        if self._own_base:
-            if self.group is not None:
-                dist.barrier(group=self.group)
-            _C.check(lib.fmoe_ep_buffer_destroy(self._own_base))
-            self._own_base = None
+        dist.barrier(group=self.group)
+        _C.check(lib.fmoe_ep_buffer_destroy(self._own_base))
+        self._own_base = None
 
 
 def p2p_route(xc: PeerExchange, hidden_states, topk_weights, topk_ids, experts_per_rank: int) -> dict:

@@ -36,7 +36,14 @@ def run(args, cfg, rank: int, world: int, local: int, clock_sampler=None) -> Non
         # rows travel by P2P stores of this package's kernels into IPC-mapped receive areas ("p2p"), or by
         # NCCL all-to-all ("nccl")
         mode = getattr(args, "ep_exchange", "p2p")
-        xc = ep.PeerExchange(None, args.tokens, cfg.top_k, cfg.H, tok["hidden"].dtype) if mode == "p2p" else None
+        xc = None
+        if mode == "p2p":
+            try:
+                xc = ep.PeerExchange(None, args.tokens, cfg.top_k, cfg.H, tok["hidden"].dtype)
+            except RuntimeError as e:  # raised on every rank together (see PeerExchange): use the NCCL exchange
+                mode = "nccl"
+                if rank == 0:
+                    print(f"# P2P exchange unavailable, using NCCL all-to-all: {e}", flush=True)
 
         def step():
             return ep.ep_fused_moe(tok["hidden"], wts["w1"], wts["w2"], tok["logits"], cfg.top_k, cfg.E, True,

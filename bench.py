@@ -336,9 +336,10 @@ def launches_per_step(cfg, T):
     numel = T * cfg.top_k
     n = 1 + (3 if numel >= 8192 else 1) + 2 + 1  # router, align (count/scan/scatter above 8192 slots), two GEMMs, sum
     if cfg.dtype == "fp8":
-        n += 2  # activation quantisation before each GEMM
+        n += 1  # quantisation of the input rows
         if name == "tcgen05" and cfg.top_k >= 2 and cfg.H % 512 == 0:
             n += 2  # token rows quantised once, then bytes and scales copied into the sorted order
+        n += 1  # quantisation of the activations between the two GEMMs
     elif name == "tcgen05":
         n += 1  # row gather into sorted order
     return n

@@ -97,6 +97,16 @@ __device__ __forceinline__ uint8_t f32_to_e4m3_bits(float v) {
   return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
 }
 
+// RN(v / s) for many v and one s: with r = RN(1/s), two residual corrections of v*r give the correctly rounded
+// quotient (Markstein), the same bits as an IEEE division, in 5 instructions per element.  The caller falls back to
+// __fdiv_rn when the group holds an infinity (the residual would be inf - inf).
+__device__ __forceinline__ float div_by_shared(float v, float s, float r) {
+  float q = v * r;
+  q = fmaf(fmaf(-q, s, v), r, q);
+  q = fmaf(fmaf(-q, s, v), r, q);
+  return q;
+}
+
 // silu(g) * u exactly as the reference kernel writes it: (g / (1 + exp(-g))) * u in fp32
 // (FlagGems-sglang src/flaggems_sglang/ops/fused_moe.py:62).
 __device__ __forceinline__ float silu_mul(float g, float u) {

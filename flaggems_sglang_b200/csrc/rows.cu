@@ -16,15 +16,6 @@ __device__ __forceinline__ int64_t mapped_row(const int32_t* row_map, int map_di
   return map_div ? s / map_div : p;
 }
 
-// RN(v / s) for many v and one s: with r = RN(1/s), two residual corrections of v*r give the correctly rounded
-// quotient (Markstein), the same bits as an IEEE division, in 5 instructions per element.  The caller falls back to
-// __fdiv_rn when the group holds an infinity (the residual would be inf - inf).
-__device__ __forceinline__ float div_by_shared(float v, float s, float r) {
-  float q = v * r;
-  q = fmaf(fmaf(-q, s, v), r, q);
-  q = fmaf(fmaf(-q, s, v), r, q);
-  return q;
-}
 
 // The work is the flat list of (output row, 128-channel group) items; 16 lanes own one item: each lane loads
 // 8 consecutive channels (16 bytes of bf16, 32 of fp32) and writes 8 bytes.  A 16-lane team walks the list with

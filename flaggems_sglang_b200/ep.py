@@ -200,8 +200,13 @@ class PeerExchange:
     # -- shared with the single-process emulation used by the tests -------------------------------------
     def _layout(self, max_tokens, top_k, hidden_size, dtype, capacity):
         self.max_tokens, self.top_k, self.H, self.dtype = int(max_tokens), int(top_k), int(hidden_size), dtype
-        # result rows go back from inside the down-projection kernel (False: a separate copy kernel, for A/B timing)
-        self.fuse_return = os.environ.get("FMOE_EP_FUSE_RETURN", "1") != "0"
+        # Result rows go back either from inside the down-projection kernel (its epilogue stores to the peer) or by a
+        # separate copy kernel.  None = by kernel family: the bf16 tcgen05 kernel has dedicated epilogue warps, so the
+        # slower peer stores overlap the next tile (measured 2.50 against 2.55 ms, Mixtral, 2 GPUs); in the fp8
+        # kernel the fold warps do the epilogue and the stores sit on the critical path (4.58 against 4.22 ms,
+        # DeepSeek-V3, 2 GPUs).  FMOE_EP_FUSE_RETURN=0/1 forces one way.
+        env = os.environ.get("FMOE_EP_FUSE_RETURN")
+        self.fuse_return = None if env is None else env != "0"
         eb = torch.empty(0, dtype=dtype).element_size()
         if (self.H * eb) % 16:
             raise ValueError("hidden rows must be a multiple of 16 bytes")
@@ -318,12 +323,13 @@ def p2p_send(xc: PeerExchange, state: dict, matrix: torch.Tensor) -> None:
         _C.stream_ptr(x.device)))
 
 
-def p2p_experts(xc: PeerExchange, state: dict, w1_local, w2_local, fuse_return: bool = True,
+def p2p_experts(xc: PeerExchange, state: dict, w1_local, w2_local, fuse_return: Optional[bool] = None,
                 **expert_kwargs) -> Optional[torch.Tensor]:
     """Phase 3 (after the barrier): grouped GEMMs over the receive area; rows past the received count carry
     id -1 and are skipped by moe_align_block_size.  With `fuse_return` (and a kernel family that takes row
     addresses) the down-projection epilogue stores every result row straight into the slot buffer of the
-    rank the row came from, and None is returned; otherwise the rows come back for `p2p_return`."""
+    rank the row came from, and None is returned; otherwise the rows come back for `p2p_return`.
+    `fuse_return=None` decides by kernel family (bf16: fused, fp8: separate)."""
     from . import _C
     from .ops.fused_moe import _pick_variant, fused_experts
 
@@ -333,6 +339,8 @@ def p2p_experts(xc: PeerExchange, state: dict, w1_local, w2_local, fuse_return: 
     name, _ = _pick_variant(torch.float8_e4m3fn if fp8 else w1_local.dtype, max(state["T"] * state["k"], 1),
                             w1_local.shape[0], w2_local.shape[2], xc.H, expert_kwargs.get("variant"))
     expert_kwargs = dict(expert_kwargs, variant=name)
+    if fuse_return is None:
+        fuse_return = not fp8
     fuse_return = fuse_return and name in ("stream", "tcgen05")
     out_rows = torch.empty(xc.capacity, dtype=torch.int64, device=dev) if fuse_return else None
     _C.check(_C.lib().fmoe_ep_mask_tail(xc.ids.data_ptr(), state["matrix"].data_ptr(), xc.rank, xc.world, xc.capacity,

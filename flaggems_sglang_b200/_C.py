@@ -18,7 +18,7 @@ OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_TIMEOUT = 0, 1, 2, 3,
 F32, BF16, E4M3 = 0, 1, 2
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_STREAM, VARIANT_TCGEN05 = 0, 1, 2, 3
 VARIANTS = {"auto": 0, "simt": 1, "stream": 2, "tcgen05": 3, "tcgen05_pair": 4}
-ACTIVATIONS = {"silu": 0, "gelu": 1}
+ACTIVATIONS = {"silu": 0, "gelu": 1, "swiglu_oai": 2}
 VARIANT_NAMES = {v: k for k, v in VARIANTS.items()}
 
 DTYPE_CODE = {torch.float32: F32, torch.bfloat16: BF16, torch.float8_e4m3fn: E4M3}
@@ -40,7 +40,8 @@ class GemmArgs(Structure):
         ("sorted_cap", c_int64), ("max_blocks", c_int64),
         ("a", c_void_p), ("a_scale", c_void_p), ("w", c_void_p), ("w_scale", c_void_p),
         ("sorted_token_ids", c_void_p), ("expert_ids", c_void_p), ("num_tokens_post_padded", c_void_p),
-        ("row_scale", c_void_p), ("out", c_void_p), ("out_scale", c_void_p), ("out_rows", c_void_p),
+        ("row_scale", c_void_p), ("out", c_void_p), ("out_scale", c_void_p),
+        ("bias", c_void_p), ("act_alpha", c_float), ("act_limit", c_float), ("out_rows", c_void_p),
     ]
 
 
@@ -55,7 +56,8 @@ class FusedArgs(Structure):
         ("routed_scaling_factor", c_float), ("reserved_f", c_float),
         ("hidden", c_void_p), ("w1", c_void_p), ("w2", c_void_p), ("w1_scale", c_void_p), ("w2_scale", c_void_p),
         ("topk_weights", c_void_p), ("topk_ids", c_void_p), ("out", c_void_p), ("workspace", c_void_p),
-        ("workspace_bytes", c_int64), ("out_rows", c_void_p),
+        ("workspace_bytes", c_int64), ("b1", c_void_p), ("b2", c_void_p), ("act_alpha", c_float),
+        ("act_limit", c_float), ("out_rows", c_void_p),
     ]
 
 

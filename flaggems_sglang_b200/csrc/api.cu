@@ -24,7 +24,10 @@ namespace {
 int validate_gemm(const GemmParams& a, bool gated, const char* who) {
   FMOE_REQUIRE(a.dtype == FMOE_F32 || a.dtype == FMOE_BF16 || a.dtype == FMOE_E4M3, "%s: unknown dtype %d", who, a.dtype);
   FMOE_REQUIRE(a.num_experts >= 1 && a.top_k >= 1 && a.block_size >= 1, "%s: bad E/top_k/block_size", who);
-  FMOE_REQUIRE(a.activation == FMOE_ACT_SILU || a.activation == FMOE_ACT_GELU, "%s: unknown activation %d", who, a.activation);
+  FMOE_REQUIRE(a.activation == FMOE_ACT_SILU || a.activation == FMOE_ACT_GELU || a.activation == FMOE_ACT_SWIGLU_OAI,
+               "%s: unknown activation %d", who, a.activation);
+  if (a.bias || a.activation == FMOE_ACT_SWIGLU_OAI)
+    FMOE_REQUIRE(a.dtype != FMOE_E4M3, "%s: bias and the swiglu_oai activation are not available with e4m3 weights", who);
   FMOE_REQUIRE(a.numel >= 0 && a.n >= 1 && a.k >= 1, "%s: bad sizes numel=%lld n=%lld k=%lld", who,
                (long long)a.numel, (long long)a.n, (long long)a.k);
   FMOE_REQUIRE(a.max_blocks >= 0 && a.max_blocks * a.block_size <= a.sorted_cap,

@@ -128,6 +128,25 @@ __device__ __forceinline__ float act_mul_fast(float g, float u, int activation) 
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
+// Output of the gate/up projection for one column: accumulators g, u of the gate and up rows, their biases
+// (0 without), the row scale, the activation and its parameters.  See FMOE_ACT_* for the order of operations.
+// FAST selects the ex2/rcp based forms (bf16 epilogues of the large-M kernels).
+template <bool FAST>
+__device__ __forceinline__ float gated_output(float g, float u, float bg, float bu, float rs, int activation,
+                                              float alpha, float limit) {
+  g += bg;
+  u += bu;
+  if (activation == FMOE_ACT_SWIGLU_OAI) {
+    if (limit > 0.f) {
+      g = fminf(g, limit);
+      u = fmaxf(-limit, fminf(u, limit));
+    }
+    const float s = FAST ? __fdividef(g, 1.0f + __expf(-alpha * g)) : __fdiv_rn(g, 1.0f + expf(-alpha * g));
+    return fmaf(s, u, s) * rs;
+  }
+  return FAST ? act_mul_fast(g * rs, u * rs, activation) : act_mul(g * rs, u * rs, activation);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

@@ -68,7 +68,11 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
   FMOE_REQUIRE(a.T >= 0 && a.H >= 1 && a.I >= 1, "fused_experts: bad sizes T=%lld H=%lld I=%lld", (long long)a.T,
                (long long)a.H, (long long)a.I);
   FMOE_REQUIRE(a.dtype == FMOE_F32 || a.dtype == FMOE_BF16 || a.dtype == FMOE_E4M3, "fused_experts: unknown dtype %d", a.dtype);
-  FMOE_REQUIRE(a.activation == FMOE_ACT_SILU || a.activation == FMOE_ACT_GELU, "fused_experts: unknown activation %d", a.activation);
+  FMOE_REQUIRE(a.activation == FMOE_ACT_SILU || a.activation == FMOE_ACT_GELU || a.activation == FMOE_ACT_SWIGLU_OAI,
+               "fused_experts: unknown activation %d", a.activation);
+  if (a.b1 || a.b2 || a.activation == FMOE_ACT_SWIGLU_OAI)
+    FMOE_REQUIRE(a.dtype != FMOE_E4M3,
+                 "fused_experts: bias and the swiglu_oai activation are not available with e4m3 weights");
   if (a.dtype == FMOE_E4M3)
     FMOE_REQUIRE(a.H % 128 == 0 && a.I % 128 == 0, "fused_experts: e4m3 needs H and I to be multiples of 128");
   FusedPlan& p = *pl;
@@ -155,6 +159,10 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
   fmoe_gemm_args g1 = g, g2 = g;
   g1.n = a.I;
   g1.activation = a.activation;
+  g1.act_alpha = a.act_alpha;
+  g1.act_limit = a.act_limit;
+  g1.bias = a.b1;
+  g2.bias = a.b2;
   g1.k = a.H;
   g1.w = a.w1;
   g1.out = act;

@@ -62,10 +62,12 @@ grouped_gemm_simt_kernel(GemmParams p) {
       }
     }
     const float rs = p.row_scale ? p.row_scale[slot] : 1.0f;
+    const float* bias = p.bias ? p.bias + (int64_t)e * w_rows : nullptr;
     if constexpr (GATED) {
-      reinterpret_cast<OutT*>(p.out)[pos * p.n + c] = from_f32<OutT>(act_mul(acc_g * rs, acc_u * rs, p.activation));
+      reinterpret_cast<OutT*>(p.out)[pos * p.n + c] = from_f32<OutT>(gated_output<false>(
+          acc_g, acc_u, bias ? bias[c] : 0.f, bias ? bias[p.n + c] : 0.f, rs, p.activation, p.act_alpha, p.act_limit));
     } else {
-      reinterpret_cast<OutT*>(p.out)[(int64_t)slot * p.n + c] = from_f32<OutT>(acc_g * rs);
+      reinterpret_cast<OutT*>(p.out)[(int64_t)slot * p.n + c] = from_f32<OutT>((acc_g + (bias ? bias[c] : 0.f)) * rs);
     }
   }
 }

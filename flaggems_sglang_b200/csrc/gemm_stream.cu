@@ -254,16 +254,19 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
       if (slot < 0) continue;
       const float rs = p.row_scale ? p.row_scale[slot] : 1.0f;
       const int col = g + 8 * (i >> 1);
+      const float* bias = p.bias ? p.bias + (int64_t)e * w_rows : nullptr;
       if constexpr (GATED) {
         if (n0 + col < p.n)
-          out[(b * BM + q * 8 + 2 * t + (i & 1)) * p.n + n0 + col] =
-              from_f32<OutT>(act_mul(acc[0][q][i] * rs, acc[1][q][i] * rs, p.activation));
+          out[(b * BM + q * 8 + 2 * t + (i & 1)) * p.n + n0 + col] = from_f32<OutT>(gated_output<false>(
+              acc[0][q][i], acc[1][q][i], bias ? bias[n0 + col] : 0.f, bias ? bias[p.n + n0 + col] : 0.f, rs,
+              p.activation, p.act_alpha, p.act_limit));
       } else {
         OutT* orow = p.out_rows ? reinterpret_cast<OutT*>(p.out_rows[slot]) : out + (int64_t)slot * p.n;
         if (!orow) continue;
 #pragma unroll
         for (int rt = 0; rt < RT; ++rt)
-          if (n0 + rt * 16 + col < p.n) orow[n0 + rt * 16 + col] = from_f32<OutT>(acc[rt][q][i] * rs);
+          if (n0 + rt * 16 + col < p.n)
+            orow[n0 + rt * 16 + col] = from_f32<OutT>((acc[rt][q][i] + (bias ? bias[n0 + rt * 16 + col] : 0.f)) * rs);
       }
     }
   if (p.out_rows) __threadfence_system();  // rows stored to a peer are complete before the kernel ends

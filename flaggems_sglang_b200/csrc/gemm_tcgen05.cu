@@ -54,6 +54,8 @@ struct TcParams {
   const int32_t* expert_ids;
   const int32_t* num_tokens_post_padded;
   const float* row_scale;
+  const float* bias;      // optional [E, w_rows] f32
+  float act_alpha, act_limit;
   void* out;
   void* const* out_rows;  // down projection: optional per-slot row addresses (may be peer memory)
   int64_t numel;
@@ -288,6 +290,10 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       const int32_t slot = (pos < p.sorted_cap) ? p.sorted_token_ids[pos] : -1;
       const bool valid = slot >= 0 && slot < p.numel;
       const float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
+      // bias entries of this tile's columns (the same for every row: broadcast loads)
+      const float* bias = p.bias ? p.bias + (int64_t)min(max(p.expert_ids[m_blk], 0), p.num_experts - 1) * p.w_rows +
+                                       (int64_t)n_tile * (GATED ? 128 : 256)
+                                 : nullptr;
       const long long te0 = p.profile ? clock64() : 0;
       const bool oke = warp_wait_relaxed(&acc_full[acc], acc_phase);
       const long long te1 = p.profile ? clock64() : 0;
@@ -315,8 +321,17 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int i = v * 8 + j * 2;
-                float o0 = act_mul_fast(__uint_as_float(g[i]) * rs, __uint_as_float(u[i]) * rs, p.activation);
-                float o1 = act_mul_fast(__uint_as_float(g[i + 1]) * rs, __uint_as_float(u[i + 1]) * rs, p.activation);
+                float o0, o1;
+                if (bias || p.activation == FMOE_ACT_SWIGLU_OAI) {
+                  const float* bg = bias ? bias + c * 32 + i : nullptr;
+                  o0 = gated_output<true>(__uint_as_float(g[i]), __uint_as_float(u[i]), bg ? bg[0] : 0.f,
+                                          bg ? bg[p.n] : 0.f, rs, p.activation, p.act_alpha, p.act_limit);
+                  o1 = gated_output<true>(__uint_as_float(g[i + 1]), __uint_as_float(u[i + 1]), bg ? bg[1] : 0.f,
+                                          bg ? bg[p.n + 1] : 0.f, rs, p.activation, p.act_alpha, p.act_limit);
+                } else {
+                  o0 = act_mul_fast(__uint_as_float(g[i]) * rs, __uint_as_float(u[i]) * rs, p.activation);
+                  o1 = act_mul_fast(__uint_as_float(g[i + 1]) * rs, __uint_as_float(u[i + 1]) * rs, p.activation);
+                }
                 w[j] = pack_bf16x2(o0, o1);
               }
               dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -341,7 +356,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int i = v * 8 + j * 2;
-                w[j] = pack_bf16x2(__uint_as_float(r[i]) * rs, __uint_as_float(r[i + 1]) * rs);
+                const float b0 = bias ? bias[c * 32 + i] : 0.f, b1 = bias ? bias[c * 32 + i + 1] : 0.f;
+                w[j] = pack_bf16x2((__uint_as_float(r[i]) + b0) * rs, (__uint_as_float(r[i + 1]) + b1) * rs);
               }
               dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
             }
@@ -444,6 +460,9 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.expert_ids = g.expert_ids;
   p.num_tokens_post_padded = g.num_tokens_post_padded;
   p.row_scale = g.row_scale;
+  p.bias = g.bias;
+  p.act_alpha = g.act_alpha;
+  p.act_limit = g.act_limit;
   p.out = g.out;
   p.out_rows = GATED ? nullptr : g.out_rows;
   p.numel = g.numel;

@@ -379,6 +379,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
 
 bool gemm_tcgen05_fp8_supports(const GemmParams& p, bool gated) {
   if (p.dtype != FMOE_E4M3 || p.out_dtype != FMOE_BF16) return false;
+  if (p.bias || p.activation == FMOE_ACT_SWIGLU_OAI) return false;  // bf16-only variant
   if (p.block_size != BM || p.a_gather) return false;
   if (p.k <= 0 || p.k % 128 != 0 || p.n <= 0 || p.n % 128 != 0) return false;
   if (!p.a_scale || !p.w_scale) return false;

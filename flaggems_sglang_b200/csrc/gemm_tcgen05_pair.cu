@@ -354,6 +354,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
 bool gemm_tcgen05_pair_supports(const GemmParams& p, bool gated) {
   if (p.dtype != FMOE_BF16 || p.out_dtype != FMOE_BF16) return false;
   if (p.block_size != PAIR_M || p.a_gather) return false;
+  if (p.bias || p.activation == FMOE_ACT_SWIGLU_OAI || p.out_rows) return false;
   if (p.k <= 0 || (p.k * 2) % 16 != 0) return false;
   if (p.n <= 0 || p.n % (gated ? 128 : 32) != 0) return false;
   if (!aligned16(p.a) || !aligned16(p.w) || !aligned16(p.out)) return false;

@@ -8,6 +8,7 @@ from .fused_moe import (  # noqa: F401
     fused_moe_flagos,
     standard_topk_to_routing,
     triton_kernel_fused_experts,
+    triton_kernel_fused_experts_with_bias,
 )
 from .moe_align_block_size import moe_align_block_size  # noqa: F401
 from .moe_sum import moe_sum  # noqa: F401
@@ -15,7 +16,8 @@ from .quant import per_token_group_quant_fp8, quant_weight_block128  # noqa: F40
 from .topk import fused_topk, grouped_topk, topk  # noqa: F401
 
 __all__ = [
-    "fused_experts", "fused_moe", "triton_kernel_fused_experts", "fused_moe_flagos",
+    "fused_experts", "fused_moe", "triton_kernel_fused_experts", "triton_kernel_fused_experts_with_bias",
+    "fused_moe_flagos",
     "standard_topk_to_routing", "RoutingData", "GatherIndx", "ScatterIndx",
     "moe_align_block_size", "moe_sum", "per_token_group_quant_fp8", "quant_weight_block128",
     "fused_topk", "grouped_topk", "topk",

@@ -151,6 +151,10 @@ def fused_experts(
     global_num_experts: int = -1,
     variant: Optional[str] = None,
     out_rows: Optional[torch.Tensor] = None,
+    b1: Optional[torch.Tensor] = None,
+    b2: Optional[torch.Tensor] = None,
+    gemm1_alpha: Optional[float] = None,
+    gemm1_clamp_limit: Optional[float] = None,
 ) -> torch.Tensor:
     """Expert computation for already-routed tokens.
 
@@ -164,6 +168,10 @@ def fused_experts(
     `out_rows` (with `no_combine`): int64 [T*k] device addresses; the result row of every slot is stored
     there by the down-projection kernel instead of into a [T,k,H] tensor (0 = skip), and None is returned.
     Used by the expert-parallel path, whose addresses are slot rows in the source ranks' memory.
+    `b1 [E,2I]` (gate entries then up entries) / `b2 [E,H]`: optional biases of the two projections;
+    `activation="swiglu_oai"` with `gemm1_alpha` (default 1.702) and `gemm1_clamp_limit` (None = no clamp) is
+    the gated unit of the reference's bias variant (src/flaggems_sglang/ops/fused_moe.py:235-325): bias, then
+    activation, then top-k weight.  bf16 / fp32 weights only.
     """
     logger.debug("FLAGGEMS_SGLANG_B200 FUSED_EXPERTS")
     assert inplace is False, "Inplace is not supported"
@@ -207,6 +215,16 @@ def fused_experts(
         ids = expert_map.to(torch.int32)[topk_ids.long()]
     ids = ids.to(torch.int32).contiguous()
 
+    if b1 is not None or b2 is not None or activation == "swiglu_oai":
+        assert not use_fp8_w8a8, "bias / swiglu_oai are not available with fp8 weights"
+        assert b1 is None or tuple(b1.shape) == (E, twoI), "b1 must be [E, 2I]"
+        assert b2 is None or tuple(b2.shape) == (E, H), "b2 must be [E, H]"
+        if b1 is not None or b2 is not None:
+            _C.require_cuda(hidden_states, b1, b2)
+        b1 = None if b1 is None else b1.float().contiguous()
+        b2 = None if b2 is None else b2.float().contiguous()
+    act_alpha = 1.702 if gemm1_alpha is None else float(gemm1_alpha)
+    act_limit = 0.0 if gemm1_clamp_limit is None else float(gemm1_clamp_limit)
     if out_rows is not None:
         assert no_combine and expert_map is None, "out_rows needs no_combine and no expert_map"
         assert out_rows.dtype == torch.int64 and out_rows.numel() >= numel and out_rows.is_contiguous()
@@ -229,7 +247,7 @@ def fused_experts(
             routed_scaling_factor=1.0 if routed_scaling_factor is None else float(routed_scaling_factor),
             hidden=x.data_ptr(), w1=w1.data_ptr(), w2=w2.data_ptr(), w1_scale=_C.ptr(w1_scale),
             w2_scale=_C.ptr(w2_scale), topk_weights=wts.data_ptr(), topk_ids=ids.data_ptr(), out=_C.ptr(out),
-            out_rows=_C.ptr(out_rows))
+            out_rows=_C.ptr(out_rows), b1=_C.ptr(b1), b2=_C.ptr(b2), act_alpha=act_alpha, act_limit=act_limit)
         need = lib.fmoe_fused_experts_workspace_bytes(fa)
         if need < 0:
             _C.check(_C.ERR_INVALID_ARG)
@@ -270,12 +288,12 @@ def fused_experts(
         act = torch.empty((cap, I), dtype=out_dtype, device=dev)
         g1 = _gemm_args(dtype=code, out_dtype=code, a_gather=gather, n=I, k=H, a_rows=a_rows, a=a_ptr,
                         w=w1.data_ptr(), row_scale=row_w if apply_router_weight_on_input else None,
-                        out=act.data_ptr(), **common)
+                        out=act.data_ptr(), bias=_C.ptr(b1), act_alpha=act_alpha, act_limit=act_limit, **common)
         with _stage("gemm1_" + name):
             _C.check(lib.fmoe_gemm1_silu(g1, st))
         g2 = _gemm_args(dtype=code, out_dtype=code, a_gather=0, n=H, k=I, a_rows=cap, a=act.data_ptr(),
                         w=w2.data_ptr(), row_scale=None if apply_router_weight_on_input else row_w,
-                        **z_args, **common)
+                        bias=_C.ptr(b2), **z_args, **common)
         with _stage("gemm2_" + name):
             _C.check(lib.fmoe_gemm2(g2, st))
     else:
@@ -437,6 +455,73 @@ def triton_kernel_fused_experts(
     return z_or_out.view(T, H)
 
 
+def triton_kernel_fused_experts_with_bias(
+    hidden_states: torch.Tensor,
+    w1: torch.Tensor,
+    w1_pcg,
+    b1: torch.Tensor,
+    w2: torch.Tensor,
+    w2_pcg,
+    b2: torch.Tensor,
+    routing_data,
+    gather_indx,
+    scatter_indx,
+    inplace: bool = False,
+    activation: str = "silu",
+    apply_router_weight_on_input: bool = False,
+    global_num_experts: int = -1,
+    gemm1_alpha: Optional[float] = None,
+    gemm1_clamp_limit: Optional[float] = None,
+) -> torch.Tensor:
+    """The reference's bias variant (src/flaggems_sglang/ops/fused_moe.py:235-325), same signature.
+
+    The reference hands the work to the third-party `matmul_ogs` with a fused swiglu; its call does not match
+    any released signature of that library, so the contract here is the published algorithm of
+    `triton_kernels.swiglu` and of the `matmul_ogs` epilogue (bias, activation, gammas):
+
+        y[p,c] = swiglu(x[tok(p)] . w1[e][:, 2c] + b1[e][2c],  x[tok(p)] . w1[e][:, 2c+1] + b1[e][2c+1]) * g_in[p]
+        swiglu(g, u) = s*u + s,  s = g'/(1 + exp(-alpha*g')),  g' = min(g, limit),  u clamped to +-limit
+        z[p,:] = (y[p,:] . w2[e] + b2[e]) * g_out[p],      out[t] = sum over the k rows of token t
+
+    w1 [E,H,2I] holds gate and linear columns interleaved (even = gate), b1 [E,2I] likewise, as that library
+    expects; they are split into the [gate rows; up rows] layout of this package's kernels once per call.
+    `activation="silu"` names this swiglu, as in the reference; alpha defaults to 1.702.  The precision
+    configs are accepted for signature compatibility and must be None (bf16 only).
+    """
+    logger.debug("FLAGGEMS_SGLANG FUSED_MOE_WITH_BIAS")
+    assert inplace is False, "Inplace is not supported"
+    assert hidden_states.dtype == torch.bfloat16, "hidden_states must be bfloat16"
+    assert w1_pcg is None and w2_pcg is None, _UNSUPPORTED_FEATURE_MSG.format(name="precision configs")
+    if activation != "silu":
+        raise ValueError(f"Unsupported FusedMoe activation: {activation}")
+    assert w1.dtype == torch.bfloat16 and w2.dtype == torch.bfloat16, "w1/w2 must be bfloat16"
+    assert hidden_states.shape[-1] == w1.shape[-2], "hidden size mismatch"
+    T, H = hidden_states.shape
+    k = routing_data.n_expts_act
+    E = w1.shape[0]
+    M = T * k
+    dev = hidden_states.device
+    topk_indx = gather_indx.src_indx.long()          # sorted position -> flat slot
+    hist = routing_data.expt_hist.long()
+    expert_of_pos = torch.repeat_interleave(torch.arange(E, device=dev), hist, output_size=M)
+    ids_flat = torch.empty(M, dtype=torch.int32, device=dev)
+    ids_flat[topk_indx] = expert_of_pos.to(torch.int32)
+    w_flat = torch.empty(M, dtype=torch.float32, device=dev)
+    w_flat[topk_indx] = routing_data.gate_scal.float()
+    # [E,H,2I] interleaved columns -> [E,2I,H] with the gate rows first
+    w1_rows = w1.transpose(1, 2)
+    w1_split = torch.cat((w1_rows[:, 0::2], w1_rows[:, 1::2]), dim=1).contiguous()
+    b1_split = None if b1 is None else torch.cat((b1[:, 0::2], b1[:, 1::2]), dim=1)
+    z_or_out = fused_experts(
+        hidden_states, w1_split, _k_major(w2), w_flat.view(T, k), ids_flat.view(T, k), activation="swiglu_oai",
+        apply_router_weight_on_input=apply_router_weight_on_input, no_combine=scatter_indx is None,
+        b1=b1_split, b2=b2, gemm1_alpha=gemm1_alpha, gemm1_clamp_limit=gemm1_clamp_limit,
+    )
+    if scatter_indx is None:
+        return z_or_out.view(M, H)[topk_indx]
+    return z_or_out.view(T, H)
+
+
 @dataclass
 class StandardCombineInput:
     hidden_states: torch.Tensor
@@ -481,6 +566,7 @@ __all__ = [
     "fused_experts",
     "fused_moe",
     "triton_kernel_fused_experts",
+    "triton_kernel_fused_experts_with_bias",
     "fused_moe_flagos",
     "standard_topk_to_routing",
     "RoutingData",

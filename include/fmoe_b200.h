@@ -35,9 +35,13 @@ extern "C" {
 #define FMOE_BF16 1
 #define FMOE_E4M3 2
 
-/* gated activation applied by gemm1 */
-#define FMOE_ACT_SILU 0
-#define FMOE_ACT_GELU 1
+/* gated activation applied by gemm1 (g = gate accumulator, u = up accumulator, both after the optional bias) */
+#define FMOE_ACT_SILU 0        /* silu(g*rs) * (u*rs): the row scale goes in first, as in the reference's gemm1 + silu pass */
+#define FMOE_ACT_GELU 1        /* gelu(g*rs) * (u*rs) */
+#define FMOE_ACT_SWIGLU_OAI 2  /* g' = min(g, limit), u' = clamp(u, -limit, limit) (limit > 0 only),
+                                  s = g' / (1 + exp(-alpha*g')), out = (s*u' + s) * rs: the swiglu of the bias variant
+                                  (src/flaggems_sglang/ops/fused_moe.py:235-325, third-party triton_kernels.swiglu);
+                                  bias, activation, then row scale, the order of that path's GEMM epilogue */
 
 /* grouped-GEMM kernel families (fmoe_gemm_args.variant) */
 #define FMOE_VARIANT_AUTO 0
@@ -164,6 +168,11 @@ typedef struct fmoe_gemm_args {
   const float* row_scale; /* [numel] top-k weights by flat slot, or NULL                 */
   void* out;           /* gemm1: [sorted_cap, I] in sorted order; gemm2: [numel, H] by slot */
   float* out_scale;    /* gemm1 with out_dtype e4m3: [sorted_cap, I/128]                 */
+  const float* bias;   /* optional f32 [E, rows of w per expert] added to the accumulator first:
+                          gemm1 [E,2I] (gate entries then up entries), gemm2 [E,H].  SIMT, STREAM and bf16
+                          TCGEN05 kernels                                                             */
+  float act_alpha;     /* FMOE_ACT_SWIGLU_OAI                                                         */
+  float act_limit;     /* FMOE_ACT_SWIGLU_OAI: clamp limit, <= 0 for none                             */
   void* const* out_rows; /* gemm2, optional: DEVICE array [numel] of row addresses; row `slot` is written
                             at out_rows[slot] instead of out + slot*H (NULL entry: row skipped).  The
                             addresses may be peer memory (expert-parallel combine fused into the
@@ -188,7 +197,8 @@ int fmoe_moe_sum(const void* z, int dtype, int64_t T, int k, int64_t H, float sc
 /*
  * Whole expert computation in one call: align -> [row gather / activation quantisation] -> gemm1+silu ->
  * [quantisation] -> gemm2 * weight -> moe_sum.  Takes over src/flaggems_sglang/ops/fused_moe.py:197-232
- * (`triton_kernel_fused_experts` body) on the serving-side layouts w1 [E,2I,H], w2 [E,H,I].
+ * (`triton_kernel_fused_experts` body) and, with b1/b2 and FMOE_ACT_SWIGLU_OAI, :235-325
+ * (`triton_kernel_fused_experts_with_bias`) on the serving-side layouts w1 [E,2I,H], w2 [E,H,I].
  * All intermediates live in the caller's `workspace` (size from fmoe_fused_experts_workspace_bytes);
  * nothing is allocated and the host is never synchronised.
  */
@@ -215,6 +225,10 @@ typedef struct fmoe_fused_args {
   void* out;            /* [T,H] or [T,k,H]                                                               */
   void* workspace;      /* 256-byte aligned                                                               */
   int64_t workspace_bytes;
+  const float* b1;      /* optional f32 [E,2I] bias of the gate/up projection (gate entries then up entries)     */
+  const float* b2;      /* optional f32 [E,H] bias of the down projection                                   */
+  float act_alpha;      /* FMOE_ACT_SWIGLU_OAI                                                              */
+  float act_limit;      /* FMOE_ACT_SWIGLU_OAI: clamp limit, <= 0 for none                                  */
   void* const* out_rows; /* with no_combine: optional DEVICE array [T*k] of row addresses that replace
                             out + slot*H (see fmoe_gemm_args.out_rows); `out` may then be NULL            */
 } fmoe_fused_args;

@@ -158,6 +158,117 @@ def fused_experts(
     return out.to(dtype)
 
 
+def swiglu_oai(y1: torch.Tensor, alpha: float = 1.702, limit: float | None = None) -> torch.Tensor:
+    """The gated unit of the reference's bias variant, on INTERLEAVED columns (even = gate, odd = linear), fp32:
+
+        g = y1[..., 0::2] clamped to (-inf, limit], u = y1[..., 1::2] clamped to [-limit, limit],
+        s = g / (1 + exp(-alpha*g)),  out = s*u + s.
+
+    The reference only names the function (`swiglu_fn`, ref:src/flaggems_sglang/ops/fused_moe.py:261, 276); the
+    arithmetic lives in the third-party dependency `triton_kernels` (not pinned by the reference): this restates
+    its published `swiglu_torch` / `compute_swiglu` (triton_kernels/swiglu.py, swiglu_details/_swiglu.py).
+    """
+    f = y1.to(torch.float32)
+    g, u = f[..., 0::2], f[..., 1::2]
+    if limit is not None:
+        g = g.clamp(max=limit)
+        u = u.clamp(min=-limit, max=limit)
+    sgl = g / (1.0 + torch.exp(-alpha * g))
+    return sgl * u + sgl
+
+
+def reference_fused_experts_with_bias(
+    x: torch.Tensor,
+    w1: torch.Tensor,
+    b1: torch.Tensor | None,
+    w2: torch.Tensor,
+    b2: torch.Tensor | None,
+    routing: dict,
+    apply_router_weight_on_input: bool = False,
+    alpha: float | None = None,
+    limit: float | None = None,
+    no_combine: bool = False,
+) -> torch.Tensor:
+    """The bias variant on the reference's layouts (ref:src/flaggems_sglang/ops/fused_moe.py:235-325):
+    w1 [E,H,2I] with interleaved gate/linear columns, b1 [E,2I] likewise, w2 [E,I,H], b2 [E,H], routing tables as
+    in `reference_fused_experts`.  Both `matmul_ogs` calls apply bias, then the fused activation, then the gammas
+    and round once to the activation dtype (third-party epilogue order; :303-324 pass `bias`, `fused_activation`,
+    `gammas` to it):
+
+        y[p] = rb( swiglu(x[tok(p)] @ w1[e] + b1[e]) * g_in[p] )
+        z[p] = rb( (y[p] @ w2[e] + b2[e]) * g_out[p] ),    out[t] = rb( sum_j z[gate_indx[t*k + j]] )
+
+    Parity of this function is unpinned against the reference itself (its call does not run against any released
+    `triton_kernels`); `swiglu_oai` is pinned against that library's torch reference in the tests.
+    """
+    dtype = x.dtype
+    k = routing["n_expts_act"]
+    alpha = 1.702 if alpha is None else alpha
+    xf = x.detach().cpu().to(torch.float32)
+    topk_indx = torch.from_numpy(routing["topk_indx"].astype(np.int64))
+    gate_indx = torch.from_numpy(routing["gate_indx"].astype(np.int64))
+    gs = torch.from_numpy(np.asarray(routing["gate_scal"], dtype=np.float32))
+    M = topk_indx.numel()
+    H = w2.shape[-1]
+    tok = topk_indx // k
+    Z = torch.zeros(M, H, dtype=torch.float32)
+    for e, lo, hi in _expert_segments(routing["hist"]):
+        acc1 = xf[tok[lo:hi]] @ w1[e].detach().cpu().to(torch.float32)
+        if b1 is not None:
+            acc1 = acc1 + b1[e].detach().cpu().to(torch.float32)
+        y = swiglu_oai(acc1, alpha, limit)
+        if apply_router_weight_on_input:
+            y = y * gs[lo:hi, None]
+        y = _rb(y, dtype)
+        acc2 = y @ w2[e].detach().cpu().to(torch.float32)
+        if b2 is not None:
+            acc2 = acc2 + b2[e].detach().cpu().to(torch.float32)
+        if not apply_router_weight_on_input:
+            acc2 = acc2 * gs[lo:hi, None]
+        Z[lo:hi] = _rb(acc2, dtype)
+    if no_combine:
+        return Z.to(dtype)
+    T = M // k
+    return moe_sum(Z[gate_indx].view(T, k, H)).to(dtype)
+
+
+def fused_experts_with_bias(x, w1, b1, w2, b2, topk_weights, topk_ids, apply_router_weight_on_input=False,
+                            alpha=None, limit=None, no_combine=False) -> torch.Tensor:
+    """Same computation on the serving-side layouts: w1 [E,2I,H] with the gate rows first ([0,I) gate, [I,2I)
+    linear), b1 [E,2I] likewise, w2 [E,H,I], b2 [E,H]; slots in `topk_ids` order."""
+    dtype = x.dtype
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E, twoI, _ = w1.shape
+    I = twoI // 2
+    alpha = 1.702 if alpha is None else alpha
+    xf = x.detach().cpu().to(torch.float32)
+    ids = topk_ids.detach().cpu().to(torch.int64).reshape(-1)
+    wts = topk_weights.detach().cpu().to(torch.float32).reshape(-1)
+    Z = torch.zeros(T * k, H, dtype=torch.float32)
+    for e in range(E):
+        slots = torch.nonzero(ids == e).reshape(-1)
+        if slots.numel() == 0:
+            continue
+        acc1 = xf[slots // k] @ w1[e].detach().cpu().to(torch.float32).t()
+        if b1 is not None:
+            acc1 = acc1 + b1[e].detach().cpu().to(torch.float32)
+        inter = torch.stack((acc1[:, :I], acc1[:, I:]), dim=-1).reshape(-1, twoI)  # back to interleaved columns
+        y = swiglu_oai(inter, alpha, limit)
+        if apply_router_weight_on_input:
+            y = y * wts[slots, None]
+        y = _rb(y, dtype)
+        acc2 = y @ w2[e].detach().cpu().to(torch.float32).t()
+        if b2 is not None:
+            acc2 = acc2 + b2[e].detach().cpu().to(torch.float32)
+        if not apply_router_weight_on_input:
+            acc2 = acc2 * wts[slots, None]
+        Z[slots] = _rb(acc2, dtype)
+    if no_combine:
+        return Z.view(T, k, H).to(dtype)
+    return moe_sum(Z.view(T, k, H)).to(dtype)
+
+
 def moe_sum(z: torch.Tensor) -> torch.Tensor:
     """out[t] = sum_j z[t,j], sequential fp32 adds in ascending j; returns fp32."""
     zf = z.detach().cpu().to(torch.float32)

@@ -19,6 +19,8 @@ reference.  What is captured:
   (TRITON_INTERPRET=1) with an fp32 output buffer, so the stored values are the
   fp32 results before any output rounding (the interpreter truncates instead of
   rounding when it stores into bf16, so a bf16 output would not be faithful).
+* ``swiglu_*.npz``: ``triton_kernels.swiglu.swiglu_torch`` (the third-party library's torch reference of the
+  gated unit the reference's bias variant names) on seeded fp32 inputs, with and without the clamp.
 """
 import argparse
 import os
@@ -96,6 +98,22 @@ def main():
             y1_bits=y1.view(torch.int16).numpy(), out_f32=out.numpy(),
         )
         print("wrote silu", rows, half)
+
+    # ---- swiglu of the bias variant: the third-party library's own torch reference ----
+    # (the reference op only names `swiglu_fn`, src/flaggems_sglang/ops/fused_moe.py:261; the arithmetic is
+    # triton_kernels.swiglu, vendored copy given by --triton-kernels)
+    from triton_kernels.swiglu import PrecisionConfig as SwigluPrecisionConfig
+    from triton_kernels.swiglu import swiglu_torch
+
+    for rows, half, alpha, limit in [(9, 64, 1.702, 7.0), (33, 40, 1.0, None), (4, 128, 1.702, 0.75)]:
+        a = torch.randn(rows, 2 * half, generator=g) * 4.0
+        out = swiglu_torch(a, alpha, SwigluPrecisionConfig(limit=limit))
+        np.savez_compressed(
+            os.path.join(here, f"swiglu_rows{rows}_half{half}.npz"),
+            a_f32=a.numpy(), out_f32=out.numpy(), alpha=np.float32(alpha),
+            limit=np.float32(-1.0 if limit is None else limit),
+        )
+        print("wrote swiglu", rows, half)
 
 
 if __name__ == "__main__":

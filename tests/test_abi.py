@@ -42,10 +42,10 @@ def test_struct_layout_matches_header():
     from flaggems_sglang_b200 import _C
 
     # 8 int32 + 6 int64 + 10 pointers
-    assert ctypes.sizeof(_C.GemmArgs) == 8 * 4 + 6 * 8 + 11 * 8
+    assert ctypes.sizeof(_C.GemmArgs) == 8 * 4 + 6 * 8 + 10 * 8 + (8 + 4 + 4) + 8
     assert _C.GemmArgs.numel.offset == 32 and _C.GemmArgs.a.offset == 80
     # 8 int32 + 3 int64 + 2 float + 9 pointers + 1 int64
-    assert ctypes.sizeof(_C.FusedArgs) == 152 and _C.FusedArgs.hidden.offset == 64
+    assert ctypes.sizeof(_C.FusedArgs) == 144 + (8 + 8 + 4 + 4) + 8 and _C.FusedArgs.hidden.offset == 64
 
 
 def test_version_and_error_buffer(lib):

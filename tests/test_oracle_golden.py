@@ -82,6 +82,43 @@ def test_silu_and_mul_matches_reference_kernel(path):
     np.testing.assert_allclose(got, g["out_f32"], rtol=2e-6, atol=1e-30)
 
 
+SWIGLU = sorted(glob.glob(os.path.join(GOLDEN, "swiglu_*.npz")))
+
+
+@pytest.mark.parametrize("path", SWIGLU, ids=[os.path.basename(p)[7:-4] for p in SWIGLU])
+def test_swiglu_matches_third_party_torch_reference(path):
+    g = np.load(path)
+    limit = float(g["limit"])
+    got = OE.swiglu_oai(torch.from_numpy(g["a_f32"]), float(g["alpha"]), None if limit < 0 else limit).numpy()
+    # a/(1+exp(-alpha a)) against a*sigmoid(alpha a): the same value up to fp32 rounding of exp and the division
+    np.testing.assert_allclose(got, g["out_f32"], rtol=3e-6, atol=1e-6)
+
+
+def test_bias_variant_layouts_agree():
+    """The bias variant on the reference's layouts (interleaved gate/linear columns, routing tables) and on the
+    serving-side layouts (gate rows first, topk ids) is one computation."""
+    torch.manual_seed(5)
+    T, H, I, E, k = 19, 64, 48, 6, 3
+    x = torch.randn(T, H).bfloat16()
+    w1_ref = (torch.randn(E, H, 2 * I) / H ** 0.5).bfloat16()   # interleaved columns
+    w2_ref = (torch.randn(E, I, H) / I ** 0.5).bfloat16()
+    b1_ref = torch.randn(E, 2 * I) * 0.2
+    b2 = torch.randn(E, H) * 0.2
+    w, ids = OR.softmax_topk(torch.randn(T, E), k, True)
+    r = OR.standard_topk_to_routing(w, ids, E)
+    for on_input in (False, True):
+        ref = OE.reference_fused_experts_with_bias(x, w1_ref, b1_ref, w2_ref, b2, r, on_input, 1.702, 7.0)
+        rows = w1_ref.transpose(1, 2)
+        w1_split = torch.cat((rows[:, 0::2], rows[:, 1::2]), dim=1).contiguous()
+        b1_split = torch.cat((b1_ref[:, 0::2], b1_ref[:, 1::2]), dim=1)
+        # slots in the reference are ordered by ascending expert per token: give the serving-side form the same order
+        ids2, perm = torch.sort(ids, dim=1)
+        w2d = torch.gather(w, 1, perm)
+        got = OE.fused_experts_with_bias(x, w1_split, b1_split, w2_ref.transpose(1, 2).contiguous(), b2, w2d, ids2,
+                                         on_input, 1.702, 7.0)
+        assert torch.equal(ref, got)
+
+
 def test_restatements_agree_with_dense_formulation():
     """Config 1 of the benchmark set (T=16,H=256,I=512,E=8,k=2, fp32, seed 0): the
     sorted/grouped restatements equal the naive per-token MoE."""

@@ -88,7 +88,9 @@ __device__ __forceinline__ bool warp_wait_relaxed(uint64_t* bar, uint32_t parity
 // GATHER: the A operand is the un-permuted [a_rows, K] input; the producer warp fetches row
 // sorted_token_ids[p] / top_k for sorted position p with TMA gather4 (32 lanes x 4 rows = one 128-row stage),
 // padding positions read row a_rows, which is outside the tensor and arrives as zeros.
-template <bool GATED, int KB, bool GATHER>
+// EXTRA: the epilogue adds a bias and/or applies the swiglu_oai unit; a separate instantiation, so that the plain
+// silu/gelu kernels keep their register allocation.
+template <bool GATED, int KB, bool GATHER, bool EXTRA>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                             const TcParams p) {
@@ -291,9 +293,10 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       const bool valid = slot >= 0 && slot < p.numel;
       const float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
       // bias entries of this tile's columns (the same for every row: broadcast loads)
-      const float* bias = p.bias ? p.bias + (int64_t)min(max(p.expert_ids[m_blk], 0), p.num_experts - 1) * p.w_rows +
-                                       (int64_t)n_tile * (GATED ? 128 : 256)
-                                 : nullptr;
+      const float* bias = (EXTRA && p.bias)
+                              ? p.bias + (int64_t)min(max(p.expert_ids[m_blk], 0), p.num_experts - 1) * p.w_rows +
+                                    (int64_t)n_tile * (GATED ? 128 : 256)
+                              : nullptr;
       const long long te0 = p.profile ? clock64() : 0;
       const bool oke = warp_wait_relaxed(&acc_full[acc], acc_phase);
       const long long te1 = p.profile ? clock64() : 0;
@@ -318,16 +321,29 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint32_t w[4];
+              // bias of the 8 gate and 8 up columns of this piece: four 16-byte broadcast loads
+              float bgv[8], buv[8];
+              if (EXTRA && bias) {
+                const float4* pg = reinterpret_cast<const float4*>(bias + c * 32 + v * 8);
+                const float4* pu = reinterpret_cast<const float4*>(bias + p.n + c * 32 + v * 8);
+                const float4 g0 = __ldg(pg), g1 = __ldg(pg + 1), u0 = __ldg(pu), u1 = __ldg(pu + 1);
+                bgv[0] = g0.x; bgv[1] = g0.y; bgv[2] = g0.z; bgv[3] = g0.w;
+                bgv[4] = g1.x; bgv[5] = g1.y; bgv[6] = g1.z; bgv[7] = g1.w;
+                buv[0] = u0.x; buv[1] = u0.y; buv[2] = u0.z; buv[3] = u0.w;
+                buv[4] = u1.x; buv[5] = u1.y; buv[6] = u1.z; buv[7] = u1.w;
+              } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) bgv[q] = buv[q] = 0.f;
+              }
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int i = v * 8 + j * 2;
                 float o0, o1;
-                if (bias || p.activation == FMOE_ACT_SWIGLU_OAI) {
-                  const float* bg = bias ? bias + c * 32 + i : nullptr;
-                  o0 = gated_output<true>(__uint_as_float(g[i]), __uint_as_float(u[i]), bg ? bg[0] : 0.f,
-                                          bg ? bg[p.n] : 0.f, rs, p.activation, p.act_alpha, p.act_limit);
-                  o1 = gated_output<true>(__uint_as_float(g[i + 1]), __uint_as_float(u[i + 1]), bg ? bg[1] : 0.f,
-                                          bg ? bg[p.n + 1] : 0.f, rs, p.activation, p.act_alpha, p.act_limit);
+                if constexpr (EXTRA) {
+                  o0 = gated_output<true>(__uint_as_float(g[i]), __uint_as_float(u[i]), bgv[2 * j], buv[2 * j], rs,
+                                          p.activation, p.act_alpha, p.act_limit);
+                  o1 = gated_output<true>(__uint_as_float(g[i + 1]), __uint_as_float(u[i + 1]), bgv[2 * j + 1],
+                                          buv[2 * j + 1], rs, p.activation, p.act_alpha, p.act_limit);
                 } else {
                   o0 = act_mul_fast(__uint_as_float(g[i]) * rs, __uint_as_float(u[i]) * rs, p.activation);
                   o1 = act_mul_fast(__uint_as_float(g[i + 1]) * rs, __uint_as_float(u[i + 1]) * rs, p.activation);
@@ -353,11 +369,20 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
               uint32_t w[4];
+              float bv[8];
+              if (EXTRA && bias) {
+                const float4* pb = reinterpret_cast<const float4*>(bias + c * 32 + v * 8);
+                const float4 b0 = __ldg(pb), b1 = __ldg(pb + 1);
+                bv[0] = b0.x; bv[1] = b0.y; bv[2] = b0.z; bv[3] = b0.w;
+                bv[4] = b1.x; bv[5] = b1.y; bv[6] = b1.z; bv[7] = b1.w;
+              } else {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) bv[q] = 0.f;
+              }
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int i = v * 8 + j * 2;
-                const float b0 = bias ? bias[c * 32 + i] : 0.f, b1 = bias ? bias[c * 32 + i + 1] : 0.f;
-                w[j] = pack_bf16x2((__uint_as_float(r[i]) + b0) * rs, (__uint_as_float(r[i + 1]) + b1) * rs);
+                w[j] = pack_bf16x2((__uint_as_float(r[i]) + bv[2 * j]) * rs, (__uint_as_float(r[i + 1]) + bv[2 * j + 1]) * rs);
               }
               dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
             }
@@ -435,14 +460,14 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t
 
 namespace {
 
-template <bool GATED, int KB, bool GATHER>
+template <bool GATED, int KB, bool GATHER, bool EXTRA>
 int launch(const GemmParams& g, cudaStream_t st) {
   constexpr int SMEM_BYTES = Ring<KB>::SMEM_BYTES, KBYTES = KB;
   const int sm_count = device_sm_count();
   static cudaError_t attr_err = cudaSuccess;
   static std::once_flag once_attr;
   std::call_once(once_attr, [] {
-    attr_err = cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED, KB, GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    attr_err = cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     SMEM_BYTES);
   });
   if (attr_err != cudaSuccess)
@@ -481,7 +506,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sm_count > 0 ? sm_count : 148, max_tiles));
   p.group_m = pick_group_m(BM, g.k * 2);
   p.profile = getenv("FMOE_TC_PROFILE") != nullptr;
-  grouped_gemm_tcgen05_kernel<GATED, KB, GATHER><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
+  grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_kernel");
 }
 
@@ -492,6 +517,7 @@ bool gemm_tcgen05_supports(const GemmParams& p, bool gated) {
   if (p.block_size != BM) return false;
   // gather mode: gate/up GEMM only; one int4 of sorted ids per lane
   if (p.a_gather && (!gated || p.top_k < 1 || !aligned16(p.sorted_token_ids))) return false;
+  if (p.bias && !aligned16(p.bias)) return false;  // 16-byte bias loads in the epilogue (n % 32 == 0 holds already)
   if (p.k <= 0 || (p.k * 2) % 16 != 0) return false;            // TMA row stride must be a multiple of 16 bytes
   if (p.n <= 0 || p.n % (gated ? 128 : 32) != 0) return false;  // gate/up pairing; 64-byte epilogue stores
   if (!aligned16(p.a) || !aligned16(p.w) || !(aligned16(p.out) && (p.out || (!gated && p.out_rows)))) return false;
@@ -507,8 +533,10 @@ int gemm_tcgen05(const GemmParams& p, bool gated, cudaStream_t st) {
                 "n %% %d == 0, 16-byte aligned pointers (got dtype=%d block=%d a_gather=%d n=%lld k=%lld)",
                 gated ? 128 : 32, p.dtype, p.block_size, p.a_gather, (long long)p.n, (long long)p.k);
   if (p.max_blocks <= 0) return FMOE_OK;
-  if (p.a_gather) return launch<true, 128, true>(p, st);
-  return gated ? launch<true, 128, false>(p, st) : launch<false, 128, false>(p, st);
+  const bool extra = p.bias != nullptr || (gated && p.activation == FMOE_ACT_SWIGLU_OAI);
+  if (p.a_gather) return extra ? launch<true, 128, true, true>(p, st) : launch<true, 128, true, false>(p, st);
+  if (gated) return extra ? launch<true, 128, false, true>(p, st) : launch<true, 128, false, false>(p, st);
+  return extra ? launch<false, 128, false, true>(p, st) : launch<false, 128, false, false>(p, st);
 }
 
 namespace {

@@ -455,6 +455,14 @@ def triton_kernel_fused_experts(
     return z_or_out.view(T, H)
 
 
+def _split_interleaved(w13_rows: torch.Tensor, b13: Optional[torch.Tensor]):
+    """[E,2I,H] with gate and linear rows interleaved (even = gate), b13 [E,2I] likewise -> the same tensors with
+    the I gate rows first, the layout of this package's gate/up kernels.  One copy of w13."""
+    w = torch.cat((w13_rows[:, 0::2], w13_rows[:, 1::2]), dim=1).contiguous()
+    b = None if b13 is None else torch.cat((b13[:, 0::2], b13[:, 1::2]), dim=1)
+    return w, b
+
+
 def triton_kernel_fused_experts_with_bias(
     hidden_states: torch.Tensor,
     w1: torch.Tensor,
@@ -508,10 +516,7 @@ def triton_kernel_fused_experts_with_bias(
     ids_flat[topk_indx] = expert_of_pos.to(torch.int32)
     w_flat = torch.empty(M, dtype=torch.float32, device=dev)
     w_flat[topk_indx] = routing_data.gate_scal.float()
-    # [E,H,2I] interleaved columns -> [E,2I,H] with the gate rows first
-    w1_rows = w1.transpose(1, 2)
-    w1_split = torch.cat((w1_rows[:, 0::2], w1_rows[:, 1::2]), dim=1).contiguous()
-    b1_split = None if b1 is None else torch.cat((b1[:, 0::2], b1[:, 1::2]), dim=1)
+    w1_split, b1_split = _split_interleaved(w1.transpose(1, 2), b1)
     z_or_out = fused_experts(
         hidden_states, w1_split, _k_major(w2), w_flat.view(T, k), ids_flat.view(T, k), activation="swiglu_oai",
         apply_router_weight_on_input=apply_router_weight_on_input, no_combine=scatter_indx is None,
@@ -537,10 +542,34 @@ def fused_moe_flagos(obj, layer: torch.nn.Module, dispatch_output):
     and returns an object with `.hidden_states`.
     """
     cfg = obj.runner.config
-    if getattr(layer, "w13_weight_bias", None) is not None or getattr(layer, "w2_weight_bias", None) is not None:
-        raise NotImplementedError("expert biases (fused swiglu variant) are not supported")
+    b13, b2 = getattr(layer, "w13_weight_bias", None), getattr(layer, "w2_weight_bias", None)
     hidden_states = dispatch_output.hidden_states
     topk_output = dispatch_output.topk_output
+    if b13 is not None or b2 is not None:
+        # bias variant (src/flaggems_sglang/ops/fused_moe.py:380-398): interleaved gate/linear rows, swiglu
+        assert b13 is not None and b2 is not None, "Bias execution requires both w13_bias and w2_bias"
+        alpha, limit = getattr(cfg, "gemm1_alpha", None), getattr(cfg, "gemm1_clamp_limit", None)
+        if hasattr(topk_output, "topk_weights"):
+            w13, b13s = _split_interleaved(layer.w13_weight, b13)
+            out = fused_experts(
+                hidden_states, w13, layer.w2_weight, topk_output.topk_weights, topk_output.topk_ids,
+                activation="swiglu_oai", apply_router_weight_on_input=cfg.apply_router_weight_on_input,
+                no_combine=cfg.no_combine, routed_scaling_factor=None if cfg.no_combine else cfg.routed_scaling_factor,
+                b1=b13s, b2=b2, gemm1_alpha=alpha, gemm1_clamp_limit=limit,
+            )
+        else:
+            routing_data, gather_indx, scatter_indx = topk_output
+            out = triton_kernel_fused_experts_with_bias(
+                hidden_states, layer.w13_weight.transpose(-1, -2), None, b13, layer.w2_weight.transpose(-1, -2), None, b2,
+                routing_data, gather_indx, None if cfg.no_combine else scatter_indx, activation=cfg.activation,
+                apply_router_weight_on_input=cfg.apply_router_weight_on_input, gemm1_alpha=alpha,
+                gemm1_clamp_limit=limit,
+            )
+            if cfg.no_combine:
+                out = out.view(hidden_states.shape[0], -1, hidden_states.shape[-1])
+            elif cfg.routed_scaling_factor is not None and cfg.routed_scaling_factor != 1.0:
+                out.mul_(cfg.routed_scaling_factor)
+        return StandardCombineInput(hidden_states=out)
     if hasattr(topk_output, "topk_weights"):
         tw, ti = topk_output.topk_weights, topk_output.topk_ids
         out = fused_experts(

@@ -104,3 +104,32 @@ def test_bias_variant_is_refused_with_fp8_weights(fg):
     with pytest.raises(AssertionError, match="fp8"):
         fg.fused_experts(x.cuda(), w1q.cuda(), w2q.cuda(), tw.cuda(), ti.cuda(), use_fp8_w8a8=True, w1_scale=s1.cuda(),
                          w2_scale=s2.cuda(), block_shape=[128, 128], b1=b1.cuda())
+
+
+def test_hook_routes_biased_layers_to_the_bias_variant(fg):
+    """`fused_moe_flagos` with `w13_weight_bias` / `w2_weight_bias` on the layer (reference hook :380-398): the
+    serving-side w13 [E,2I,H] holds gate and linear rows interleaved."""
+    from types import SimpleNamespace as NS
+
+    T, H, I, E, k = 21, 256, 128, 8, 2
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w13 = (torch.randn(E, 2 * I, H, generator=g) / H ** 0.5).bfloat16()     # interleaved rows
+    w2 = (torch.randn(E, H, I, generator=g) / I ** 0.5).bfloat16()
+    b13 = torch.randn(E, 2 * I, generator=g) * 0.3
+    b2 = torch.randn(E, H, generator=g) * 0.3
+    tw, ti = OR.softmax_topk(torch.randn(T, E, generator=g), k, True)
+    r = OR.standard_topk_to_routing(tw, ti, E)
+    ref = OE.reference_fused_experts_with_bias(x, w13.transpose(1, 2), b13, w2.transpose(1, 2), b2, r, False, 1.702, 7.0)
+    layer = NS(w13_weight=w13.cuda(), w2_weight=w2.cuda(), w13_weight_bias=b13.cuda(), w2_weight_bias=b2.cuda())
+    cfg = NS(num_experts=E, activation="silu", apply_router_weight_on_input=False, no_combine=False,
+             routed_scaling_factor=None, gemm1_alpha=1.702, gemm1_clamp_limit=7.0)
+    disp = NS(hidden_states=x.cuda(), topk_output=NS(topk_weights=tw.cuda(), topk_ids=ti.cuda()))
+    out = fg.fused_moe_flagos(NS(runner=NS(config=cfg)), layer, disp).hidden_states
+    assert_close_moe(out, ref, "bf16", "hook, (weights, ids) routing")
+    disp2 = NS(hidden_states=x.cuda(), topk_output=fg.standard_topk_to_routing(tw.cuda(), ti.cuda(), E))
+    out2 = fg.fused_moe_flagos(NS(runner=NS(config=cfg)), layer, disp2).hidden_states
+    assert_close_moe(out2, ref, "bf16", "hook, routing triple")
+    with pytest.raises(AssertionError, match="both w13_bias and w2_bias"):
+        fg.fused_moe_flagos(NS(runner=NS(config=cfg)), NS(w13_weight=w13.cuda(), w2_weight=w2.cuda(),
+                                                          w13_weight_bias=b13.cuda(), w2_weight_bias=None), disp)

@@ -81,6 +81,7 @@ SIGNATURES = {
     "fmoe_gemm1_silu": (c_int, [POINTER(GemmArgs), c_void_p]),
     "fmoe_gemm2": (c_int, [POINTER(GemmArgs), c_void_p]),
     "fmoe_moe_sum": (c_int, [c_void_p, c_int, c_int64, c_int, c_int64, c_float, c_void_p, c_void_p]),
+    "fmoe_moe_sum_add": (c_int, [c_void_p, c_int, c_int64, c_int, c_int64, c_float, c_void_p, c_void_p, c_void_p]),
     "fmoe_pick_variant": (c_int, [c_int, c_int64, c_int, c_int64, c_int64, c_int, POINTER(c_int), POINTER(c_int)]),
     "fmoe_fused_experts_workspace_bytes": (c_int64, [POINTER(FusedArgs)]),
     "fmoe_fused_experts": (c_int, [POINTER(FusedArgs), c_void_p]),

@@ -131,7 +131,8 @@ gather_rows_kernel(const uint4* __restrict__ x, int64_t rows_out, int64_t vec_pe
 // each thread owns 8 bf16 (or 4 f32) columns of one token and adds the k slots in order
 template <typename T>
 __global__ void __launch_bounds__(256)
-moe_sum_kernel(const T* __restrict__ z, int64_t Tn, int k, int64_t H, float scale, T* __restrict__ out) {
+moe_sum_kernel(const T* __restrict__ z, int64_t Tn, int k, int64_t H, float scale, const T* __restrict__ addend,
+               T* __restrict__ out) {
   pdl_entry();
   constexpr int V = 16 / sizeof(T);
   const int64_t vec_per_row = H / V;
@@ -154,6 +155,12 @@ moe_sum_kernel(const T* __restrict__ z, int64_t Tn, int k, int64_t H, float scal
       T r = from_f32<T>(acc[v]);
       if (scale != 1.0f) r = from_f32<T>(to_f32(r) * scale);
       o[v] = r;
+    }
+    if (addend) {  // e.g. the shared expert's output: one more rounded add, as the separate `+=` would do
+      uint4 raw = __ldg(reinterpret_cast<const uint4*>(addend + t * H) + c);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int v = 0; v < V; ++v) o[v] = from_f32<T>(to_f32(o[v]) + to_f32(e[v]));
     }
     reinterpret_cast<uint4*>(out + t * H)[c] = res;
   }
@@ -201,19 +208,25 @@ extern "C" int fmoe_gather_rows(const void* x, int elem_bytes, int64_t rows_out,
 
 extern "C" int fmoe_moe_sum(const void* z, int dtype, int64_t T, int k, int64_t H, float scale, void* out,
                             void* stream) {
+  return fmoe_moe_sum_add(z, dtype, T, k, H, scale, nullptr, out, stream);
+}
+
+extern "C" int fmoe_moe_sum_add(const void* z, int dtype, int64_t T, int k, int64_t H, float scale,
+                                const void* addend, void* out, void* stream) {
   using namespace fmoe;
   FMOE_REQUIRE(dtype == FMOE_BF16 || dtype == FMOE_F32, "moe_sum: dtype must be bf16 or f32");
   const int eb = dtype == FMOE_BF16 ? 2 : 4;
   FMOE_REQUIRE(k >= 1 && H > 0 && (H * eb) % 16 == 0, "moe_sum: need k >= 1 and H*elem %% 16 == 0");
   if (T <= 0) return FMOE_OK;
-  FMOE_REQUIRE(z && out && aligned16(z) && aligned16(out), "moe_sum: null or misaligned pointer");
+  FMOE_REQUIRE(z && out && aligned16(z) && aligned16(out) && aligned16(addend), "moe_sum: null or misaligned pointer");
   int64_t total = T * (H * eb / 16);
   unsigned grid = (unsigned)std::min<int64_t>(ceil_div<int64_t>(total, 256), 148 * 16);
   auto st = (cudaStream_t)stream;
   if (dtype == FMOE_BF16)
     launch_pdl(moe_sum_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (const __nv_bfloat16*)z, T, k, H, scale,
-               (__nv_bfloat16*)out);
+               (const __nv_bfloat16*)addend, (__nv_bfloat16*)out);
   else
-    launch_pdl(moe_sum_kernel<float>, dim3(grid), dim3(256), 0, st, (const float*)z, T, k, H, scale, (float*)out);
+    launch_pdl(moe_sum_kernel<float>, dim3(grid), dim3(256), 0, st, (const float*)z, T, k, H, scale,
+               (const float*)addend, (float*)out);
   return launch_status("moe_sum_kernel");
 }

@@ -193,6 +193,10 @@ int fmoe_gemm2(const fmoe_gemm_args* args, void* stream);
  */
 int fmoe_moe_sum(const void* z, int dtype, int64_t T, int k, int64_t H, float scale,
                  void* out, void* stream);
+/* Same, then out = round(out + addend) with addend [T, H] of the same dtype (NULL: none): the shared expert's
+ * output joins the routed experts' in the combine pass instead of in a separate `+=` over [T, H]. */
+int fmoe_moe_sum_add(const void* z, int dtype, int64_t T, int k, int64_t H, float scale,
+                     const void* addend, void* out, void* stream);
 
 /*
  * Whole expert computation in one call: align -> [row gather / activation quantisation] -> gemm1+silu ->

@@ -95,6 +95,26 @@ def test_moe_sum_bit_exact(fg, T, k, H, dtype, scale):
     assert torch.equal(out.cpu(), ref)
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("scale", [None, 2.5])
+def test_moe_sum_with_shared_expert_addend_bit_exact(fg, dtype, scale):
+    """out = round(round(round(sum_j z) * scale) + shared): the post-scale (ref fused_moe.py:415-420) and the
+    shared expert's `+=` folded into the combine pass, with the roundings of the separate ops."""
+    torch.manual_seed(11)
+    T, k, H = 37, 8, 1024
+    z = torch.randn(T, k, H).to(dtype)
+    shared = torch.randn(T, H).to(dtype)
+    out = torch.empty(T, H, dtype=dtype, device="cuda")
+    fg.moe_sum(z.cuda(), out, scale, shared_output=shared.cuda())
+    ref = OE.moe_sum(z).to(dtype)
+    if scale is not None:
+        ref = (ref.float() * scale).to(dtype)
+    ref = (ref.float() + shared.float()).to(dtype)
+    assert torch.equal(out.cpu(), ref)
+    with pytest.raises(ValueError, match="shared_output"):
+        fg.moe_sum(z.cuda(), out, scale, shared_output=shared[:, :512].cuda())
+
+
 def test_gather_rows_and_fused_gather_quant(fg):
     from flaggems_sglang_b200 import _C
 

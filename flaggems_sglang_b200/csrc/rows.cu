@@ -97,11 +97,15 @@ quant_group128_kernel(const InT* __restrict__ x, int64_t rows_out, int64_t K, co
       uint32_t lo = 0, hi = 0;
       if (amax <= 3.0e38f) {
         const float r = __frcp_rn(s);
+        float qv[8];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          lo |= (uint32_t)f32_to_e4m3_bits(div_by_shared(v[u][i], s, r)) << (8 * i);
-          hi |= (uint32_t)f32_to_e4m3_bits(div_by_shared(v[u][4 + i], s, r)) << (8 * i);
-        }
+        for (int i = 0; i < 8; ++i) qv[i] = div_by_shared(v[u][i], s, r);
+        // two values per conversion instruction (low byte = first value)
+        auto pair = [](float a, float b) {
+          return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+        };
+        lo = pair(qv[0], qv[1]) | (pair(qv[2], qv[3]) << 16);
+        hi = pair(qv[4], qv[5]) | (pair(qv[6], qv[7]) << 16);
       } else {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {

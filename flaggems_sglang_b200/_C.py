@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_uint32, c_void_p
 
 import torch  # noqa: F401  (loads the CUDA runtime the library links against)
 
@@ -30,10 +30,19 @@ class FmoeError(RuntimeError):
         self.code = code
 
 
-class GemmArgs(Structure):
+class _SizedStructure(Structure):
+    """ctypes mirror of an argument struct that begins with `struct_size`: filled in on construction."""
+
+    def __init__(self, *args, **kw):
+        super().__init__(*args, **kw)
+        self.struct_size = ctypes.sizeof(type(self))
+
+
+class GemmArgs(_SizedStructure):
     """Mirror of struct fmoe_gemm_args."""
 
     _fields_ = [
+        ("struct_size", c_uint32), ("reserved0", c_int32),
         ("dtype", c_int32), ("out_dtype", c_int32), ("variant", c_int32), ("num_experts", c_int32),
         ("top_k", c_int32), ("block_size", c_int32), ("a_gather", c_int32), ("activation", c_int32),
         ("numel", c_int64), ("n", c_int64), ("k", c_int64), ("a_rows", c_int64),
@@ -45,10 +54,11 @@ class GemmArgs(Structure):
     ]
 
 
-class FusedArgs(Structure):
+class FusedArgs(_SizedStructure):
     """Mirror of struct fmoe_fused_args."""
 
     _fields_ = [
+        ("struct_size", c_uint32), ("reserved0", c_int32),
         ("dtype", c_int32), ("variant", c_int32), ("num_experts", c_int32), ("top_k", c_int32),
         ("apply_router_weight_on_input", c_int32), ("no_combine", c_int32), ("zero_dropped", c_int32),
         ("activation", c_int32),

@@ -55,6 +55,9 @@ int validate_gemm(const GemmParams& a, bool gated, const char* who) {
 
 int dispatch_gemm(const fmoe_gemm_args* args, bool gated, void* stream, const char* who) {
   if (!args) return fail(FMOE_ERR_INVALID_ARG, "%s: args is null", who);
+  if (args->struct_size != sizeof(fmoe_gemm_args))
+    return fail(FMOE_ERR_INVALID_ARG, "%s: fmoe_gemm_args.struct_size is %u, this library's struct has %zu bytes "
+                "(binding built against another header?)", who, args->struct_size, sizeof(fmoe_gemm_args));
   const GemmParams& a = *args;
   int rc = validate_gemm(a, gated, who);
   if (rc) return rc;
@@ -82,7 +85,7 @@ int dispatch_gemm(const fmoe_gemm_args* args, bool gated, void* stream, const ch
 }  // namespace
 }  // namespace fmoe
 
-extern "C" int fmoe_version(void) { return 1; }
+extern "C" int fmoe_version(void) { return 2; }
 
 extern "C" const char* fmoe_last_error(void) { return fmoe::last_error_buffer(); }
 

@@ -8,6 +8,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
 
 #include "../../include/fmoe_b200.h"
 
@@ -73,6 +74,26 @@ inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
   (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // the error is picked up by launch_status()
 }
 #endif
+
+// One-time set-up that is a property of a DEVICE (cudaFuncSetAttribute, the SM count): runs once per device
+// ordinal, with that device current, so a process that drives several GPUs configures each of them.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+  std::mutex mu;
+  bool done[kMaxDevices] = {};
+};
+template <typename Fn>
+inline cudaError_t per_device_once(PerDeviceOnce& st, Fn fn) {
+  int dev = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  if (dev < 0 || dev >= kMaxDevices) return fn();
+  std::lock_guard<std::mutex> lock(st.mu);
+  if (st.done[dev]) return cudaSuccess;
+  err = fn();
+  if (err == cudaSuccess) st.done[dev] = true;
+  return err;
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -64,6 +64,9 @@ inline bool tc_gathers_input(int variant, int dtype) {
 }
 
 int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
+  if (a.struct_size != sizeof(fmoe_fused_args))
+    return fail(FMOE_ERR_INVALID_ARG, "fused_experts: fmoe_fused_args.struct_size is %u, this library's struct has %zu "
+                "bytes (binding built against another header?)", a.struct_size, sizeof(fmoe_fused_args));
   FMOE_REQUIRE(a.num_experts >= 1 && a.num_experts <= 1024 && a.top_k >= 1, "fused_experts: bad E or top_k");
   FMOE_REQUIRE(a.T >= 0 && a.H >= 1 && a.I >= 1, "fused_experts: bad sizes T=%lld H=%lld I=%lld", (long long)a.T,
                (long long)a.H, (long long)a.I);
@@ -145,6 +148,7 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
   if (a.zero_dropped) FMOE_CUDA_OK(cudaMemsetAsync(z, 0, (size_t)(p.numel * a.H * eb), st));
 
   fmoe_gemm_args g{};
+  g.struct_size = (uint32_t)sizeof(fmoe_gemm_args);
   g.variant = p.variant;
   g.num_experts = a.num_experts;
   g.top_k = a.top_k;

@@ -429,15 +429,20 @@ EncodeTiledFn encode_tiled_fn() {
 
 }  // namespace
 
+// SM count of the current device (cached per device ordinal).
 int device_sm_count() {
-  static int sm_count = 0;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
-  });
-  return sm_count;
+  static std::mutex mu;
+  static int sm_count[kMaxDevices] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (dev < 0 || dev >= kMaxDevices) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (sm_count[dev] == 0) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+  return sm_count[dev];
 }
 
 // 2-D row-major [rows, cols] tensor of `elem_bytes` elements; box = kbytes (128 or 64) x box_rows, swizzle of the same width.
@@ -464,11 +469,10 @@ template <bool GATED, int KB, bool GATHER, bool EXTRA>
 int launch(const GemmParams& g, cudaStream_t st) {
   constexpr int SMEM_BYTES = Ring<KB>::SMEM_BYTES, KBYTES = KB;
   const int sm_count = device_sm_count();
-  static cudaError_t attr_err = cudaSuccess;
-  static std::once_flag once_attr;
-  std::call_once(once_attr, [] {
-    attr_err = cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    SMEM_BYTES);
+  static PerDeviceOnce once_attr;  // the opt-in to > 48 KB of dynamic shared memory is per device
+  const cudaError_t attr_err = per_device_once(once_attr, [] {
+    return cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
   });
   if (attr_err != cudaSuccess)
     return fail(FMOE_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", SMEM_BYTES, cudaGetErrorString(attr_err));

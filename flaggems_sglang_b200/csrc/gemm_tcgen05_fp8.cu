@@ -334,11 +334,10 @@ namespace {
 
 template <bool GATED>
 int launch(const GemmParams& g, cudaStream_t st) {
-  static std::once_flag once_attr;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once_attr, [] {
-    attr_err = cudaFuncSetAttribute(grouped_gemm_tcgen05_fp8_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    SMEM_BYTES);
+  static PerDeviceOnce once_attr;  // the opt-in to > 48 KB of dynamic shared memory is per device
+  const cudaError_t attr_err = per_device_once(once_attr, [] {
+    return cudaFuncSetAttribute(grouped_gemm_tcgen05_fp8_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                SMEM_BYTES);
   });
   if (attr_err != cudaSuccess)
     return fail(FMOE_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", SMEM_BYTES, cudaGetErrorString(attr_err));

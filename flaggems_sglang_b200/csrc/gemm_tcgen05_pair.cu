@@ -311,11 +311,10 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
 
 template <bool GATED>
 int launch(const GemmParams& g, cudaStream_t st) {
-  static cudaError_t attr_err = cudaSuccess;
-  static std::once_flag once_attr;
-  std::call_once(once_attr, [] {
-    attr_err = cudaFuncSetAttribute(grouped_gemm_tcgen05_pair_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    SMEM_BYTES);
+  static PerDeviceOnce once_attr;  // the opt-in to > 48 KB of dynamic shared memory is per device
+  const cudaError_t attr_err = per_device_once(once_attr, [] {
+    return cudaFuncSetAttribute(grouped_gemm_tcgen05_pair_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                SMEM_BYTES);
   });
   if (attr_err != cudaSuccess)
     return fail(FMOE_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", SMEM_BYTES, cudaGetErrorString(attr_err));

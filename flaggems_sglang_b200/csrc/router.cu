@@ -2,6 +2,8 @@
 //   fmoe_topk_softmax : softmax -> top-k -> renormalise
 //   fmoe_topk_grouped : sigmoid + bias, group-limited top-k (DeepSeek-V3 style)
 // Expert e of a token lives in lane e % 32, register e / 32 (coalesced loads).
+// NaN contract: a NaN logit (or a NaN biased score) ranks as -inf, ties go to the lower index, and a softmax row
+// without any logit above -inf is routed as if all its logits were equal; every id written is inside [0, E).
 #include "common.cuh"
 
 namespace fmoe {
@@ -84,10 +86,17 @@ topk_softmax_kernel(const float* __restrict__ logits, int64_t T, int E, int k, i
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     int e = lane + 32 * i;
-    key[i] = (e < E) ? row[e] : kNegInf;
+    const float v = (e < E) ? row[e] : kNegInf;
+    key[i] = (v != v) ? kNegInf : v;  // NaN ranks as -inf
     mx = fmaxf(mx, key[i]);
   }
   mx = warp_max(mx);
+  if (mx == kNegInf) {  // no logit above -inf: equal logits (uniform probabilities, experts 0..k-1)
+    mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+      if (lane + 32 * i < E) key[i] = 0.f;
+  }
   float denom = 0.f;
 #pragma unroll
   for (int i = 0; i < VPT; ++i)
@@ -97,9 +106,15 @@ topk_softmax_kernel(const float* __restrict__ logits, int64_t T, int E, int k, i
   select_topk<VPT>(key, E, k, lane, s_ids[warp]);
   __syncwarp();
   // lane j owns winner j
-  int id = (lane < k) ? s_ids[warp][lane] : 0;
-  float p = 0.f;
-  if (lane < k) p = __fdiv_rn(expf(row[id] - mx), denom);
+  int id = (lane < k) ? min(max(s_ids[warp][lane], 0), E - 1) : 0;
+  // the winner's (sanitised) logit lives in lane id % 32, register id / 32
+  float kv = kNegInf;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const float cand = __shfl_sync(0xffffffffu, key[i], id & 31);
+    if (i == (id >> 5)) kv = cand;
+  }
+  float p = (lane < k) ? __fdiv_rn(expf(kv - mx), denom) : 0.f;
   if (renorm) {
     float s = 0.f;
     for (int j = 0; j < k; ++j) s += __shfl_sync(0xffffffffu, p, j);  // sequential, j ascending
@@ -131,9 +146,11 @@ topk_grouped_kernel(const float* __restrict__ logits, const float* __restrict__ 
     int e = lane + 32 * i;
     if (e < E) {
       // correctly rounded fp32 sigmoid: evaluate in fp64, round once
-      double z = (double)row[e];
+      const float lg = row[e];
+      double z = (lg != lg) ? -INFINITY : (double)lg;  // NaN ranks as -inf (score 0)
       float s = (float)(1.0 / (1.0 + exp(-z)));
       float c = s + (bias ? bias[e] : 0.f);
+      if (c != c) c = kNegInf;
       s_score[e] = s;
       s_choice[e] = c;
       key[i] = c;
@@ -157,6 +174,7 @@ topk_grouped_kernel(const float* __restrict__ logits, const float* __restrict__ 
       }
     }
     gscore = (gsz >= 2) ? (m1 + m2) : m1;
+    if (gscore != gscore) gscore = kNegInf;  // +inf + -inf
   }
   // keep the topk_group best groups (ties -> lower group index)
   uint32_t keep = 0;
@@ -167,7 +185,7 @@ topk_grouped_kernel(const float* __restrict__ logits, const float* __restrict__ 
       b.idx = 0x7fffffff;
     }
     b = warp_argmax(b);
-    keep |= 1u << b.idx;
+    if (b.idx < 32) keep |= 1u << b.idx;
   }
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
@@ -176,7 +194,7 @@ topk_grouped_kernel(const float* __restrict__ logits, const float* __restrict__ 
   }
   select_topk<VPT>(key, E, k, lane, s_ids[warp]);
   __syncwarp();
-  int id = (lane < k) ? s_ids[warp][lane] : 0;
+  int id = (lane < k) ? min(max(s_ids[warp][lane], 0), E - 1) : 0;
   float w = (lane < k) ? s_score[id] : 0.f;
   if (renorm) {
     float s = 0.f;

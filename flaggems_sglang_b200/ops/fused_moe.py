@@ -532,6 +532,32 @@ class StandardCombineInput:
     hidden_states: torch.Tensor
 
 
+def _split_interleaved_cached(layer, b13):
+    """`_split_interleaved` of the layer's w13 / bias, kept on the layer until either tensor is replaced or
+    modified in place (data pointer and version counter), so that the copy is not repeated on every call."""
+    w = layer.w13_weight
+    key = (w.data_ptr(), w._version, tuple(w.shape), b13.data_ptr(), b13._version)
+    cached = getattr(layer, "_fmoe_split_w13", None)
+    if cached is None or cached[0] != key:
+        cached = (key, _split_interleaved(w, b13))
+        try:
+            layer._fmoe_split_w13 = cached
+        except Exception:  # noqa: BLE001  (a layer object that refuses new attributes: split per call)
+            pass
+    return cached[1]
+
+
+def _standard_output_type():
+    """The combine-input container of the serving stack when it is importable (the reference imports it at
+    src/flaggems_sglang/ops/fused_moe.py:337-339), this module's stand-in with the same field otherwise."""
+    try:
+        from sglang.srt.layers.moe.token_dispatcher.standard import StandardCombineInput as _Sgl
+
+        return _Sgl
+    except Exception:  # noqa: BLE001
+        return StandardCombineInput
+
+
 def fused_moe_flagos(obj, layer: torch.nn.Module, dispatch_output):
     """Serving-side hook with the reference's signature (src/flaggems_sglang/ops/fused_moe.py:328-422).
 
@@ -539,22 +565,29 @@ def fused_moe_flagos(obj, layer: torch.nn.Module, dispatch_output):
     transposes and copies both on every call, :342-343), accepts either the standard
     `(topk_weights, topk_ids)` output or a routing triple, honours `no_combine`,
     `apply_router_weight_on_input` and `routed_scaling_factor` of `obj.runner.config`,
-    and returns an object with `.hidden_states`.
+    and returns SGLang's `StandardCombineInput` (or, without SGLang, an object with the same `.hidden_states`).
+
+    `no_combine`: as in the reference (:355-366, 408-413), a standard top-k output is first converted to the
+    routing triple, and the un-combined rows come back in EXPERT-SORTED order viewed as [T, k, H] — for both
+    routing formats.  (`fused_experts(no_combine=True)` on the serving-side layouts returns rows by flat slot.)
     """
     cfg = obj.runner.config
     b13, b2 = getattr(layer, "w13_weight_bias", None), getattr(layer, "w2_weight_bias", None)
     hidden_states = dispatch_output.hidden_states
     topk_output = dispatch_output.topk_output
+    if cfg.no_combine and hasattr(topk_output, "topk_weights"):
+        topk_output = standard_topk_to_routing(topk_output.topk_weights, topk_output.topk_ids, layer.w13_weight.shape[0])
+    Out = _standard_output_type()
     if b13 is not None or b2 is not None:
         # bias variant (src/flaggems_sglang/ops/fused_moe.py:380-398): interleaved gate/linear rows, swiglu
         assert b13 is not None and b2 is not None, "Bias execution requires both w13_bias and w2_bias"
         alpha, limit = getattr(cfg, "gemm1_alpha", None), getattr(cfg, "gemm1_clamp_limit", None)
         if hasattr(topk_output, "topk_weights"):
-            w13, b13s = _split_interleaved(layer.w13_weight, b13)
+            w13, b13s = _split_interleaved_cached(layer, b13)
             out = fused_experts(
                 hidden_states, w13, layer.w2_weight, topk_output.topk_weights, topk_output.topk_ids,
                 activation="swiglu_oai", apply_router_weight_on_input=cfg.apply_router_weight_on_input,
-                no_combine=cfg.no_combine, routed_scaling_factor=None if cfg.no_combine else cfg.routed_scaling_factor,
+                routed_scaling_factor=cfg.routed_scaling_factor,
                 b1=b13s, b2=b2, gemm1_alpha=alpha, gemm1_clamp_limit=limit,
             )
         else:
@@ -569,13 +602,13 @@ def fused_moe_flagos(obj, layer: torch.nn.Module, dispatch_output):
                 out = out.view(hidden_states.shape[0], -1, hidden_states.shape[-1])
             elif cfg.routed_scaling_factor is not None and cfg.routed_scaling_factor != 1.0:
                 out.mul_(cfg.routed_scaling_factor)
-        return StandardCombineInput(hidden_states=out)
+        return Out(hidden_states=out)
     if hasattr(topk_output, "topk_weights"):
         tw, ti = topk_output.topk_weights, topk_output.topk_ids
         out = fused_experts(
             hidden_states, layer.w13_weight, layer.w2_weight, tw, ti, activation=cfg.activation,
-            apply_router_weight_on_input=cfg.apply_router_weight_on_input, no_combine=cfg.no_combine,
-            routed_scaling_factor=None if cfg.no_combine else cfg.routed_scaling_factor,
+            apply_router_weight_on_input=cfg.apply_router_weight_on_input,
+            routed_scaling_factor=cfg.routed_scaling_factor,
         )
     else:
         routing_data, gather_indx, scatter_indx = topk_output
@@ -588,7 +621,7 @@ def fused_moe_flagos(obj, layer: torch.nn.Module, dispatch_output):
             out = out.view(hidden_states.shape[0], -1, hidden_states.shape[-1])
         elif cfg.routed_scaling_factor is not None and cfg.routed_scaling_factor != 1.0:
             out.mul_(cfg.routed_scaling_factor)
-    return StandardCombineInput(hidden_states=out)
+    return Out(hidden_states=out)
 
 
 __all__ = [

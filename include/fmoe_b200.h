@@ -8,7 +8,8 @@
  *
  * Conventions
  *   - every pointer is a DEVICE pointer unless stated otherwise; the caller owns
- *     all memory, the library never allocates or frees (workspaces are passed in);
+ *     all memory, and the compute entry points never allocate or free (workspaces are
+ *     passed in); only fmoe_ep_buffer_create / _destroy allocate, at set-up time;
  *   - every function returns FMOE_OK (0) or an FMOE_ERR_* code; a human-readable
  *     message for the calling thread's last failure is at fmoe_last_error();
  *   - `stream` is a cudaStream_t passed as void*; work is enqueued, not awaited;
@@ -50,6 +51,7 @@ extern "C" {
 #define FMOE_VARIANT_TCGEN05 3 /* TMA + tcgen05/TMEM persistent kernel for large M */
 #define FMOE_VARIANT_TCGEN05_PAIR 4 /* same on CTA pairs (cta_group::2), 256-row blocks, bf16 */
 
+/* ABI version: 2 = argument structs begin with struct_size. */
 int fmoe_version(void);
 /* Message of the last error returned on the calling thread ("" if none). */
 const char* fmoe_last_error(void);
@@ -61,7 +63,9 @@ int fmoe_sm_count(void);
  * Replaces the routing the reference's caller performs before the hook
  * (src/flaggems_sglang/ops/fused_moe.py:355-366 consumes topk_weights/topk_ids;
  * tests/test_fused_moe.py:38-41 builds them with softmax -> topk -> renormalise).
- * Ranking is on the raw logits, ties go to the lower expert index.
+ * Ranking is on the raw logits, ties go to the lower expert index.  A NaN logit ranks as -inf (weight 0); a row
+ * with no logit above -inf is routed as if all its logits were equal (ids 0..k-1, equal weights); a +inf logit
+ * gives NaN weights as softmax does.  Every id written is inside [0, E).
  *   logits [T,E] f32 row-major -> topk_weights [T,k] f32, topk_ids [T,k] i32
  * Limits: 1 <= k <= 32, k <= E <= 1024.
  */
@@ -76,6 +80,7 @@ int fmoe_topk_softmax(const float* logits, int64_t T, int E, int k, int renormal
  *   group score = sum of the 2 largest c of the group; keep topk_group groups;
  *   ids = top-k of c inside kept groups; weights = s[ids], renormalised by
  *   (sum + 1e-20) when `renormalize`, then multiplied by `scale`.
+ *   A NaN logit counts as -inf (s = 0), a NaN c (or NaN group score) as -inf; every id written is inside [0, E).
  * Limits: E <= 1024, E % n_group == 0, n_group <= 32, k <= 32.
  */
 int fmoe_topk_grouped(const float* logits, const float* bias, int64_t T, int E, int k,
@@ -143,6 +148,9 @@ int fmoe_gather_rows(const void* x, int elem_bytes, int64_t rows_out, int64_t K,
  * src/flaggems_sglang/ops/fused_moe.py:205-231.
  */
 typedef struct fmoe_gemm_args {
+  uint32_t struct_size;/* sizeof(fmoe_gemm_args) as the CALLER compiled it; a size the library does not know is
+                          refused with FMOE_ERR_INVALID_ARG before any other field is read   */
+  int32_t reserved0;   /* 0                                                               */
   int32_t dtype;       /* FMOE_F32 | FMOE_BF16 | FMOE_E4M3: type of a and w            */
   int32_t out_dtype;   /* FMOE_F32 | FMOE_BF16 | FMOE_E4M3 (gemm1+TCGEN05 fp8 only)     */
   int32_t variant;     /* FMOE_VARIANT_*                                                 */
@@ -207,6 +215,8 @@ int fmoe_moe_sum_add(const void* z, int dtype, int64_t T, int k, int64_t H, floa
  * nothing is allocated and the host is never synchronised.
  */
 typedef struct fmoe_fused_args {
+  uint32_t struct_size; /* sizeof(fmoe_fused_args) as the caller compiled it (checked like fmoe_gemm_args.struct_size) */
+  int32_t reserved0;    /* 0                                                                              */
   int32_t dtype;        /* FMOE_F32 | FMOE_BF16: type of hidden/w1/w2/out; FMOE_E4M3: e4m3 weights with
                            128x128 scales, bf16 hidden/out, activations quantised per token per 128 channels */
   int32_t variant;      /* FMOE_VARIANT_* (AUTO: chosen from the shape)                                   */

@@ -29,6 +29,10 @@ def softmax_topk(logits: torch.Tensor, k: int, renormalize: bool = True):
     """
     logits = logits.detach().to(torch.float32).cpu()
     T, E = logits.shape
+    # NaN contract (builder-defined): NaN ranks as -inf; a row with nothing above -inf counts as all-equal logits
+    logits = torch.where(torch.isnan(logits), torch.full_like(logits, float("-inf")), logits)
+    dead = (logits == float("-inf")).all(dim=1, keepdim=True)
+    logits = torch.where(dead, torch.zeros_like(logits), logits)
     order = torch.argsort(-logits, dim=1, stable=True)[:, :k]
     probs = torch.softmax(logits, dim=-1)
     w = torch.take_along_dim(probs, order, dim=1)
@@ -71,7 +75,9 @@ def grouped_topk(
       w = s[ids] (un-biased); renormalise: w /= (sum_j w_j + 1e-20) summed j=0..k-1
       w *= routed_scaling_factor when given.
     """
-    s = sigmoid_f32(logits)
+    logits = logits.detach().cpu().to(torch.float32)
+    # NaN contract (builder-defined): a NaN logit counts as -inf, a NaN biased score or group score as -inf
+    s = sigmoid_f32(torch.where(torch.isnan(logits), torch.full_like(logits, float("-inf")), logits))
     T, E = s.shape
     bias = (
         torch.zeros(E, dtype=torch.float32)
@@ -79,6 +85,7 @@ def grouped_topk(
         else correction_bias.detach().cpu().to(torch.float32)
     )
     c = s + bias[None, :]
+    c = torch.where(torch.isnan(c), torch.full_like(c, float("-inf")), c)
     gsz = E // num_expert_group
     cg = c.view(T, num_expert_group, gsz)
     if gsz >= 2:
@@ -86,6 +93,7 @@ def grouped_topk(
         gscore = top2[..., 0] + top2[..., 1]
     else:
         gscore = cg[..., 0]
+    gscore = torch.where(torch.isnan(gscore), torch.full_like(gscore, float("-inf")), gscore)
     gorder = torch.argsort(-gscore, dim=1, stable=True)[:, :topk_group]
     gmask = torch.zeros(T, num_expert_group, dtype=torch.bool)
     gmask.scatter_(1, gorder, True)

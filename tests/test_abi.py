@@ -41,15 +41,59 @@ def test_struct_layout_matches_header():
 
     from flaggems_sglang_b200 import _C
 
-    # 8 int32 + 6 int64 + 10 pointers
-    assert ctypes.sizeof(_C.GemmArgs) == 8 * 4 + 6 * 8 + 10 * 8 + (8 + 4 + 4) + 8
-    assert _C.GemmArgs.numel.offset == 32 and _C.GemmArgs.a.offset == 80
-    # 8 int32 + 3 int64 + 2 float + 9 pointers + 1 int64
-    assert ctypes.sizeof(_C.FusedArgs) == 144 + (8 + 8 + 4 + 4) + 8 and _C.FusedArgs.hidden.offset == 64
+    # struct_size + reserved, 8 int32, 6 int64, 10 pointers, bias pointer + 2 floats, out_rows
+    assert ctypes.sizeof(_C.GemmArgs) == 8 + 8 * 4 + 6 * 8 + 10 * 8 + (8 + 4 + 4) + 8
+    assert _C.GemmArgs.struct_size.offset == 0 and _C.GemmArgs.numel.offset == 40 and _C.GemmArgs.a.offset == 88
+    # struct_size + reserved, 8 int32, 3 int64, 2 float, 9 pointers, 1 int64, 2 pointers + 2 floats, out_rows
+    assert ctypes.sizeof(_C.FusedArgs) == 8 + 144 + (8 + 8 + 4 + 4) + 8 and _C.FusedArgs.hidden.offset == 72
+    assert _C.GemmArgs().struct_size == ctypes.sizeof(_C.GemmArgs)
+    assert _C.FusedArgs(T=3).struct_size == ctypes.sizeof(_C.FusedArgs)
+
+
+def test_unknown_struct_size_is_refused(lib):
+    """A binding compiled against another version of the header is caught before any field is trusted."""
+    import ctypes
+
+    from flaggems_sglang_b200 import _C
+
+    g = _C.GemmArgs(dtype=_C.BF16, num_experts=4, top_k=2, block_size=16, numel=8, n=128, k=128)
+    g.struct_size -= 24  # the size of a struct that ends before bias / act_alpha / act_limit / out_rows
+    assert lib.fmoe_gemm2(ctypes.byref(g), None) == _C.ERR_INVALID_ARG and b"struct_size" in lib.fmoe_last_error()
+    assert lib.fmoe_gemm1_silu(ctypes.byref(g), None) == _C.ERR_INVALID_ARG
+    f = _C.FusedArgs(dtype=_C.BF16, num_experts=4, top_k=2, T=4, H=128, I=128)
+    f.struct_size = 0
+    assert lib.fmoe_fused_experts_workspace_bytes(ctypes.byref(f)) < 0 and b"struct_size" in lib.fmoe_last_error()
+    assert lib.fmoe_fused_experts(ctypes.byref(f), None) == _C.ERR_INVALID_ARG
+    assert lib.fmoe_fused_experts_static(ctypes.byref(f), None) == _C.ERR_INVALID_ARG
+
+
+def _integration_snippet():
+    """The ctypes stub INTEGRATION.md shows to a maintainer of the reference, as source text."""
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    blocks = re.findall(r"```python\n(.*?)```", text, flags=re.S)
+    stub = [b for b in blocks if "class GemmArgs" in b]
+    assert len(stub) == 1, "INTEGRATION.md must hold exactly one ctypes stub with a GemmArgs mirror"
+    return stub[0]
+
+
+def test_integration_stub_struct_matches_binding(lib):
+    """The struct mirror printed in INTEGRATION.md has the layout of the real one (a stale copy there would make
+    the library read past the caller's struct)."""
+    import ctypes
+
+    from flaggems_sglang_b200 import _C
+
+    ns = {"LIBFMOE_PATH": _C.LIB_PATH}
+    exec(compile(_integration_snippet(), "INTEGRATION.md", "exec"), ns)
+    G = ns["GemmArgs"]
+    assert ctypes.sizeof(G) == ctypes.sizeof(_C.GemmArgs)
+    assert [(n, getattr(G, n).offset) for n, _ in G._fields_] == \
+        [(n, getattr(_C.GemmArgs, n).offset) for n, _ in _C.GemmArgs._fields_]
+    assert G(n=1).struct_size == ctypes.sizeof(_C.GemmArgs)
 
 
 def test_version_and_error_buffer(lib):
-    assert lib.fmoe_version() == 1
+    assert lib.fmoe_version() == 2
     # an invalid call reports through the status code and the message buffer, without touching a device
     rc = lib.fmoe_topk_softmax(None, 4, 0, 1, 1, None, None, None)
     assert rc == 1

@@ -291,6 +291,16 @@ def test_hook(fg):
     disp2 = NS(hidden_states=x.cuda(), topk_output=triple)
     out2 = fg.fused_moe_flagos(NS(runner=NS(config=cfg)), layer, disp2).hidden_states
     assert_close_moe(out2, OE.fused_experts(x, w1, w2, tw, ti, routed_scaling_factor=2.5), "bf16", "hook triple")
+    # no_combine: both routing formats return the rows in expert-sorted order viewed [T,k,H], as the reference
+    # hook does (src/flaggems_sglang/ops/fused_moe.py:355-366, 408-413), without the scaling factor
+    cfg_nc = NS(**{**vars(cfg), "no_combine": True})
+    routing = OR.standard_topk_to_routing(tw, ti, E)
+    w1r, w2r = w1.transpose(1, 2).contiguous(), w2.transpose(1, 2).contiguous()
+    zref = OE.reference_fused_experts(x, w1r, w2r, routing, no_combine=True).view(T, k, H)
+    z_std = fg.fused_moe_flagos(NS(runner=NS(config=cfg_nc)), layer, disp).hidden_states
+    z_tri = fg.fused_moe_flagos(NS(runner=NS(config=cfg_nc)), layer, disp2).hidden_states
+    assert z_std.shape == (T, k, H) and torch.equal(z_std, z_tri)
+    assert_close_moe(z_std, zref, "bf16", "hook no_combine")
 
 
 # ------------------------------------------------------------------ fp8 w8a8 block quant
@@ -354,50 +364,88 @@ def test_fp8_quantise_once_then_copy_equals_quantising_sorted_rows(fg):
 
 
 # ------------------------------------------------------------------ full benchmark sizes
-def _sampled_dense_check(fg, cfg_name, T, sample, kind, variant=None):
-    """Run the layer at its full size on the GPU and check `sample` tokens against the dense
-    per-token oracle evaluated on the CPU with the same weights."""
+def _sampled_oracle_check(fg, cfg_name, T, sample, kind, variant=None, skew=False):
+    """Run the layer at its full size on the GPU and check `sample` evenly spaced tokens against the CPU oracle
+    evaluated on the same weights (the oracle walks the experts those tokens route to, one expert at a time)."""
     from flaggems_sglang_b200 import workloads as W
 
     cfg = W.CONFIGS[cfg_name]
     wts = W.make_weights(cfg, "cuda", seed=0)
-    tok = W.make_tokens(cfg, T, "cuda", seed=0)
+    tok = W.make_tokens(cfg, T, "cuda", seed=0, skew=skew)
     tw, ti = W.route(cfg, tok)
     kw = {}
     if cfg.dtype == "fp8":
         kw = dict(use_fp8_w8a8=True, w1_scale=wts["w1_scale"], w2_scale=wts["w2_scale"], block_shape=[128, 128])
     out = fg.fused_experts(tok["hidden"], wts["w1"], wts["w2"], tw, ti, variant=variant, **kw)
-    idx = torch.linspace(0, T - 1, min(sample, T)).long().unique()
-    for t in idx.tolist():
-        ids_t = ti[t].cpu()
-        experts = ids_t.tolist()
-        x_t = tok["hidden"][t : t + 1].cpu()
-        w1s = torch.stack([wts["w1"][e].cpu() for e in experts])
-        w2s = torch.stack([wts["w2"][e].cpu() for e in experts])
-        local_ids = torch.arange(len(experts), dtype=torch.int32)[None, :]
-        if cfg.dtype == "fp8":
-            s1 = torch.stack([wts["w1_scale"][e].cpu() for e in experts])
-            s2 = torch.stack([wts["w2_scale"][e].cpu() for e in experts])
-            ref = OE.fused_experts_fp8(x_t, w1s, s1, w2s, s2, tw[t : t + 1].cpu(), local_ids)
-        else:
-            ref = OE.fused_experts(x_t, w1s, w2s, tw[t : t + 1].cpu(), local_ids)
-        assert_close_moe(out[t : t + 1], ref, kind, f"{cfg_name} T={T} token {t}")
+    idx = torch.linspace(0, T - 1, min(sample, T)).long().unique().cuda()
+    x_s, tw_s, ti_s = tok["hidden"][idx].cpu(), tw[idx].cpu(), ti[idx].cpu()
+    if cfg.dtype == "fp8":
+        ref = OE.fused_experts_fp8(x_s, wts["w1"], wts["w1_scale"], wts["w2"], wts["w2_scale"], tw_s, ti_s)
+    else:
+        ref = OE.fused_experts(x_s, wts["w1"], wts["w2"], tw_s, ti_s)
+    l2, ma = assert_close_moe(out[idx], ref, kind, f"{cfg_name} T={T}{' zipf' if skew else ''} {idx.numel()} tokens")
+    print(f"{cfg_name} T={T} skew={skew}: {idx.numel()} tokens vs oracle rel-L2 {l2:.2e} max-abs/max {ma:.2e}")
     return out
 
 
-@pytest.mark.parametrize("T", [1, 64, 4096])
+@pytest.mark.parametrize("T", [1, 64, 1024, 4096])
 def test_mixtral_full_size_sampled(fg, T):
-    out = _sampled_dense_check(fg, "mixtral", T, 3, "bf16")
+    out = _sampled_oracle_check(fg, "mixtral", T, 64, "bf16")
     if T == 64:  # the two tensor-core families agree at full size
-        other = _sampled_dense_check(fg, "mixtral", T, 1, "bf16", variant="tcgen05")
+        other = _sampled_oracle_check(fg, "mixtral", T, 8, "bf16", variant="tcgen05")
         assert rel_l2(out, other) < 5e-3
 
 
-@pytest.mark.parametrize("T", [1, 512, 8192])
-def test_qwen3_full_size_sampled(fg, T):
-    _sampled_dense_check(fg, "qwen3", T, 3, "bf16")
+@pytest.mark.parametrize("T,skew", [(1, False), (512, False), (8192, False), (512, True), (8192, True)])
+def test_qwen3_full_size_sampled(fg, T, skew):
+    """Uniform and Zipf(1.2)-skewed routing (hot and empty experts) at the configuration's sizes."""
+    _sampled_oracle_check(fg, "qwen3", T, 64, "bf16", skew=skew)
 
 
-@pytest.mark.parametrize("T", [1, 64, 4096])
+@pytest.mark.parametrize("T", [1, 64, 1024, 4096, 16384])
 def test_dsv3_fp8_full_size_sampled(fg, T):
-    _sampled_dense_check(fg, "dsv3", T, 2, "fp8")
+    _sampled_oracle_check(fg, "dsv3", T, 24, "fp8")
+
+
+def test_two_devices_in_one_process(fg):
+    """Kernels that opt in to large dynamic shared memory are configured per device: a second GPU driven from the
+    same process runs the tcgen05 kernels too."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs in one process")
+    from flaggems_sglang_b200 import _C
+
+    T, H, I, E, k = 300, 256, 256, 8, 2
+    x, w1, w2, logits = _layer(T, H, I, E, k, torch.bfloat16, 31)
+    tw, ti = OR.softmax_topk(logits, k, True)
+    ref = OE.fused_experts(x, w1, w2, tw, ti)
+    q1, s1 = OQ.quant_weight_block128(w1.float())
+    q2, s2 = OQ.quant_weight_block128(w2.float())
+    ref8 = OE.fused_experts_fp8(x, q1, s1, q2, s2, tw, ti)
+    for d in (0, 1):
+        dev = torch.device("cuda", d)
+        with torch.cuda.device(dev):
+            out = fg.fused_experts(x.to(dev), w1.to(dev), w2.to(dev), tw.to(dev), ti.to(dev), variant="tcgen05")
+            out8 = fg.fused_experts(x.to(dev), q1.to(dev), q2.to(dev), tw.to(dev), ti.to(dev), variant="tcgen05",
+                                    use_fp8_w8a8=True, w1_scale=s1.to(dev), w2_scale=s2.to(dev), block_shape=[128, 128])
+            _C.check_device_status(dev)
+        assert_close_moe(out, ref, "bf16", f"tcgen05 on cuda:{d}")
+        assert_close_moe(out8, ref8, "fp8", f"tcgen05 fp8 on cuda:{d}")
+
+
+def test_integration_stub_runs(fg):
+    """The ctypes stub of INTEGRATION.md, executed as printed, computes the bf16 layer through the raw C ABI."""
+    import re
+
+    from flaggems_sglang_b200 import _C
+
+    text = open(os.path.join(os.path.dirname(os.path.dirname(GOLDEN)), "INTEGRATION.md")).read()
+    stub = [b for b in re.findall(r"```python\n(.*?)```", text, flags=re.S) if "class GemmArgs" in b]
+    assert len(stub) == 1
+    ns = {"LIBFMOE_PATH": _C.LIB_PATH}
+    exec(compile(stub[0], "INTEGRATION.md", "exec"), ns)
+    T, H, I, E, k = 50, 256, 384, 8, 2
+    x, w1, w2, logits = _layer(T, H, I, E, k, torch.bfloat16, 77)
+    tw, ti = OR.softmax_topk(logits, k, True)
+    out = ns["fused_experts_bf16"](x.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ti.cuda().to(torch.int32))
+    _C.check_device_status()
+    assert_close_moe(out, OE.fused_experts(x, w1, w2, tw, ti), "bf16", "INTEGRATION.md stub")

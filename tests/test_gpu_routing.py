@@ -166,3 +166,39 @@ def test_align_agrees_with_reference_tile_maps(fg, path):
         np.testing.assert_array_equal(e.cpu().numpy()[:tiles], g[f"block_pid_map_{bm}"][:tiles] & 0xFFFF)
         used = s.cpu().numpy()[: tiles * bm]
         np.testing.assert_array_equal(used[used < ids.numel()] // k, g["topk_indx"] // k)
+
+
+# ---------------------------------------------------------------- NaN / -inf rows stay in bounds
+def _poisoned_logits(T, E, seed):
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(T, E, generator=g)
+    logits[0] = float("nan")                 # a whole NaN row (a diverged model)
+    logits[1] = float("-inf")                # nothing selectable
+    logits[2, ::3] = float("nan")            # scattered NaNs
+    logits[3, : E - 2] = float("-inf")       # fewer finite logits than k
+    return logits
+
+
+@pytest.mark.parametrize("E,k", [(8, 2), (128, 8), (256, 8)])
+def test_softmax_topk_nan_rows_in_bounds(fg, E, k):
+    logits = _poisoned_logits(6, E, 3)
+    w, ids = fg.fused_topk(None, logits.cuda(), k, True)
+    ow, oids = OR.softmax_topk(logits, k, True)
+    assert int(ids.min()) >= 0 and int(ids.max()) < E
+    assert torch.equal(ids.cpu(), oids)
+    torch.testing.assert_close(w.cpu(), ow, rtol=1e-5, atol=1e-9, equal_nan=True)
+    assert torch.isfinite(w[:3]).all()       # NaN and all -inf rows give finite weights
+
+
+@pytest.mark.parametrize("with_bias", [True, False])
+def test_grouped_topk_nan_rows_in_bounds(fg, with_bias):
+    E, k, ng, tg = 256, 8, 8, 4
+    logits = _poisoned_logits(6, E, 4)
+    bias = torch.randn(E) * 0.1 if with_bias else None
+    if with_bias:
+        bias[5] = float("nan")
+    w, ids = fg.grouped_topk(None, logits.cuda(), k, True, ng, tg, None if bias is None else bias.cuda(), 2.5)
+    ow, oids = OR.grouped_topk(logits, bias, k, ng, tg, True, 2.5)
+    assert int(ids.min()) >= 0 and int(ids.max()) < E
+    assert torch.equal(ids.cpu(), oids)
+    torch.testing.assert_close(w.cpu(), ow, rtol=1e-5, atol=1e-9, equal_nan=True)

@@ -89,3 +89,24 @@ def test_reference_routing_tables_are_inverse_permutations(T, k, E, seed):
         pm = r["block_pid_map"][bm]
         tiles = int(r["token_offs_pad"][bm][-1])
         assert (pm[:tiles] >= 0).all() and (pm[tiles:] == -1).all()
+
+
+def test_routers_keep_ids_in_range_on_nan_and_inf_rows():
+    """NaN contract of both routers: NaN ranks as -inf, ids always inside [0, E), NaN / all -inf rows of the
+    softmax router get finite weights."""
+    E, k = 64, 6
+    g = torch.Generator().manual_seed(9)
+    logits = torch.randn(5, E, generator=g)
+    logits[0] = float("nan")
+    logits[1] = float("-inf")
+    logits[2, 1::2] = float("nan")
+    w, ids = OR.softmax_topk(logits, k, True)
+    assert ids.min() >= 0 and ids.max() < E and torch.isfinite(w).all()
+    assert ids[0].tolist() == list(range(k)) and ids[1].tolist() == list(range(k))
+    assert not set(ids[2].tolist()) & set(range(1, E, 2))   # NaN entries lose to every finite logit
+    torch.testing.assert_close(w[0], torch.full((k,), 1.0 / k))
+    bias = torch.randn(E, generator=g) * 0.1
+    bias[3] = float("nan")
+    gw, gids = OR.grouped_topk(logits, bias, k, 8, 4, True, 2.5)
+    assert gids.min() >= 0 and gids.max() < E
+    assert 3 not in gids[3:].reshape(-1).tolist()           # the NaN-biased expert is never chosen over finite ones

@@ -24,6 +24,7 @@ unchanged on CPU ranks (gloo) in the tests, where the backend is the CPU oracle.
 """
 from __future__ import annotations
 
+import contextlib
 import os
 from dataclasses import dataclass
 from typing import Optional
@@ -141,7 +142,8 @@ class PeerExchange:
     """
 
     def __init__(self, group, max_tokens: int, top_k: int, hidden_size: int, dtype=torch.bfloat16,
-                 capacity: Optional[int] = None, device=None):
+                 capacity: Optional[int] = None, device=None, _lib=None):
+        """`_lib`: stand-in for the C library (tests inject allocation / mapping failures on chosen ranks)."""
         import ctypes
 
         from . import _C
@@ -151,7 +153,7 @@ class PeerExchange:
         self.rank = dist.get_rank(group)
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self._layout(max_tokens, top_k, hidden_size, dtype, capacity)
-        lib = _C.lib()
+        lib = self._lib = _lib if _lib is not None else _C.lib()
         base = ctypes.c_void_p()
         handle = (ctypes.c_ubyte * 64)()
         self._own_base, self._opened = None, []
@@ -165,7 +167,8 @@ class PeerExchange:
                 raise RuntimeError(f"PeerExchange: {what} failed on " +
                                    (f"this rank: {problem}" if problem else "another rank"))
 
-        with torch.cuda.device(self.device):
+        on_device = torch.cuda.device(self.device) if self.device.type == "cuda" else contextlib.nullcontext()
+        with on_device:
             problem = None
             try:
                 _C.check(lib.fmoe_ep_buffer_create(self.nbytes, ctypes.byref(base), handle))
@@ -253,7 +256,7 @@ class PeerExchange:
         for xc, st in zip(out, stores):
             xc._bind(bases, st)
             xc.ids.fill_(-1)
-            xc._opened, xc._own_base, xc._flag = [], None, None
+            xc._opened, xc._own_base, xc._flag, xc._lib = [], None, None, None
         return out
 
     def barrier(self):
@@ -262,9 +265,7 @@ class PeerExchange:
         dist.all_reduce(self._flag, group=self.group)
 
     def _release(self):
-        from . import _C
-
-        lib = _C.lib()
+        lib = self._lib
         for p in self._opened:
             lib.fmoe_ep_buffer_close(p)
         self._opened = []
@@ -278,7 +279,7 @@ class PeerExchange:
 
         if not self._own_base:  # emulated instance, or closed already
             return
-        lib = _C.lib()
+        lib = self._lib
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
         for p in self._opened:
@@ -425,13 +426,19 @@ def ep_fused_experts(
     with _phase("plan", timed):
         ids = topk_ids.to(torch.int32).reshape(-1)
         dest = torch.div(ids, e_local, rounding_mode="floor").to(torch.int32)
+        dest = torch.where((ids >= 0) & (ids < num_global_experts), dest, torch.full_like(dest, world))  # world = nowhere
         perm, counts = backend.sort_by_rank(dest, world)
-        # count exchange: one [N,N] matrix, one host read per layer call
-        matrix = torch.empty(world * world, dtype=counts.dtype, device=counts.device)
-        dist.all_gather_into_tensor(matrix, counts.contiguous(), group=group)
-        plan = plan_from_count_matrix(matrix.view(world, world).cpu(), rank)
-    if sum(plan.send_counts) != T * k:
-        raise RuntimeError("dispatch counts do not add up to T*k (expert id out of range?)")
+        # count exchange: one [N, N+1] matrix (last column = the slots the rank had to place), one host read per
+        # layer call.  Every rank checks every row, so a rank whose counts do not add up (an expert id out of
+        # range) makes ALL ranks raise here instead of leaving the others waiting in the all-to-all.
+        mine = torch.cat((counts.to(torch.int64)[:world], counts.new_tensor([T * k], dtype=torch.int64)))
+        matrix = torch.empty(world * (world + 1), dtype=torch.int64, device=counts.device)
+        dist.all_gather_into_tensor(matrix, mine.contiguous(), group=group)
+        matrix = matrix.view(world, world + 1).cpu()
+        bad = [i for i in range(world) if int(matrix[i, :world].sum()) != int(matrix[i, world])]
+        if bad:
+            raise RuntimeError(f"dispatch counts of rank(s) {bad} do not add up to their T*k (expert id out of range?)")
+        plan = plan_from_count_matrix(matrix[:, :world], rank)
 
     with _phase("pack", timed):
         lperm = perm.long()

@@ -6,9 +6,12 @@
 One step = one `fused_moe` call on one batch of T synthetic tokens of the named layer.  Prints ONE JSON
 line.  `value` is tokens/s with the inputs resident in HBM, device-timed with CUDA events; `e2e` is the
 same call with host buffers (pinned) copied in and the result copied out inside the timed region.
-With N > 1 (torchrun) the experts are sharded E/N per GPU and tokens are exchanged with NCCL all-to-all
-(expert parallel, weak scaling: T tokens per rank).  `--impl reference` times the CPU restatement of the
-reference path (oracle/) on the host cores on a bounded sample of the same workload.
+The headline is the Mixtral-8x7B layer at T=4096; the same line carries the per-T sweep of that layer and,
+under "qwen3", "refbench" (the reference's own benchmark shapes) and "dsv3", the sweeps of the other
+configurations, a parity figure against the CPU oracle ("parity") and a same-box timing of the reference's
+Triton path ("vs_triton").  With N > 1 (torchrun) the experts are sharded E/N per GPU and tokens are
+exchanged over NVLink (expert parallel, weak scaling: T tokens per rank).  `--impl reference` times the CPU
+restatement of the reference path (oracle/) on the host cores on a bounded sample of the same workload.
 """
 from __future__ import annotations
 
@@ -103,8 +106,18 @@ def cpu_sample_tokens(cfg, T):
     return min(T, 64 if cfg.dtype != "fp8" else 8)
 
 
-def run_cpu_oracle(cfg, T, steps, warmup, seed=0):
-    """-> (tokens/s, sample description, cores).  Weights are restricted to the experts the sample routes to."""
+def workload_name(cfg, T):
+    router = "softmax top-k renormalised" if cfg.router == "softmax" else "grouped top-k"
+    return f"{cfg.name} MoE layer H={cfg.H} I={cfg.I} E={cfg.E} top_k={cfg.top_k}, T={T}, {router}"
+
+
+def run_cpu_oracle(cfg, T, steps, warmup, seed=0, gpu=None):
+    """Times the CPU oracle on the first tokens of the batch -> (tokens/s, ms, sample text, cores, output, Ts).
+
+    Weights are restricted to the experts the sample routes to.  With `gpu` = (weights, tokens) of the product
+    arm the sample is a copy of those tensors, so that the oracle's output can be compared with the GPU's."""
+    import dataclasses
+
     from flaggems_sglang_b200 import workloads as W
     from oracle import experts as OE
     from oracle import routing as OR
@@ -112,7 +125,10 @@ def run_cpu_oracle(cfg, T, steps, warmup, seed=0):
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     Ts = cpu_sample_tokens(cfg, T)
-    tok = W.make_tokens(cfg, Ts, "cpu", seed=seed)
+    if gpu is None:
+        tok = W.make_tokens(cfg, Ts, "cpu", seed=seed)
+    else:
+        tok = {k: v[:Ts].cpu() if v.dim() == 2 else v.cpu() for k, v in gpu[1].items()}
     if cfg.router == "grouped":
         tw, ti = OR.grouped_topk(tok["logits"], tok["correction_bias"], cfg.top_k, cfg.n_group, cfg.topk_group, True, None)
     else:
@@ -120,10 +136,12 @@ def run_cpu_oracle(cfg, T, steps, warmup, seed=0):
     used = sorted(set(ti.reshape(-1).tolist()))
     remap = {e: i for i, e in enumerate(used)}
     ti_local = torch.tensor([[remap[int(e)] for e in row] for row in ti], dtype=torch.int32)
-    import dataclasses
-
-    parts = [W.make_weights(dataclasses.replace(cfg), "cpu", seed=seed, num_experts=1, expert_offset=e) for e in used]
-    w = {key: torch.cat([p[key] for p in parts]) for key in parts[0]}
+    if gpu is None:
+        parts = [W.make_weights(dataclasses.replace(cfg), "cpu", seed=seed, num_experts=1, expert_offset=e) for e in used]
+        w = {key: torch.cat([p[key] for p in parts]) for key in parts[0]}
+    else:
+        sel = torch.tensor(used, device=gpu[0]["w1"].device)
+        w = {key: val[sel].cpu() for key, val in gpu[0].items()}
 
     def step():
         if cfg.dtype == "fp8":
@@ -131,30 +149,30 @@ def run_cpu_oracle(cfg, T, steps, warmup, seed=0):
                                         routed_scaling_factor=cfg.routed_scaling_factor)
         return OE.fused_experts(tok["hidden"], w["w1"], w["w2"], tw, ti_local)
 
+    out = None
     for _ in range(warmup):
-        step()
+        out = step()
     t0 = time.perf_counter()
     for _ in range(steps):
-        step()
+        out = step()
     dt = (time.perf_counter() - t0) / max(1, steps)
     sample = (f"first {Ts} tokens of the T={T} batch, {len(used)} experts touched, torch fp32 matmul on up-cast weights, "
               f"{steps} steps")
-    return Ts / dt, dt * 1e3, sample, cores
+    return Ts / dt, dt * 1e3, sample, cores, out, Ts
 
 
 def reference_arm(args, cfg):
+    """`--impl reference`: the CPU oracle port on all host cores, K steps after W warm-up steps, each step a
+    bounded sample (the first tokens) of the product arm's batch."""
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 5))
-    warmup = max(0, min(args.warmup, 1))
-    val, ms, sample, cores = run_cpu_oracle(cfg, args.tokens, steps, warmup)
+    val, ms, sample, cores, _, _ = run_cpu_oracle(cfg, args.tokens, args.steps, args.warmup)
     line = {
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": cfg.dtype, "data": "synthetic",
-        "config": {"workload": f"{cfg.name} MoE layer H={cfg.H} I={cfg.I} E={cfg.E} top_k={cfg.top_k}, T={args.tokens}",
-                   "tokens_per_step": args.tokens},
+        "config": {"workload": workload_name(cfg, args.tokens), "tokens_per_step": args.tokens},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -242,7 +260,9 @@ def time_steps(step, steps, warmup, flush=False):
 
 
 def stage_times(step, steps):
-    """Average device time per stage (ms) with events around each GEMM launch, over `steps` calls."""
+    """Average device time per stage (ms) with events around each launch, in a pass of its own (the kernels are
+    launched one by one from Python): used for the CUDA-graph / L2-flushed points, whose timed loop cannot
+    carry events."""
     import importlib
 
     FM = importlib.import_module("flaggems_sglang_b200.ops.fused_moe")
@@ -258,11 +278,57 @@ def stage_times(step, steps):
     return {k: sum(v) / len(v) for k, v in acc.items()}
 
 
-def measure_point(cfg, wts, T, steps, warmup, peaks, seed=0):
+def time_steps_staged(step, steps, warmup, names):
+    """Device time of `steps` production calls AND the average duration of every stage inside those same calls:
+    the library records caller-provided events at its stage boundaries (fmoe_debug_stage_events), so the
+    per-kernel times and the step time come from one timed region."""
+    import ctypes
+
+    from flaggems_sglang_b200 import _C
+
+    lib = _C.lib()
+    n = 7
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(n)] for _ in range(steps)]
+    for row in evs:
+        for e in row:
+            e.record()  # creates the underlying handle
+    torch.cuda.synchronize()
+    arrs = [(ctypes.c_void_p * n)(*[e.cuda_event for e in row]) for row in evs]
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        _C.check(lib.fmoe_debug_stage_events(arrs[i], n))
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    st = {}
+    for j, name in enumerate(names):
+        if name is None:
+            continue
+        st[name] = sum(row[j].elapsed_time(row[j + 1]) for row in evs) / steps
+    return ms, st
+
+
+def stage_names(cfg, T):
+    from flaggems_sglang_b200.ops.fused_moe import _pick_variant
+
+    dt = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn}[cfg.dtype]
+    name, _ = _pick_variant(dt, T * cfg.top_k, cfg.E, cfg.I, cfg.H, None)
+    fp8 = cfg.dtype == "fp8"
+    g = ("gemm1_fp8_" if fp8 else "gemm1_") + name, ("gemm2_fp8_" if fp8 else "gemm2_") + name
+    prep = "quant_input" if fp8 else ("gather_rows" if name.startswith("tcgen05") else None)
+    return ["align", prep, g[0], "quant_act" if fp8 else None, g[1], "moe_sum"]
+
+
+def measure_point(cfg, wts, T, steps, warmup, peaks, seed=0, skew=False):
     """One (config, T) point -> dict with ms, tokens/s, roofline of the whole call and of the dominant kernel."""
     from flaggems_sglang_b200 import workloads as W
 
-    tok = W.make_tokens(cfg, T, "cuda", seed=seed)
+    tok = W.make_tokens(cfg, T, "cuda", seed=seed, skew=skew)
     step = make_step(cfg, wts, tok)
     use_graph = T <= GRAPH_MAX_TOKENS
     _, ids = W.route(cfg, tok)
@@ -270,8 +336,13 @@ def measure_point(cfg, wts, T, steps, warmup, peaks, seed=0):
     nbytes, flops = W.algorithmic_bytes_flops(cfg, T, active)
     # inputs smaller than twice the L2 could be served from L2 on the next iteration: flush before every step
     flush = nbytes < 2 * torch.cuda.get_device_properties(0).L2_cache_size
-    ms = time_steps(graphed(step) if use_graph else step, steps, warmup, flush=flush)
-    st = stage_times(step, max(3, steps // 2))
+    if use_graph or flush:
+        ms = time_steps(graphed(step) if use_graph else step, steps, warmup, flush=flush)
+        st = stage_times(step, max(3, steps // 2))
+        st_src = "separate pass, one launch per stage from the host"
+    else:
+        ms, st = time_steps_staged(step, steps, warmup, stage_names(cfg, T))
+        st_src = "events inside the timed loop"
     p_tensor = peaks["bf16_tflops"] * (2.0 if cfg.dtype == "fp8" else 1.0)
     t_hbm = nbytes / (peaks["hbm_gbs"] * 1e9)
     t_tc = flops / (p_tensor * 1e12)
@@ -280,7 +351,14 @@ def measure_point(cfg, wts, T, steps, warmup, peaks, seed=0):
     return {"T": T, "ms": ms, "cuda_graph": use_graph, "l2_flush": flush, "tokens_per_s": T / (ms * 1e-3), "active_experts": active, "bound": bound,
             "roofline_ms": t_roof * 1e3, "roofline_frac": t_roof / (ms * 1e-3),
             "achieved_gbs": nbytes / (ms * 1e-3) / 1e9, "achieved_tflops": flops / (ms * 1e-3) / 1e12,
-            "stages_ms": st, "alg_bytes": nbytes, "alg_flops": flops}
+            "stages_ms": st, "stages_source": st_src, "alg_bytes": nbytes, "alg_flops": flops, "skew": skew, "tok": tok}
+
+
+# DRAM traffic of the gate/up GEMM per launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture; the
+# summaries with the full commands are under profiles/).  Keyed by (config, T).
+MEASURED_TRAFFIC = {
+    ("mixtral", 4096): (3.25e9 + 0.235e9, "profiles/grouped_gemm_tcgen05_bf16_mixtral.md, full-size capture"),
+}
 
 
 def dominant_kernel_roofline(cfg, T, point, peaks):
@@ -294,37 +372,79 @@ def dominant_kernel_roofline(cfg, T, point, peaks):
     M = T * cfg.top_k
     flops = 4.0 * M * cfg.H * cfg.I
     nbytes = point["active_experts"] * 2 * cfg.I * cfg.H * bw + T * cfg.H * bw + M * cfg.I * bw
+    traffic, traffic_src = MEASURED_TRAFFIC.get((cfg.name, T), (None, None))
+    common = {"kernel": name, "launch_ms": st[name], "timing": point["stages_source"], "traffic": traffic,
+              "traffic_source": traffic_src, "alg_flops_per_launch": flops, "alg_bytes_per_launch": nbytes}
     if point["bound"] == "tensor":
         peak = peaks["bf16_tflops"] * (2.0 if cfg.dtype == "fp8" else 1.0)
         ach = flops / t / 1e12
-        return {"kernel": name, "bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
-                "traffic": None, "peak_source": peaks["source"] + " (burst cuBLAS bf16" + (", x2 nominal for fp8)" if cfg.dtype == "fp8" else ")"),
-                "launch_ms": st[name], "alg_flops_per_launch": flops}
+        return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                "peak_source": peaks["source"] + " (burst cuBLAS bf16" + (", x2 nominal for fp8)" if cfg.dtype == "fp8" else ")"),
+                **common}
     ach = nbytes / t / 1e9
-    return {"kernel": name, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-            "frac": ach / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"] + " (copy bandwidth)",
-            "launch_ms": st[name], "alg_bytes_per_launch": nbytes}
+    return {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": ach / peaks["hbm_gbs"], "peak_source": peaks["source"] + " (copy bandwidth)", **common}
 
 
 def e2e_run(cfg, wts, T, steps, warmup, seed=0):
-    """Same call from pinned host buffers: H2D of hidden+logits and D2H of the result inside the timed region."""
+    """Same call from pinned host buffers: H2D of hidden+logits and D2H of the result inside the timed region.
+
+    The copies run on two side streams and are double-buffered: while step i computes, the inputs of step i+1
+    are already on their way in and the result of step i-1 on its way out (the three engines of the GPU work
+    at the same time); every step's input copy, compute and output copy are ordered by events."""
     from flaggems_sglang_b200 import workloads as W
 
     tok = W.make_tokens(cfg, T, "cuda", seed=seed)
     h_host = tok["hidden"].cpu().pin_memory()
     l_host = tok["logits"].cpu().pin_memory()
-    out_host = torch.empty(T, cfg.H, dtype=torch.bfloat16 if cfg.dtype != "fp32" else torch.float32).pin_memory()
+    odt = torch.bfloat16 if cfg.dtype != "fp32" else torch.float32
+    out_host = [torch.empty(T, cfg.H, dtype=odt).pin_memory() for _ in range(2)]
+    h_dev = [torch.empty_like(tok["hidden"]) for _ in range(2)]
+    l_dev = [torch.empty_like(tok["logits"]) for _ in range(2)]
+    o_dev = [None, None]
     step = make_step(cfg, wts, tok)
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
 
-    def one():
-        h = h_host.to("cuda", non_blocking=True)
-        lg = l_host.to("cuda", non_blocking=True)
-        out = step(h, lg)
-        out_host.copy_(out, non_blocking=True)
+    def copy_in(i):
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_free[b])  # the compute that last read this buffer has finished
+            h_dev[b].copy_(h_host, non_blocking=True)
+            l_dev[b].copy_(l_host, non_blocking=True)
+            ev_in[b].record(s_in)
 
-    ms = time_steps(one, steps, warmup)
+    def run(n):
+        for b in range(2):
+            ev_free[b].record(main)
+        copy_in(0)
+        for i in range(n):
+            b = i & 1
+            if i + 1 < n:
+                copy_in(i + 1)
+            main.wait_event(ev_in[b])
+            o_dev[b] = step(h_dev[b], l_dev[b])
+            ev_free[b].record(main)
+            ev_done[b].record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_done[b])
+                out_host[b].copy_(o_dev[b], non_blocking=True)
+                o_dev[b].record_stream(s_out)
+        main.wait_stream(s_out)
+
+    run(max(warmup, 2))
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    run(steps)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
     h2d = h_host.numel() * h_host.element_size() + l_host.numel() * l_host.element_size()
-    d2h = out_host.numel() * out_host.element_size()
+    d2h = out_host[0].numel() * out_host[0].element_size()
     return ms, h2d, d2h
 
 
@@ -345,6 +465,110 @@ def launches_per_step(cfg, T):
     return n
 
 
+def sweep_entry(cfg, T, pt, peaks):
+    dom = dominant_kernel_roofline(cfg, T, pt, peaks)
+    return {"T": T, "routing": "zipf-1.2" if pt["skew"] else "uniform", "ms": round(pt["ms"], 4),
+            "tokens_per_s": round(pt["tokens_per_s"], 1), "cuda_graph": pt["cuda_graph"], "l2_flush": pt["l2_flush"],
+            "bound": pt["bound"], "roofline_frac": round(pt["roofline_frac"], 4),
+            "gemm1_frac": None if dom is None else round(dom["frac"], 4), "active_experts": pt["active_experts"],
+            "stages_ms": {k: round(v, 4) for k, v in pt["stages_ms"].items()}, "stages_source": pt["stages_source"]}
+
+
+def config_sweep(name, peaks, steps, extra_T=(), skew_T=()):
+    """Sweep of one more configuration (its own weights, freed afterwards) -> list of sweep entries."""
+    from flaggems_sglang_b200 import workloads as W
+
+    cfg = W.CONFIGS[name]
+    wts = W.make_weights(cfg, "cuda", seed=0)
+    out = []
+    try:
+        for T, skew in [(t, False) for t in sorted(set(cfg.sweep_T) | set(extra_T))] + [(t, True) for t in skew_T]:
+            pt = measure_point(cfg, wts, T, steps, 3, peaks, skew=skew)
+            out.append(sweep_entry(cfg, T, pt, peaks))
+    finally:
+        del wts
+        torch.cuda.empty_cache()
+    return out
+
+
+def parity_vs_oracle(cfg, wts, tok, T):
+    """CPU oracle on the first tokens of the product arm's batch: its timing is the cpu_baseline, its output is
+    compared with the GPU's for those tokens."""
+    step = make_step(cfg, wts, tok)
+    got = step()
+    torch.cuda.synchronize()
+    val, ms, sample, cores, ref, Ts = run_cpu_oracle(cfg, T, 2, 1, gpu=(wts, tok))
+    g, r = got[:Ts].float().cpu(), ref.float()
+    parity = {"tokens": Ts, "against": "CPU oracle (oracle/experts.py) on the same weights and tokens",
+              "rel_l2": float((g - r).norm() / r.norm()), "max_abs_frac": float((g - r).abs().max() / r.abs().max())}
+    return {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}, parity
+
+
+def vs_triton(cfg, wts, tokens):
+    """Same box, same inputs: the REAL reference operator (`flaggems_sglang.triton_kernel_fused_experts` from the
+    offline install under baseline/_ref, running the `triton_kernels` copy vLLM vendors) against this package,
+    both timed with the reference's own method (triton.testing.do_bench, median; ref
+    benchmark/performance_utils.py:365-377).  bf16 only (the reference rejects fp8).  Outside every timed region
+    of the headline."""
+    import tempfile
+
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "flaggems_sglang")):
+        return {"unavailable": "no reference install under baseline/_ref"}
+    try:
+        import vllm
+
+        stub = tempfile.mkdtemp()
+        os.makedirs(os.path.join(stub, "sgl_kernel"))
+        with open(os.path.join(stub, "sgl_kernel", "__init__.py"), "w") as f:
+            f.write("def gelu_and_mul(x, out):\n    raise NotImplementedError\n")
+        os.environ.setdefault("DNN_VENDOR", "nvidia")
+        sys.path[:0] = [ref_dir, os.path.join(os.path.dirname(vllm.__file__), "third_party"), stub]
+        import flaggems_sglang
+        import triton
+        from flaggems_sglang.ops import fused_moe as ref_fm
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"reference import failed: {type(e).__name__}: {e}"[:300]}
+    import flaggems_sglang_b200 as fg
+    from flaggems_sglang_b200 import workloads as W
+
+    out = {"reference": "flaggems_sglang.triton_kernel_fused_experts (baseline/_ref) on vLLM's triton_kernels",
+           "timing": "triton.testing.do_bench median, L2 flushed between calls", "points": []}
+    w1r = wts["w1"].transpose(1, 2).contiguous()  # the reference's [E,H,2I] / [E,I,H] layouts, prepared once
+    w2r = wts["w2"].transpose(1, 2).contiguous()
+    for T in tokens:
+        rec = {"T": T}
+        try:
+            tok = W.make_tokens(cfg, T, "cuda", seed=0)
+            tw, ti = W.route(cfg, tok)
+            x = tok["hidden"]
+            tables = ref_fm._standard_topk_to_triton_kernels(tw, ti, cfg.E)
+
+            def ref_experts():
+                return flaggems_sglang.triton_kernel_fused_experts(x, w1r, w2r, *tables)
+
+            def ref_with_routing():
+                return flaggems_sglang.triton_kernel_fused_experts(
+                    x, w1r, w2r, *ref_fm._standard_topk_to_triton_kernels(tw, ti, cfg.E))
+
+            def ours():
+                return fg.fused_experts(x, wts["w1"], wts["w2"], tw, ti)
+
+            r, g = ref_experts().float(), ours().float()
+            rec["rel_l2"] = float((g - r).norm() / r.norm())
+            rec["reference_experts_ms"] = triton.testing.do_bench(ref_experts, warmup=20, rep=100, return_mode="median")
+            rec["reference_routing_plus_experts_ms"] = triton.testing.do_bench(ref_with_routing, warmup=20, rep=100,
+                                                                                return_mode="median")
+            rec["ours_ms"] = triton.testing.do_bench(ours, warmup=20, rep=100, return_mode="median")
+            rec["speedup_experts"] = rec["reference_experts_ms"] / rec["ours_ms"]
+            rec["speedup_with_routing"] = rec["reference_routing_plus_experts_ms"] / rec["ours_ms"]
+        except Exception as e:  # noqa: BLE001  (the vendored third-party copy is not pinned by the reference)
+            rec["error"] = f"{type(e).__name__}: {e}"[:300]
+        out["points"].append(rec)
+    del w1r, w2r
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -353,10 +577,13 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--config", default="mixtral")
     ap.add_argument("--tokens", type=int, default=4096)
-    ap.add_argument("--no-sweep", action="store_true", help="skip the per-T sweep of the configuration")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the per-T sweeps (this configuration's and the others')")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity leg")
+    ap.add_argument("--no-triton", action="store_true", help="skip the same-box timing of the reference's Triton path")
+    ap.add_argument("--skew", action="store_true", help="Zipf(1.2)-skewed routing for the headline point")
     ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"],
                     help="N>1: token exchange by this package's P2P-store kernels (default) or by NCCL all-to-all")
+    ap.add_argument("--no-c5", action="store_true", help="N>1: skip the DeepSeek-V3 fp8 expert-parallel block")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -382,25 +609,34 @@ def main():
 
     sampler = ClockSampler(0)
     sampler.start()
-    point = measure_point(cfg, wts, T, args.steps, args.warmup, peaks)
+    point = measure_point(cfg, wts, T, args.steps, args.warmup, peaks, skew=args.skew)
     clocks = sampler.stop()
     e2e_ms, h2d, d2h = e2e_run(cfg, wts, T, args.steps, args.warmup)
 
+    sweep_steps = max(5, args.steps // 2)
     sweep = []
     if not args.no_sweep:
         for Ts in cfg.sweep_T:
-            pt = point if Ts == T else measure_point(cfg, wts, Ts, max(5, args.steps // 2), 3, peaks)
-            dom = dominant_kernel_roofline(cfg, Ts, pt, peaks)
-            sweep.append({"T": Ts, "ms": round(pt["ms"], 4), "tokens_per_s": round(pt["tokens_per_s"], 1),
-                          "cuda_graph": pt["cuda_graph"], "l2_flush": pt["l2_flush"], "bound": pt["bound"], "roofline_frac": round(pt["roofline_frac"], 4),
-                          "gemm1_frac": None if dom is None else round(dom["frac"], 4),
-                          "active_experts": pt["active_experts"],
-                          "stages_ms": {k: round(v, 4) for k, v in pt["stages_ms"].items()}})
+            pt = point if (Ts == T and not args.skew) else measure_point(cfg, wts, Ts, sweep_steps, 3, peaks)
+            sweep.append(sweep_entry(cfg, Ts, pt, peaks))
 
-    cpu = None
+    cpu = parity = None
     if not args.no_cpu:
-        val, ms, sample, cores = run_cpu_oracle(cfg, T, 2, 1)
-        cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        cpu, parity = parity_vs_oracle(cfg, wts, point["tok"], T)
+
+    triton_cmp = None
+    if not args.no_triton and cfg.dtype == "bf16":
+        triton_cmp = vs_triton(cfg, wts, [t for t in (64, 1024, 4096) if t in cfg.sweep_T] or [T])
+
+    others = {}
+    if not args.no_sweep and args.config == "mixtral":
+        del wts
+        torch.cuda.empty_cache()
+        # the other configurations of the metric; DeepSeek-V3 also at the per-rank sizes of the expert-parallel
+        # runs (128, 4096), so that weak-scaling efficiency can be read against one GPU doing the same tokens
+        others["qwen3"] = config_sweep("qwen3", peaks, sweep_steps, skew_T=(512, 8192))
+        others["refbench"] = config_sweep("refbench", peaks, sweep_steps)
+        others["dsv3"] = config_sweep("dsv3", peaks, sweep_steps, extra_T=(128, 4096), skew_T=(4096,))
 
     from flaggems_sglang_b200 import _C
 
@@ -409,10 +645,9 @@ def main():
         "metric": METRIC, "value": point["tokens_per_s"], "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": point["ms"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": cfg.dtype, "data": "synthetic",
-        "config": {"workload": f"{cfg.name} MoE layer H={cfg.H} I={cfg.I} E={cfg.E} top_k={cfg.top_k}, T={T}, "
-                               f"softmax top-k renormalised" if cfg.router == "softmax" else
-                               f"{cfg.name} MoE layer H={cfg.H} I={cfg.I} E={cfg.E} top_k={cfg.top_k}, T={T}, grouped top-k",
-                   "tokens_per_step": T, "l2": ("flushed before every step" if point["l2_flush"]
+        "config": {"workload": workload_name(cfg, T), "tokens_per_step": T,
+                   "routing": "zipf-1.2 skew" if args.skew else "uniform",
+                   "l2": ("flushed before every step" if point["l2_flush"]
                           else "weights re-read every step exceed L2 (no flush needed)"),
                    "active_experts": point["active_experts"]},
         "roofline": dominant_kernel_roofline(cfg, T, point, peaks),
@@ -420,11 +655,15 @@ def main():
                            "achieved_tflops": point["achieved_tflops"], "achieved_gbs": point["achieved_gbs"],
                            "peaks": peaks},
         "cpu_baseline": cpu,
+        "parity": parity,
         "e2e": {"value": T / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h},
+                "d2h_bytes_per_step": d2h, "copies": "pinned host buffers, side streams, double-buffered"},
         "gpu_launches": launches_per_step(cfg, T) * args.steps,
         "clocks": clocks,
+        "stages_ms": {k: round(v, 4) for k, v in point["stages_ms"].items()},
         "sweep": sweep,
+        **others,
+        "vs_triton": triton_cmp,
     }
     print(json.dumps(line), flush=True)
 

@@ -122,7 +122,20 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
   return FMOE_OK;
 }
 
+namespace {
+// Optional per-stage timing (fmoe_debug_stage_events): events of the calling thread's NEXT fused call.
+thread_local void* const* t_stage_events = nullptr;
+thread_local int t_stage_count = 0;
+}  // namespace
+
 int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* stream) {
+  void* const* stage_ev = t_stage_events;
+  const int stage_n = t_stage_count;
+  t_stage_events = nullptr;
+  t_stage_count = 0;
+  auto mark = [&](int i) {
+    if (stage_ev && i < stage_n && stage_ev[i]) cudaEventRecord((cudaEvent_t)stage_ev[i], (cudaStream_t)stream);
+  };
   if (a.T == 0) return FMOE_OK;
   FMOE_REQUIRE(a.hidden && a.w1 && a.w2 && a.topk_weights && a.topk_ids && (a.out || a.out_rows), "fused_experts: null pointer");
   if (a.out_rows) {
@@ -142,9 +155,11 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
   void* z = a.no_combine ? a.out : (void*)(ws + p.off_z);
   auto st = (cudaStream_t)stream;
 
+  mark(0);
   int rc = fmoe_moe_align_block_size_ws(a.topk_ids, p.numel, a.num_experts, p.block, sorted, p.cap, experts, p.nblk, npp,
                                         ws + p.off_align_ws, p.align_ws_bytes, stream);
   if (rc) return rc;
+  mark(1);
   if (a.zero_dropped) FMOE_CUDA_OK(cudaMemsetAsync(z, 0, (size_t)(p.numel * a.H * eb), st));
 
   fmoe_gemm_args g{};
@@ -223,18 +238,24 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
     g2.a_scale = reinterpret_cast<float*>(ws + p.off_actq_scale);
     g2.w_scale = a.w2_scale;
   }
+  mark(2);
   rc = fmoe_gemm1_silu(&g1, stream);
   if (rc) return rc;
+  mark(3);
   if (fp8) {
     // padding positions of the sorted order (most of the rows at small T) are zero-filled, not quantised
     rc = fmoe_quant_fp8_group128(act, g1.out_dtype, p.cap, a.I, sorted, 0, p.numel, npp, ws + p.off_actq,
                                  reinterpret_cast<float*>(ws + p.off_actq_scale), stream);
     if (rc) return rc;
   }
+  mark(4);
   rc = fmoe_gemm2(&g2, stream);
   if (rc) return rc;
+  mark(5);
   if (a.no_combine) return FMOE_OK;
-  return fmoe_moe_sum(z, io, a.T, a.top_k, a.H, a.routed_scaling_factor == 0.f ? 1.0f : a.routed_scaling_factor, a.out, stream);
+  rc = fmoe_moe_sum(z, io, a.T, a.top_k, a.H, a.routed_scaling_factor == 0.f ? 1.0f : a.routed_scaling_factor, a.out, stream);
+  mark(6);
+  return rc;
 }
 
 }  // namespace fmoe
@@ -243,6 +264,14 @@ extern "C" int fmoe_pick_variant(int dtype, int64_t numel, int E, int64_t I, int
                                  int* variant_out, int* block_out) {
   if (!variant_out || !block_out) return fmoe::fail(FMOE_ERR_INVALID_ARG, "pick_variant: null output pointer");
   return fmoe::pick_variant(dtype, numel, E, I, H, forced_variant, variant_out, block_out);
+}
+
+extern "C" int fmoe_debug_stage_events(void* const* events, int n) {
+  if (n < 0 || n > FMOE_STAGE_EVENTS || (n > 0 && !events))
+    return fmoe::fail(FMOE_ERR_INVALID_ARG, "stage events: need 0 <= n <= %d and a non-null array", FMOE_STAGE_EVENTS);
+  fmoe::t_stage_events = n ? events : nullptr;
+  fmoe::t_stage_count = n;
+  return FMOE_OK;
 }
 
 extern "C" int64_t fmoe_fused_experts_workspace_bytes(const fmoe_fused_args* args) {

@@ -345,6 +345,18 @@ int fmoe_check_device_status(void* stream);
 int fmoe_selftest_bounded_wait(int64_t limit_cycles, void* stream);
 
 /*
+ * Diagnostic: per-stage device timing of the calling thread's NEXT fmoe_fused_experts / _static call.
+ * `events` is a HOST array of n cudaEvent_t handles (created by the caller with timing enabled, NULL entries
+ * are skipped) that stays valid until that call returns; the call records them on its stream at the stage
+ * boundaries and forgets the array:
+ *   [0] start  [1] align done  [2] input rows gathered / quantised  [3] gate/up GEMM done
+ *   [4] activations quantised (e4m3 only)  [5] down GEMM done  [6] sum done
+ * n = 0 cancels.  No counterpart in the reference (it times whole calls, benchmark/performance_utils.py:365-377).
+ */
+#define FMOE_STAGE_EVENTS 7
+int fmoe_debug_stage_events(void* const* events, int n);
+
+/*
  * Diagnostic: with the environment variable FMOE_TC_PROFILE set, the bf16 tcgen05 kernel records, per
  * CTA, clock cycles spent waiting {tiles, MMA on accumulator, MMA on data, producer on free stage,
  * epilogue on accumulator, epilogue busy, -, -}.  Copies the last launch's n values (8 per CTA, at most

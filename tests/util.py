@@ -5,10 +5,15 @@ import torch
 # Tolerances of the floating-point parity tests (the kernels fuse silu*mul into the first
 # GEMM's epilogue and accumulate in a different order than the oracle's fp32 matmul, so
 # outputs differ from it by rounding noise of the storage type):
-BF16_REL_L2 = 1e-2          # relative L2 error, bf16 path
-BF16_MAX_ABS_FRAC = 2.0 ** -6  # max |diff| <= this * max|ref|
-FP8_REL_L2 = 3e-2
-FP8_MAX_ABS_FRAC = 2.0 ** -3
+BF16_REL_L2 = 1e-2          # relative L2 error, bf16 path (worst seen on B200: 5.1e-3)
+# max |diff| <= this * max|ref|.  One bf16 ulp at the largest magnitude is between 2^-8 and 2^-7 of it, and the two
+# sides round intermediates at different points, so a 2-ulp difference on the largest element (2^-6) is the bar
+# for arbitrary cases (worst seen: 9.9e-3); the end-to-end comparison with the real reference operator
+# (tests/test_e2e_reference.py) holds the tighter 2^-7 (worst seen: 6.8e-3).
+BF16_MAX_ABS_FRAC = 2.0 ** -6
+BF16_MAX_ABS_FRAC_E2E = 2.0 ** -7
+FP8_REL_L2 = 3e-2           # worst seen: 1.2e-2
+FP8_MAX_ABS_FRAC = 2.0 ** -5   # worst seen: 1.9e-2
 FP32_REL_L2 = 1e-5
 
 

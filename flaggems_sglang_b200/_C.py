@@ -111,6 +111,7 @@ SIGNATURES = {
     "fmoe_selftest_bounded_wait": (c_int, [c_int64, c_void_p]),
     "fmoe_debug_tcgen05_wait_profile": (c_int, [c_void_p, c_int]),
     "fmoe_debug_stage_events": (c_int, [c_void_p, c_int]),
+    "fmoe_debug_wait_profile": (c_int, [c_int, c_void_p, c_int]),
     "fmoe_check_device_status": (c_int, [c_void_p]),
 }
 

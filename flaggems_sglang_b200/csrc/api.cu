@@ -112,6 +112,8 @@ extern "C" int fmoe_gemm2(const fmoe_gemm_args* args, void* stream) {
 
 namespace fmoe {
 int read_wait_profile(long long* host_out, int n);
+int read_wait_profile_pair(long long* host_out, int n);
+int read_wait_profile_fp8(long long* host_out, int n);
 int launch_bounded_wait_selftest(long long limit_cycles, cudaStream_t st);
 }  // namespace fmoe
 
@@ -123,6 +125,14 @@ extern "C" int fmoe_selftest_bounded_wait(int64_t limit_cycles, void* stream) {
 extern "C" int fmoe_debug_tcgen05_wait_profile(int64_t* host_out, int n) {
   if (!host_out || n < 0 || n > 256 * 8) return fmoe::fail(FMOE_ERR_INVALID_ARG, "wait profile: bad buffer");
   return fmoe::read_wait_profile(reinterpret_cast<long long*>(host_out), n);
+}
+
+extern "C" int fmoe_debug_wait_profile(int variant, int64_t* host_out, int n) {
+  if (!host_out || n < 0 || n > (variant == -FMOE_VARIANT_TCGEN05 ? 2 : 1) * 256 * 8) return fmoe::fail(FMOE_ERR_INVALID_ARG, "wait profile: bad buffer");
+  if (variant == FMOE_VARIANT_TCGEN05) return fmoe::read_wait_profile(reinterpret_cast<long long*>(host_out), n);
+  if (variant == FMOE_VARIANT_TCGEN05_PAIR) return fmoe::read_wait_profile_pair(reinterpret_cast<long long*>(host_out), n);
+  if (variant == -FMOE_VARIANT_TCGEN05) return fmoe::read_wait_profile_fp8(reinterpret_cast<long long*>(host_out), n);
+  return fmoe::fail(FMOE_ERR_INVALID_ARG, "wait profile: variant %d keeps none", variant);
 }
 
 extern "C" int fmoe_check_device_status(void* stream) {

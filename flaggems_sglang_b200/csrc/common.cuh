@@ -95,7 +95,7 @@ inline cudaError_t per_device_once(PerDeviceOnce& st, Fn fn) {
   return err;
 }
 
-inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+__host__ __device__ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 template <typename T>
 __host__ __device__ constexpr T ceil_div(T a, T b) {

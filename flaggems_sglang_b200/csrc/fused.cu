@@ -16,7 +16,9 @@ int pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forc
   const int64_t active = std::max<int64_t>(1, std::min<int64_t>(E, numel));
   const double rows = (double)numel / (double)active;  // rows per active expert if routing were uniform
   const bool stream_ok = (H % 128 == 0) && (I % 128 == 0);
-  const bool tc_ok = dtype == FMOE_BF16 ? (I % 128 == 0 && H % 32 == 0) : (I % 128 == 0 && H % 128 == 0);
+  // e4m3: a tile's block scales are staged in shared memory, which bounds the reduction length at 8192
+  const bool tc_ok = dtype == FMOE_BF16 ? (I % 128 == 0 && H % 32 == 0)
+                                        : (I % 128 == 0 && H % 128 == 0 && I <= 8192 && H <= 8192);
   int v = forced;
   if (v == FMOE_VARIANT_AUTO) {
     // measured on B200: up to 4 rows per expert the two families tie (both stream the weights once at ~90 % of
@@ -28,7 +30,7 @@ int pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forc
   }
   switch (v) {
     case FMOE_VARIANT_TCGEN05:
-      if (!tc_ok) return fail(FMOE_ERR_UNSUPPORTED, "tcgen05 kernels need I %% 128 == 0 and H %% 32 == 0 (128 for e4m3)");
+      if (!tc_ok) return fail(FMOE_ERR_UNSUPPORTED, "tcgen05 kernels need I %% 128 == 0 and H %% 32 == 0 (e4m3: H %% 128 == 0, H and I up to 8192)");
       *block = 128;
       break;
     case FMOE_VARIANT_TCGEN05_PAIR:

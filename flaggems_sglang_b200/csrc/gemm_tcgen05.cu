@@ -44,7 +44,7 @@ struct Ring {
   static constexpr int A_BYTES = BM * KB;
   static constexpr int B_BYTES = BN * KB;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;  // + expert table
 };
 constexpr int TMEM_COLS = 512;
 constexpr int kThreads = 192;
@@ -69,6 +69,8 @@ struct TcParams {
   int32_t activation;
   int32_t group_m;
   int32_t profile;
+  int32_t l2_hints;    // 1: TMA loads carry L2 eviction priorities (weights evict_first, activation rows evict_last)
+  int32_t debug;       // timing experiment only (results are wrong): 1 = no TMA loads, the MMA warp never waits for data
   int32_t top_k;       // gather mode: input row of slot s is s / top_k
   int32_t a_rows;      // gather mode: rows of the input tensor (a row index >= a_rows reads zeros)
 };
@@ -104,6 +106,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   uint64_t* acc_full = bars + 2 * STAGES;     // [2] MMA -> epilogue
   uint64_t* acc_empty = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  int32_t* expert_table = reinterpret_cast<int32_t*>(smem + STAGES * STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -126,13 +129,13 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     ptx::tmem_alloc(tmem_slot, TMEM_COLS);
     ptx::tmem_relinquish();
   }
+  const int used_blocks = min((int)(*p.num_tokens_post_padded / BM), p.max_blocks);
+  const int64_t total_tiles = (int64_t)used_blocks * p.n_tiles;
   ptx::tc_fence_before_sync();
-  __syncthreads();
+  build_expert_table(expert_table, p.num_experts, p.expert_ids, used_blocks);  // ends with __syncthreads()
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int used_blocks = min((int)(*p.num_tokens_post_padded / BM), p.max_blocks);
-  const int64_t total_tiles = (int64_t)used_blocks * p.n_tiles;
   TileCursor cursor;
   const int k_steps = p.k_steps;
 
@@ -144,9 +147,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     long long prof_a = 0;
     // coordinates of a tile; looked up one tile ahead so that the index loads never stall the ring
     auto tile_rows = [&](int64_t tile, int32_t* row_a, int32_t* row_b0, int32_t* row_b1) {
-      int m_blk, n_tile;
-      cursor.locate(tile, used_blocks, p.n_tiles, p.group_m, p.expert_ids, &m_blk, &n_tile);
-      const int e = min(max(p.expert_ids[m_blk], 0), p.num_experts - 1);
+      int m_blk, n_tile, e;
+      cursor.locate(tile, p.n_tiles, p.group_m, p.num_experts, p.expert_ids, expert_table, &m_blk, &n_tile, &e);
       *row_a = m_blk * BM;
       *row_b0 = (int32_t)((int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256));
       *row_b1 = GATED ? (int32_t)(*row_b0 + p.n) : *row_b0 + 128;
@@ -157,13 +159,14 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       auto src = [&](int32_t slot) { return (slot >= 0 && slot < p.numel) ? slot / p.top_k : p.a_rows; };
       return make_int4(src(s.x), src(s.y), src(s.z), src(s.w));
     };
+    const uint64_t pol_w = ptx::l2_policy_evict_first(), pol_a = ptx::l2_policy_evict_last();
     int32_t row_a = 0, row_b0 = 0, row_b1 = 0, nrow_a = 0, nrow_b0 = 0, nrow_b1 = 0;
     int4 src_rows = make_int4(0, 0, 0, 0), nsrc_rows = src_rows;
     if ((int64_t)blockIdx.x < total_tiles) {
       tile_rows(blockIdx.x, &row_a, &row_b0, &row_b1);
       if constexpr (GATHER) src_rows = lane_rows(row_a);
     }
-    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+    for (int64_t tile = blockIdx.x; tile < total_tiles && alive && p.debug != 1; tile += gridDim.x) {
       const bool has_next = tile + gridDim.x < total_tiles;
       for (int ks = 0; ks < k_steps; ++ks) {
         const long long tp0 = p.profile ? clock64() : 0;
@@ -179,9 +182,15 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           uint8_t* sb = sa + A_BYTES;
           ptx::mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
           const int32_t x = ks * (KBYTES / 2);  // element coordinate (bf16)
-          if constexpr (!GATHER) ptx::tma_load_2d(sa, &map_a, x, row_a, &full_bar[stage]);
-          ptx::tma_load_2d(sb, &map_b, x, row_b0, &full_bar[stage]);
-          ptx::tma_load_2d(sb + B_BYTES / 2, &map_b, x, row_b1, &full_bar[stage]);
+          if (p.l2_hints) {
+            if constexpr (!GATHER) ptx::tma_load_2d_hint(sa, &map_a, x, row_a, &full_bar[stage], pol_a);
+            ptx::tma_load_2d_hint(sb, &map_b, x, row_b0, &full_bar[stage], pol_w);
+            ptx::tma_load_2d_hint(sb + B_BYTES / 2, &map_b, x, row_b1, &full_bar[stage], pol_w);
+          } else {
+            if constexpr (!GATHER) ptx::tma_load_2d(sa, &map_a, x, row_a, &full_bar[stage]);
+            ptx::tma_load_2d(sb, &map_b, x, row_b0, &full_bar[stage]);
+            ptx::tma_load_2d(sb + B_BYTES / 2, &map_b, x, row_b1, &full_bar[stage]);
+          }
         }
         __syncwarp();
         if constexpr (GATHER) {
@@ -205,7 +214,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     }
     if (p.profile && lane == 0 && blockIdx.x < 256) g_wait_prof[blockIdx.x * 8 + 3] = prof_a;
     // drain: do not leave while our own bulk copies may still be landing in shared memory
-    if (alive) {
+    if (alive && p.debug != 1) {
       for (int s = 0; s < STAGES; ++s) {
         // the consumer releases a stage only after its data arrived, so waiting for every
         // stage to be free again covers all outstanding copies
@@ -243,7 +252,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       const uint32_t d_tmem = tmem_base + acc * BN;
       for (int ks = 0; ks < k_steps; ++ks) {
         const long long tm1 = p.profile ? clock64() : 0;
-        const bool okd = warp_wait(&full_bar[stage], phase);
+        const bool okd = p.debug == 1 ? true : warp_wait(&full_bar[stage], phase);
         if (p.profile) prof_data += clock64() - tm1;
         if (!okd) {
           report(0x240 | stage);
@@ -260,7 +269,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             // 32 bytes of K per MMA (16 bf16): advance the start address by 32 B = 2 units
             ptx::mma_f16_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (ks | kk) != 0);
           }
-          ptx::mma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
+          if (p.debug != 1) ptx::mma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
         }
         __syncwarp();
         if (++stage == STAGES) {
@@ -283,8 +292,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     long long prof_wait = 0, prof_busy = 0;
     const int row = warp * 32 + lane;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-      int m_blk, n_tile;
-      cursor.locate(tile, used_blocks, p.n_tiles, p.group_m, p.expert_ids, &m_blk, &n_tile);
+      int m_blk, n_tile, tile_e;
+      cursor.locate(tile, p.n_tiles, p.group_m, p.num_experts, p.expert_ids, expert_table, &m_blk, &n_tile, &tile_e);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ++local;
@@ -294,7 +303,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       const float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
       // bias entries of this tile's columns (the same for every row: broadcast loads)
       const float* bias = (EXTRA && p.bias)
-                              ? p.bias + (int64_t)min(max(p.expert_ids[m_blk], 0), p.num_experts - 1) * p.w_rows +
+                              ? p.bias + (int64_t)tile_e * p.w_rows +
                                     (int64_t)n_tile * (GATED ? 128 : 256)
                               : nullptr;
       const long long te0 = p.profile ? clock64() : 0;
@@ -467,12 +476,14 @@ namespace {
 
 template <bool GATED, int KB, bool GATHER, bool EXTRA>
 int launch(const GemmParams& g, cudaStream_t st) {
-  constexpr int SMEM_BYTES = Ring<KB>::SMEM_BYTES, KBYTES = KB;
+  constexpr int KBYTES = KB;
+  constexpr int MAX_SMEM = Ring<KB>::SMEM_BYTES + expert_table_bytes(1024);
+  const int SMEM_BYTES = Ring<KB>::SMEM_BYTES + expert_table_bytes(g.num_experts);
   const int sm_count = device_sm_count();
   static PerDeviceOnce once_attr;  // the opt-in to > 48 KB of dynamic shared memory is per device
   const cudaError_t attr_err = per_device_once(once_attr, [] {
     return cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA>,
-                                cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
   });
   if (attr_err != cudaSuccess)
     return fail(FMOE_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", SMEM_BYTES, cudaGetErrorString(attr_err));
@@ -510,6 +521,8 @@ int launch(const GemmParams& g, cudaStream_t st) {
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sm_count > 0 ? sm_count : 148, max_tiles));
   p.group_m = pick_group_m(BM, g.k * 2);
   p.profile = getenv("FMOE_TC_PROFILE") != nullptr;
+  p.debug = getenv("FMOE_TC_DEBUG") ? atoi(getenv("FMOE_TC_DEBUG")) : 0;
+  p.l2_hints = getenv("FMOE_TC_L2_HINTS") ? atoi(getenv("FMOE_TC_L2_HINTS")) : 0;
   grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_kernel");
 }
@@ -526,7 +539,7 @@ bool gemm_tcgen05_supports(const GemmParams& p, bool gated) {
   if (p.n <= 0 || p.n % (gated ? 128 : 32) != 0) return false;  // gate/up pairing; 64-byte epilogue stores
   if (!aligned16(p.a) || !aligned16(p.w) || !(aligned16(p.out) && (p.out || (!gated && p.out_rows)))) return false;
   if ((int64_t)p.num_experts * (gated ? 2 * p.n : p.n) >= (1ll << 31) || p.a_rows >= (1ll << 31)) return false;
-  if (p.max_blocks >= (1ll << 24)) return false;
+  if (p.max_blocks >= (1ll << 24) || p.num_experts > 1024) return false;
   return true;
 }
 

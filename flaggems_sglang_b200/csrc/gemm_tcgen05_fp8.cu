@@ -2,43 +2,58 @@
 //
 // tcgen05 accumulates in fp32 inside TMEM and cannot apply a different scale to every 128-wide K block, so
 // every K block (128 bytes = 128 e4m3 = one scale block) is multiplied into a FRESH 128x256 TMEM partial
-// (4 MMAs of K=32, the first one overwriting), and the epilogue warps fold it into register accumulators:
+// (4 MMAs of K=32, the first one overwriting), and the fold warps add it into register accumulators:
 //     acc[row, col] += partial[row, col] * a_scale[row, kb] * w_scale[col/128, kb]
 // Two TMEM partials (2 x 256 columns) ping-pong, so the MMAs of block kb+1 run while block kb is folded.
 //
-//   warps 0-15: fold + epilogue.  Warp w owns TMEM lanes 32*(w%4).. (rows) and quarter c = w/4 of the columns:
-//               gemm1: gate columns [32c,32c+32) and the matching up columns [128+32c, ...), 64 accumulators;
-//               gemm2: columns [64c, 64c+64).  Four warps per scheduler hide the TMEM load latency.
-//   warp 16   : TMA producer (A 128x128 B box, B two 128-row boxes), 4-stage ring
+//   warps 0-15: fold + epilogue.  Warp w owns TMEM lanes 32*(w%4).. (rows) and, of each 128-column half of the
+//               partial, columns [32c, 32c+32) with c = w/4: 64 accumulators per thread.  gemm1: the halves are the
+//               gate and the up columns; gemm2: output columns n0+32c.. and n0+128+32c...  The FMAs are issued as
+//               packed fma.rn.f32x2 (two accumulators per instruction): the fold is bound by instruction issue.
+//   warp 16   : TMA producer (A 128x128 B box, B two 128-row boxes), 3-stage ring
 //   warp 17   : MMA issuer
+//   warps 18-19: scale stagers.  One tile ahead of the fold warps they look the tile up (expert, row block, column
+//               tile) and copy its block scales into shared memory: the 128 x K/128 activation scales transposed to
+//               [K block][row] and the two weight-scale rows.  Read straight from global memory by the fold warps,
+//               the activation scales cost 32 L1 wavefronts per warp and K block (one per row); from shared memory
+//               they are one conflict-free wavefront, and the fold warps keep no pointers or tile cursor in registers
+//               (the kernel runs at its 96-register limit, every spill lands in the fold loop).
 // Same tile schedule, bounded waits and status word as the bf16 kernel; cluster size 1, every CTA loads its own tiles.
 #include "gemm.cuh"
 #include "ptx_sm100.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace fmoe {
 
 // This translation unit's status word (device code is not linked across files); read by status_word_fp8().
 __device__ int g_device_status_fp8 = 0;
+// Wait-time profile of the instrumented build of the kernel (FMOE_TC_PROFILE=1): per CTA
+// {tiles, fold waits for the MMAs, fold busy, fold waits for staged scales, epilogue, kernel cycles, -, -};
+// [0]: down GEMM, [1]: gate/up GEMM
+__device__ long long g_wait_prof_fp8[2 * 256 * 8];
 
 namespace {
 
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int KBYTES = 128;
-// Three 48 KB stages (147 KB of shared memory -> 164 KB carve-out, 92 KB of L1) measured 2.5-4 % faster on the
-// gate/up GEMM than four (196 KB carve-out, 60 KB of L1): the kernel is bound by its fold warps, which read block
-// scales and a few spilled registers through L1, not by TMA latency.  One KB beyond the 196 KB carve-out (228 KB,
-// 28 KB of L1) measured 40 % slower.
+// Three 48 KB stages: the kernel is bound by its fold warps, not by TMA latency, and the space is better spent on
+// the staged scales.
 constexpr int STAGES = 3;
 constexpr int A_BYTES = BM * KBYTES;
 constexpr int B_BYTES = BN * KBYTES;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int kEpiWarps = 16;
-constexpr int kThreads = (kEpiWarps + 4) * 32;  // warps 18, 19 only exist to complete the fifth warpgroup
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int kThreads = (kEpiWarps + 4) * 32;
+constexpr int SMEM_BASE_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int kMaxStagedKBlocks = 64;  // two scale buffers of (128 + 2) * kblocks floats + 16 bytes must fit beside the ring
+constexpr int scale_buf_bytes(int kblocks) { return (BM + 2) * kblocks * 4 + 16; }
+constexpr int smem_bytes(int kblocks, int num_experts) {
+  return SMEM_BASE_BYTES + expert_table_bytes(num_experts) + 2 * scale_buf_bytes(kblocks);
+}
 
 struct Fp8Params {
   const int32_t* sorted_token_ids;
@@ -59,17 +74,44 @@ struct Fp8Params {
   int32_t max_blocks;
   int32_t activation;
   int32_t group_m;
+  int32_t spin;   // 1: the partial hand-overs are polled with test_wait instead of try_wait
+  int32_t debug;  // instrumented build only, timing experiments (results are wrong): bit 0 = the fold skips the TMEM
+                  // read-out and the FMAs, bit 1 = no MMAs are issued, bit 2 = read-out without FMAs
 };
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_device_status_fp8, 0, code); }
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
   return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity));
 }
+// hand-overs of the TMEM partials (once per K block in each direction): polled without suspending
+template <bool SPIN>
+__device__ __forceinline__ bool warp_wait_fast(uint64_t* bar, uint32_t parity) {
+  return __all_sync(0xffffffffu, SPIN ? ptx::mbar_wait_spin(bar, parity) : ptx::mbar_wait(bar, parity));
+}
 
-template <bool GATED>
+// acc (two packed floats) += v * f, both lanes
+__device__ __forceinline__ void fma2(unsigned long long& acc, uint32_t v0, uint32_t v1, unsigned long long ff) {
+  unsigned long long v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(v0), "r"(v1));
+  asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc) : "l"(v), "l"(ff));
+}
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+  unsigned long long v;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(a), "f"(b));
+  return v;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+
+// MODE 0: production.  MODE 1: instrumented build with wait-time counters (reading the clock is slow enough to distort
+// the fold loop; use it for proportions only).  MODE 2: timing experiments selected by Fp8Params::debug, no counters.
+template <bool GATED, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                 const Fp8Params p) {
+  constexpr bool PROF = MODE == 1;
+  constexpr bool DBG = MODE == 2;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -77,9 +119,15 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
   uint64_t* empty_bar = bars + STAGES;            // [STAGES] MMA -> TMA
   uint64_t* part_full = bars + 2 * STAGES;        // [2] MMA -> fold
   uint64_t* part_empty = bars + 2 * STAGES + 2;   // [2] fold -> MMA
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* scale_full = bars + 2 * STAGES + 4;   // [2] stagers -> fold
+  uint64_t* scale_empty = bars + 2 * STAGES + 6;  // [2] fold -> stagers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 8);
+  int32_t* expert_table = reinterpret_cast<int32_t*>(smem + STAGES * STAGE_BYTES + 256);
+  // staged scales, two buffers: [kblocks][128] activation scales, [2][kblocks] weight scales, {m_blk, n_tile, expert, -}
+  uint8_t* scale_base = smem + STAGES * STAGE_BYTES + 256 + expert_table_bytes(p.num_experts);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long t_kernel0 = PROF ? clock64() : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -89,6 +137,8 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(&part_full[a], 1);
       ptx::mbar_init(&part_empty[a], kEpiWarps);  // one arrival per fold warp
+      ptx::mbar_init(&scale_full[a], 2);           // one arrival per stager warp
+      ptx::mbar_init(&scale_empty[a], kEpiWarps);
     }
     ptx::fence_barrier_init();
   }
@@ -100,26 +150,24 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     ptx::tmem_alloc(tmem_slot, TMEM_COLS);
     ptx::tmem_relinquish();
   }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  ptx::tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-
   const int used_blocks = min((int)(*p.num_tokens_post_padded / BM), p.max_blocks);
   const int64_t total_tiles = (int64_t)used_blocks * p.n_tiles;
-  TileCursor cursor;
+  ptx::tc_fence_before_sync();
+  build_expert_table(expert_table, p.num_experts, p.expert_ids, used_blocks);  // ends with __syncthreads()
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
   const int kblocks = p.kblocks;
 
   if (warp == kEpiWarps) {
     // ---------------- TMA producer ----------------
+    TileCursor cursor;
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
-    // coordinates of a tile; looked up one tile ahead so that the index loads never stall the ring
+    // coordinates of a tile; looked up one tile ahead so that the index load never stalls the ring
     auto tile_rows = [&](int64_t tile, int32_t* row_a, int32_t* row_b0, int32_t* row_b1) {
-      int m_blk, n_tile;
-      cursor.locate(tile, used_blocks, p.n_tiles, p.group_m, p.expert_ids, &m_blk, &n_tile);
-      const int e = min(max(p.expert_ids[m_blk], 0), p.num_experts - 1);
+      int m_blk, n_tile, e;
+      cursor.locate(tile, p.n_tiles, p.group_m, p.num_experts, p.expert_ids, expert_table, &m_blk, &n_tile, &e);
       *row_a = m_blk * BM;
       *row_b0 = (int32_t)((int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256));
       *row_b1 = GATED ? (int32_t)(*row_b0 + p.n) : *row_b0 + 128;
@@ -177,7 +225,7 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
       for (int kb = 0; kb < kblocks; ++kb, ++step) {
         const int buf = step & 1;
         const uint32_t buf_phase = (step >> 1) & 1;
-        if (!warp_wait(&part_empty[buf], buf_phase ^ 1)) {
+        if (!(p.spin ? warp_wait_fast<true>(&part_empty[buf], buf_phase ^ 1) : warp_wait_fast<false>(&part_empty[buf], buf_phase ^ 1))) {
           report(0x600 | buf);
           alive = false;
           break;
@@ -193,9 +241,11 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
           const uint64_t da = ptx::smem_desc_sw128(sa);
           const uint64_t db = ptx::smem_desc_sw128(sa + A_BYTES);
           const uint32_t d_tmem = tmem_base + buf * BN;
+          if (!DBG || !(p.debug & 2)) {
 #pragma unroll
-          for (int kk = 0; kk < KBYTES / 32; ++kk)
-            ptx::mma_f8f6f4_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, kk != 0);
+            for (int kk = 0; kk < KBYTES / 32; ++kk)
+              ptx::mma_f8f6f4_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, kk != 0);
+          }
           ptx::mma_commit(&empty_bar[stage]);
           ptx::mma_commit(&part_full[buf]);
         }
@@ -208,72 +258,85 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     }
   } else if (warp < kEpiWarps) {
     // ---------------- fold + epilogue (warps 0-15) ----------------
-    const int quarter = warp & 3, cpart = warp >> 2;  // TMEM lane quarter, column quarter
+    const int quarter = warp & 3, cpart = warp >> 2;  // TMEM lane quarter, 32-column piece of each half
     const int row = quarter * 32 + lane;
-    const int64_t sblocks_per_expert = p.w_rows / 128;
     uint32_t step = 0;
+    uint32_t ltile = 0;  // tiles started by this CTA (selects the scale buffer and its phase)
     bool alive = true;
-    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
-      int m_blk, n_tile;
-      cursor.locate(tile, used_blocks, p.n_tiles, p.group_m, p.expert_ids, &m_blk, &n_tile);
-      const int e = min(max(p.expert_ids[m_blk], 0), p.num_experts - 1);
+    long long prof_fw = 0, prof_fb = 0, prof_sw = 0, prof_epi = 0;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++ltile) {
+      const int tb = (int)(ltile & 1);
+      const float* s_a = reinterpret_cast<const float*>(scale_base + tb * scale_buf_bytes(kblocks)) + row;
+      const float* s_w = reinterpret_cast<const float*>(scale_base + tb * scale_buf_bytes(kblocks)) + BM * kblocks;
+      const long long tq0 = PROF ? clock64() : 0;
+      if (!warp_wait(&scale_full[tb], (ltile >> 1) & 1)) {
+        report(0x740 | tb);
+        alive = false;
+        break;
+      }
+      if (PROF) prof_sw += clock64() - tq0;
+      const int32_t* meta = reinterpret_cast<const int32_t*>(s_w + 2 * kblocks);
+      const int m_blk = meta[0], n_tile = meta[1];
       const int64_t pos = (int64_t)m_blk * BM + row;
-      const bool in_cap = pos < p.sorted_cap;
-      const int32_t slot = in_cap ? p.sorted_token_ids[pos] : -1;
-      const bool valid = slot >= 0 && slot < p.numel;
-      const float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
-      const float* sa_row = p.a_scale + (in_cap ? pos : 0) * kblocks;
-      // weight-scale rows of this warp's two 32-column pieces (gemm1: gate / up; gemm2: both in one 128-block)
-      const int64_t sw_blk0 = GATED ? n_tile : min(2 * (int64_t)n_tile + (cpart >> 1), sblocks_per_expert - 1);
-      const int64_t sw_blk1 = GATED ? (p.n / 128 + n_tile) : sw_blk0;
-      const float* sw0 = p.w_scale + ((int64_t)e * sblocks_per_expert + sw_blk0) * kblocks;
-      const float* sw1 = p.w_scale + ((int64_t)e * sblocks_per_expert + sw_blk1) * kblocks;
-      const int col0 = GATED ? 32 * cpart : 64 * cpart;
-      const int col1 = GATED ? 128 + 32 * cpart : 64 * cpart + 32;
+      const int32_t slot = (pos < p.sorted_cap) ? p.sorted_token_ids[pos] : -1;  // consumed by the epilogue
 
-      float acc[64];
+      unsigned long long acc[32];  // 64 packed accumulators: [0,16) first half's 32 columns, [16,32) second half's
 #pragma unroll
-      for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+      for (int i = 0; i < 32; ++i) acc[i] = 0ull;
 
-      float sa_n = in_cap ? sa_row[0] : 0.f, s0_n = sw0[0], s1_n = sw1[0];
+      float sa_n = s_a[0], s0_n = s_w[0], s1_n = s_w[kblocks];
       for (int kb = 0; kb < kblocks; ++kb, ++step) {
         const int buf = step & 1;
-        const uint32_t buf_phase = (step >> 1) & 1;
         const float f0 = sa_n * s0_n, f1 = sa_n * s1_n;
-        if (kb + 1 < kblocks) {  // prefetch the next block's scales while waiting for the MMAs
-          sa_n = in_cap ? sa_row[kb + 1] : 0.f;
-          s0_n = sw0[kb + 1];
-          s1_n = sw1[kb + 1];
+        if (kb + 1 < kblocks) {  // the next block's scales, fetched while waiting for the MMAs
+          sa_n = s_a[(kb + 1) * BM];
+          s0_n = s_w[kb + 1];
+          s1_n = s_w[kblocks + kb + 1];
         }
-        if (!warp_wait(&part_full[buf], buf_phase)) {
+        const long long tf0 = PROF ? clock64() : 0;
+        if (!(p.spin ? warp_wait_fast<true>(&part_full[buf], (step >> 1) & 1) : warp_wait_fast<false>(&part_full[buf], (step >> 1) & 1))) {
           report(0x700 | buf);
           alive = false;
           break;
         }
+        const long long tf1 = PROF ? clock64() : 0;
         ptx::tc_fence_after_sync();
-        const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16) + 32 * cpart;
+        if (!DBG || !(p.debug & 1)) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          // 16 columns at a time keeps the staging registers small (64 accumulators stay live); two loads in
-          // flight per wait were measured no faster: the fold is bound by TMEM read-out, 128 KB per K block
-          uint32_t v[16];
-          ptx::tmem_ld_32x32b_x16(taddr + ((c < 2) ? col0 + 16 * c : col1 + 16 * (c - 2)), v);
-          ptx::tmem_ld_wait();
-          const float f = (c < 2) ? f0 : f1;
+          for (int c = 0; c < 4; ++c) {
+            // 16 columns at a time keeps the staging registers small (the 64 accumulators stay live)
+            uint32_t v[16];
+            ptx::tmem_ld_32x32b_x16(taddr + (c >> 1) * 128 + (c & 1) * 16, v);
+            ptx::tmem_ld_wait();
+            if (!DBG || !(p.debug & 4)) {
+              const unsigned long long ff = (c < 2) ? pack2(f0, f0) : pack2(f1, f1);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) acc[16 * c + i] = fmaf(__uint_as_float(v[i]), f, acc[16 * c + i]);
+              for (int i = 0; i < 8; ++i) fma2(acc[8 * c + i], v[2 * i], v[2 * i + 1], ff);
+            }
+          }
         }
         // 512 separate arrivals on one barrier word would serialise for longer than the fold itself:
         // the warp's lanes order their TMEM reads, then one lane arrives for all of them
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&part_empty[buf]);
+        if (PROF) {
+          prof_fw += tf1 - tf0;
+          prof_fb += clock64() - tf1;
+        }
       }
       if (!alive) break;
+      // this warp has read the tile's last staged scale
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&scale_empty[tb]);
 
+      const long long te0 = PROF ? clock64() : 0;
+      const bool valid = slot >= 0 && slot < p.numel;
+      const float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
       if constexpr (GATED) {
-        // acc[0..31] gate, acc[32..63] up -> output columns n_tile*128 + 32*cpart + [0,32)
-        if (in_cap) {
+        // acc[0..15] gate, acc[16..31] up -> output columns n_tile*128 + 32*cpart + [0,32)
+        if (pos < p.sorted_cap) {
           __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + pos * p.n + (int64_t)n_tile * 128 + 32 * cpart;
           uint4* dst = reinterpret_cast<uint4*>(orow);
 #pragma unroll
@@ -281,32 +344,109 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
             uint32_t w[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const int i = v * 8 + j * 2;
-              w[j] = pack_bf16x2(act_mul_fast(acc[i] * rs, acc[32 + i] * rs, p.activation),
-                                 act_mul_fast(acc[i + 1] * rs, acc[32 + i + 1] * rs, p.activation));
+              float g0, g1, u0, u1;
+              unpack2(acc[v * 4 + j], g0, g1);
+              unpack2(acc[16 + v * 4 + j], u0, u1);
+              w[j] = pack_bf16x2(act_mul_fast(g0 * rs, u0 * rs, p.activation), act_mul_fast(g1 * rs, u1 * rs, p.activation));
             }
             dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       } else {
-        const int64_t colg = (int64_t)n_tile * 256 + 64 * cpart;
+        // acc[0..15]: columns n0 + 32*cpart + [0,32); acc[16..31]: columns n0 + 128 + 32*cpart + [0,32)
         __nv_bfloat16* obase = !valid ? nullptr
                                : p.out_rows ? reinterpret_cast<__nv_bfloat16*>(p.out_rows[slot])
                                             : reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)slot * p.n;
-        if (obase && colg < p.n) {
-          uint4* dst = reinterpret_cast<uint4*>(obase + colg);
 #pragma unroll
-          for (int v = 0; v < 8; ++v) {
-            uint32_t w[4];
+        for (int h = 0; h < 2; ++h) {
+          const int64_t colg = (int64_t)n_tile * 256 + 128 * h + 32 * cpart;
+          if (obase && colg < p.n) {
+            uint4* dst = reinterpret_cast<uint4*>(obase + colg);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int i = v * 8 + j * 2;
-              w[j] = pack_bf16x2(acc[i] * rs, acc[i + 1] * rs);
+            for (int v = 0; v < 4; ++v) {
+              uint32_t w[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float a0, a1;
+                unpack2(acc[16 * h + v * 4 + j], a0, a1);
+                w[j] = pack_bf16x2(a0 * rs, a1 * rs);
+              }
+              dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
             }
-            dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
           }
         }
       }
+      if (PROF) prof_epi += clock64() - te0;
+    }
+    if (PROF && threadIdx.x == 0 && blockIdx.x < 256) {
+      long long* out = g_wait_prof_fp8 + (GATED ? 2048 : 0) + blockIdx.x * 8;
+      out[0] = ltile;
+      out[1] = prof_fw;
+      out[2] = prof_fb;
+      out[3] = prof_sw;
+      out[4] = prof_epi;
+    }
+  } else {
+    // ---------------- scale stagers (warps 18-19): 64 rows each, one tile ahead of the fold ----------------
+    TileCursor cursor;
+    const int half = warp - (kEpiWarps + 2);
+    const int64_t sblocks_per_expert = p.w_rows / 128;
+    uint32_t ltile = 0;
+    bool alive = true;
+    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++ltile) {
+      const int tb = (int)(ltile & 1);
+      int m_blk, n_tile, e;
+      cursor.locate(tile, p.n_tiles, p.group_m, p.num_experts, p.expert_ids, expert_table, &m_blk, &n_tile, &e);
+      if (!warp_wait(&scale_empty[tb], ((ltile >> 1) & 1) ^ 1)) {
+        report(0x780 | tb);
+        alive = false;
+        break;
+      }
+      float* s_a = reinterpret_cast<float*>(scale_base + tb * scale_buf_bytes(kblocks));
+      float* s_w = s_a + BM * kblocks;
+      // activation scales: lane = row (conflict-free transposed stores), 16 bytes of K blocks per load,
+      // four loads in flight per lane
+      for (int rr = 0; rr < 64; rr += 32) {
+        const int r = half * 64 + rr + lane;
+        const int64_t pos = (int64_t)m_blk * BM + r;
+        const bool in_cap = pos < p.sorted_cap;
+        const float* srow = p.a_scale + (in_cap ? pos : 0) * kblocks;
+        if ((kblocks & 3) != 0 || !aligned16(p.a_scale)) {  // rows that are not whole 16-byte pieces: scalar loads
+          for (int j = 0; j < kblocks; ++j) s_a[j * BM + r] = in_cap ? __ldg(srow + j) : 0.f;
+          continue;
+        }
+        const float4* src = reinterpret_cast<const float4*>(srow);
+        const int nvec = kblocks / 4;
+        for (int j0 = 0; j0 < nvec; j0 += 4) {
+          float4 v[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            v[u] = (in_cap && j0 + u < nvec) ? __ldg(src + j0 + u) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (j0 + u < nvec) {
+              float* d = s_a + (4 * (j0 + u)) * BM + r;
+              d[0] = v[u].x;
+              d[BM] = v[u].y;
+              d[2 * BM] = v[u].z;
+              d[3 * BM] = v[u].w;
+            }
+          }
+        }
+      }
+      // weight scales: stager `half` copies row `half` (gate / up, or the tile's first / second 128 columns)
+      const int64_t blk = GATED ? (half == 0 ? (int64_t)n_tile : p.n / 128 + n_tile)
+                                : min(2 * (int64_t)n_tile + half, sblocks_per_expert - 1);
+      const float* wsrc = p.w_scale + ((int64_t)e * sblocks_per_expert + blk) * kblocks;
+      for (int j = lane; j < kblocks; j += 32) s_w[half * kblocks + j] = __ldg(wsrc + j);
+      if (half == 0 && lane == 0) {
+        int32_t* meta = reinterpret_cast<int32_t*>(s_w + 2 * kblocks);
+        meta[0] = m_blk;
+        meta[1] = n_tile;
+        meta[2] = e;
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&scale_full[tb]);
     }
   }
 
@@ -317,11 +457,9 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     ptx::tc_fence_after_sync();
     ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (PROF && threadIdx.x == 0 && blockIdx.x < 256)
+    g_wait_prof_fp8[(GATED ? 2048 : 0) + blockIdx.x * 8 + 5] = clock64() - t_kernel0;
 }
-
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 }  // namespace
 
@@ -332,15 +470,18 @@ int device_sm_count();
 
 namespace {
 
-template <bool GATED>
+template <bool GATED, int MODE>
 int launch(const GemmParams& g, cudaStream_t st) {
+  constexpr int MAX_SMEM = smem_bytes(kMaxStagedKBlocks, 1024);
+  static_assert(MAX_SMEM <= 227 * 1024, "scale buffers do not fit beside the ring");
   static PerDeviceOnce once_attr;  // the opt-in to > 48 KB of dynamic shared memory is per device
   const cudaError_t attr_err = per_device_once(once_attr, [] {
-    return cudaFuncSetAttribute(grouped_gemm_tcgen05_fp8_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                SMEM_BYTES);
+    return cudaFuncSetAttribute(grouped_gemm_tcgen05_fp8_kernel<GATED, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                MAX_SMEM);
   });
   if (attr_err != cudaSuccess)
-    return fail(FMOE_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", SMEM_BYTES, cudaGetErrorString(attr_err));
+    return fail(FMOE_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", MAX_SMEM, cudaGetErrorString(attr_err));
+  const int SMEM_BYTES = smem_bytes((int)(g.k / 128), g.num_experts);
   const int64_t w_rows = GATED ? 2 * g.n : g.n;
   CUtensorMap map_a, map_b;
   int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 1, BM, false, 128);
@@ -365,12 +506,14 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.n_tiles = (int)ceil_div<int64_t>(g.n, GATED ? 128 : 256);
   p.max_blocks = (int)g.max_blocks;
   p.activation = g.activation;
+  p.spin = getenv("FMOE_FP8_SPIN") ? atoi(getenv("FMOE_FP8_SPIN")) : 0;
+  p.debug = (MODE == 2 && getenv("FMOE_FP8_DEBUG")) ? atoi(getenv("FMOE_FP8_DEBUG")) : 0;
 
   const int64_t max_tiles = g.max_blocks * p.n_tiles;
   const int sms = device_sm_count();
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sms > 0 ? sms : 148, max_tiles));
   p.group_m = pick_group_m(BM, g.k);
-  grouped_gemm_tcgen05_fp8_kernel<GATED><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
+  grouped_gemm_tcgen05_fp8_kernel<GATED, MODE><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_fp8_kernel");
 }
 
@@ -381,11 +524,17 @@ bool gemm_tcgen05_fp8_supports(const GemmParams& p, bool gated) {
   if (p.bias || p.activation == FMOE_ACT_SWIGLU_OAI) return false;  // bf16-only variant
   if (p.block_size != BM || p.a_gather) return false;
   if (p.k <= 0 || p.k % 128 != 0 || p.n <= 0 || p.n % 128 != 0) return false;
+  if (p.k / 128 > kMaxStagedKBlocks) return false;  // a tile's block scales are staged in shared memory beside the ring
   if (!p.a_scale || !p.w_scale) return false;
   if (!aligned16(p.a) || !aligned16(p.w) || !(aligned16(p.out) && (p.out || (!gated && p.out_rows)))) return false;
   if ((int64_t)p.num_experts * (gated ? 2 * p.n : p.n) >= (1ll << 31) || p.a_rows >= (1ll << 31)) return false;
-  if (p.max_blocks >= (1ll << 24)) return false;
+  if (p.max_blocks >= (1ll << 24) || p.num_experts > 1024) return false;
   return true;
+}
+
+int read_wait_profile_fp8(long long* host_out, int n) {
+  FMOE_CUDA_OK(cudaMemcpyFromSymbol(host_out, g_wait_prof_fp8, sizeof(long long) * (size_t)n));
+  return FMOE_OK;
 }
 
 int status_word_fp8(int* out, bool clear) {
@@ -398,9 +547,13 @@ int status_word_fp8(int* out, bool clear) {
 int gemm_tcgen05_fp8(const GemmParams& p, bool gated, cudaStream_t st) {
   if (!gemm_tcgen05_fp8_supports(p, gated))
     return fail(FMOE_ERR_UNSUPPORTED,
-                "tcgen05 fp8 gemm: needs e4m3 in, bf16 out, block_size 128, sorted input rows, n and k multiples of 128");
+                "tcgen05 fp8 gemm: needs e4m3 in, bf16 out, block_size 128, sorted input rows, n a multiple of 128, "
+                "k a multiple of 128 up to 8192");
   if (p.max_blocks <= 0) return FMOE_OK;
-  return gated ? launch<true>(p, st) : launch<false>(p, st);
+  static const int mode = getenv("FMOE_FP8_DEBUG") ? 2 : (getenv("FMOE_TC_PROFILE") ? 1 : 0);
+  if (mode == 2) return gated ? launch<true, 2>(p, st) : launch<false, 2>(p, st);
+  if (mode == 1) return gated ? launch<true, 1>(p, st) : launch<false, 1>(p, st);
+  return gated ? launch<true, 0>(p, st) : launch<false, 0>(p, st);
 }
 
 }  // namespace fmoe

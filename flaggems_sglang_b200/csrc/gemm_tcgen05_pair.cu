@@ -20,12 +20,16 @@
 #include "gemm.cuh"
 #include "ptx_sm100.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace fmoe {
 
 // This translation unit's status word (device code is not linked across files); read by status_word_pair().
 __device__ int g_device_status_pair = 0;
+// Optional wait-time profile (FMOE_TC_PROFILE=1), same columns as the single-CTA kernel's: per CTA
+// {tiles, mma wait acc, mma wait data, producer wait, epilogue wait, epilogue busy, -, -}
+__device__ long long g_wait_prof_pair[256 * 8];
 int make_tensor_map_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t cols, int elem_bytes, int box_rows,
                        bool weights, int kbytes);
 int device_sm_count();
@@ -60,6 +64,8 @@ struct PairParams {
   int32_t max_blocks;  // blocks of 256 rows
   int32_t activation;
   int32_t group_m;
+  int32_t profile;
+  int32_t debug;  // timing experiment only (results are wrong): 1 = no TMA loads, the MMA warp never waits for data
 };
 
 __device__ __forceinline__ void report(int code) { atomicCAS(&g_device_status_pair, 0, code); }
@@ -83,6 +89,7 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
   uint64_t* acc_full = bars + 2 * STAGES;         // [2] per CTA: MMA -> this CTA's epilogue
   uint64_t* acc_empty = bars + 2 * STAGES + 2;    // [2] used in CTA 0: both epilogues -> MMA
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  int32_t* expert_table = reinterpret_cast<int32_t*>(smem + STAGES * STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
@@ -108,14 +115,14 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
     ptx::tmem_alloc_pair(tmem_slot, TMEM_COLS);
     ptx::tmem_relinquish_pair();
   }
+  const int used_blocks = min((int)(*p.num_tokens_post_padded / PAIR_M), p.max_blocks);
+  const int64_t total_tiles = (int64_t)used_blocks * p.n_tiles;
   ptx::tc_fence_before_sync();
-  __syncthreads();
+  build_expert_table(expert_table, p.num_experts, p.expert_ids, used_blocks);  // ends with __syncthreads()
   ptx::cluster_sync_all();  // the other CTA's barriers exist before anything is signalled across
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int used_blocks = min((int)(*p.num_tokens_post_padded / PAIR_M), p.max_blocks);
-  const int64_t total_tiles = (int64_t)used_blocks * p.n_tiles;
   TileCursor cursor;
   const int k_steps = p.k_steps;
 
@@ -124,20 +131,23 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
     int stage = 0;
     uint32_t phase = 0;
     bool alive = true;
+    long long prof_p = 0;
     auto tile_rows = [&](int64_t tile, int32_t* row_a, int32_t* row_b) {
-      int m_blk, n_tile;
-      cursor.locate(tile, used_blocks, p.n_tiles, p.group_m, p.expert_ids, &m_blk, &n_tile);
-      const int e = min(max(p.expert_ids[m_blk], 0), p.num_experts - 1);
+      int m_blk, n_tile, e;
+      cursor.locate(tile, p.n_tiles, p.group_m, p.num_experts, p.expert_ids, expert_table, &m_blk, &n_tile, &e);
       *row_a = m_blk * PAIR_M + (int)rank * BM;
       const int64_t b0 = (int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256);
       *row_b = (int32_t)(leader ? b0 : (GATED ? b0 + p.n : b0 + 128));
     };
     int32_t row_a = 0, row_b = 0, nrow_a = 0, nrow_b = 0;
     if ((int64_t)cluster_id < total_tiles) tile_rows(cluster_id, &row_a, &row_b);
-    for (int64_t tile = cluster_id; tile < total_tiles && alive; tile += num_clusters) {
+    for (int64_t tile = cluster_id; tile < total_tiles && alive && p.debug != 1; tile += num_clusters) {
       const bool has_next = tile + num_clusters < total_tiles;
       for (int ks = 0; ks < k_steps; ++ks) {
-        if (!warp_wait(&empty_bar[stage], phase ^ 1)) {
+        const long long tp0 = p.profile ? clock64() : 0;
+        const bool okp = warp_wait(&empty_bar[stage], phase ^ 1);
+        if (p.profile) prof_p += clock64() - tp0;
+        if (!okp) {
           report(0x900 | stage);
           alive = false;
           break;
@@ -161,7 +171,8 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
       row_a = nrow_a;
       row_b = nrow_b;
     }
-    if (alive) {  // drain: every stage this CTA filled has been consumed
+    if (p.profile && lane == 0 && blockIdx.x < 256) g_wait_prof_pair[blockIdx.x * 8 + 3] = prof_p;
+    if (alive && p.debug != 1) {  // drain: every stage this CTA filled has been consumed
       for (int s = 0; s < STAGES; ++s) {
         if (!warp_wait(&empty_bar[stage], phase ^ 1)) {
           report(0x980 | stage);
@@ -181,11 +192,15 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
       uint32_t phase = 0;
       int local = 0;
       bool alive = true;
+      long long prof_acc = 0, prof_data = 0;
       for (int64_t tile = cluster_id; tile < total_tiles && alive; tile += num_clusters) {
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         ++local;
-        if (!warp_wait(&acc_empty[acc], acc_phase ^ 1)) {
+        const long long tm0 = p.profile ? clock64() : 0;
+        const bool oka = warp_wait(&acc_empty[acc], acc_phase ^ 1);
+        if (p.profile) prof_acc += clock64() - tm0;
+        if (!oka) {
           report(0xA00 | acc);
           alive = false;
           break;
@@ -193,7 +208,10 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int ks = 0; ks < k_steps; ++ks) {
-          if (!warp_wait(&full_bar[stage], phase)) {
+          const long long tm1 = p.profile ? clock64() : 0;
+          const bool okd = p.debug == 1 ? true : warp_wait(&full_bar[stage], phase);
+          if (p.profile) prof_data += clock64() - tm1;
+          if (!okd) {
             report(0xA40 | stage);
             alive = false;
             break;
@@ -208,8 +226,10 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
               ptx::mma_f16_ss_pair(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (ks | kk) != 0);
             // the stage is free in both CTAs once these MMAs have read it
             const uint32_t eb = ptx::smem_u32(&empty_bar[stage]);
-            ptx::mma_commit_pair(eb);
-            ptx::mma_commit_pair(eb | ptx::kPeerRankBit);
+            if (p.debug != 1) {
+              ptx::mma_commit_pair(eb);
+              ptx::mma_commit_pair(eb | ptx::kPeerRankBit);
+            }
           }
           __syncwarp();
           if (++stage == STAGES) {
@@ -224,15 +244,21 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
         }
         __syncwarp();
       }
+      if (p.profile && lane == 0 && blockIdx.x < 256) {
+        g_wait_prof_pair[blockIdx.x * 8 + 0] = local;
+        g_wait_prof_pair[blockIdx.x * 8 + 1] = prof_acc;
+        g_wait_prof_pair[blockIdx.x * 8 + 2] = prof_data;
+      }
     }
   } else {
     // ---------------- epilogue (warps 0-3, both CTAs, own 128 rows) ----------------
     int local = 0;
     bool alive = true;
+    long long prof_wait = 0, prof_busy = 0;
     const int row = warp * 32 + lane;
     for (int64_t tile = cluster_id; tile < total_tiles && alive; tile += num_clusters) {
-      int m_blk, n_tile;
-      cursor.locate(tile, used_blocks, p.n_tiles, p.group_m, p.expert_ids, &m_blk, &n_tile);
+      int m_blk, n_tile, tile_e;
+      cursor.locate(tile, p.n_tiles, p.group_m, p.num_experts, p.expert_ids, expert_table, &m_blk, &n_tile, &tile_e);
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ++local;
@@ -240,7 +266,11 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
       const int32_t slot = (pos < p.sorted_cap) ? p.sorted_token_ids[pos] : -1;
       const bool valid = slot >= 0 && slot < p.numel;
       const float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
-      if (!warp_wait_relaxed(&acc_full[acc], acc_phase)) {
+      const long long te0 = p.profile ? clock64() : 0;
+      const bool oke = warp_wait_relaxed(&acc_full[acc], acc_phase);
+      const long long te1 = p.profile ? clock64() : 0;
+      prof_wait += te1 - te0;
+      if (!oke) {
         report(0xB00 | acc);
         alive = false;
         break;
@@ -297,6 +327,11 @@ grouped_gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, cons
       // this thread is done with the accumulator: tell CTA 0's MMA warp
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive_cluster(ptx::smem_u32(&acc_empty[acc]) & ~ptx::kPeerRankBit);
+      if (p.profile) prof_busy += clock64() - te1;
+    }
+    if (p.profile && threadIdx.x == 0 && blockIdx.x < 256) {
+      g_wait_prof_pair[blockIdx.x * 8 + 4] = prof_wait;
+      g_wait_prof_pair[blockIdx.x * 8 + 5] = prof_busy;
     }
   }
 
@@ -314,7 +349,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
   static PerDeviceOnce once_attr;  // the opt-in to > 48 KB of dynamic shared memory is per device
   const cudaError_t attr_err = per_device_once(once_attr, [] {
     return cudaFuncSetAttribute(grouped_gemm_tcgen05_pair_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                SMEM_BYTES);
+                                SMEM_BYTES + expert_table_bytes(1024));
   });
   if (attr_err != cudaSuccess)
     return fail(FMOE_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", SMEM_BYTES, cudaGetErrorString(attr_err));
@@ -344,7 +379,10 @@ int launch(const GemmParams& g, cudaStream_t st) {
   const int sms = device_sm_count();
   const int64_t pairs = std::max<int64_t>(1, std::min<int64_t>((sms > 0 ? sms : 148) / 2, max_tiles));
   p.group_m = pick_group_m(PAIR_M, g.k * 2);
-  grouped_gemm_tcgen05_pair_kernel<GATED><<<(unsigned)(2 * pairs), kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
+  p.profile = getenv("FMOE_TC_PROFILE") != nullptr;
+  p.debug = getenv("FMOE_TC_DEBUG") ? atoi(getenv("FMOE_TC_DEBUG")) : 0;
+  grouped_gemm_tcgen05_pair_kernel<GATED><<<(unsigned)(2 * pairs), kThreads, SMEM_BYTES + expert_table_bytes(g.num_experts), st>>>(
+      map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_pair_kernel");
 }
 
@@ -358,8 +396,13 @@ bool gemm_tcgen05_pair_supports(const GemmParams& p, bool gated) {
   if (p.n <= 0 || p.n % (gated ? 128 : 32) != 0) return false;
   if (!aligned16(p.a) || !aligned16(p.w) || !aligned16(p.out)) return false;
   if ((int64_t)p.num_experts * (gated ? 2 * p.n : p.n) >= (1ll << 31) || p.a_rows >= (1ll << 31)) return false;
-  if (p.max_blocks >= (1ll << 23)) return false;
+  if (p.max_blocks >= (1ll << 23) || p.num_experts > 1024) return false;
   return true;
+}
+
+int read_wait_profile_pair(long long* host_out, int n) {
+  FMOE_CUDA_OK(cudaMemcpyFromSymbol(host_out, g_wait_prof_pair, sizeof(long long) * (size_t)n));
+  return FMOE_OK;
 }
 
 int status_word_pair(int* out, bool clear) {

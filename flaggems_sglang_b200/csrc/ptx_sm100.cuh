@@ -53,6 +53,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return mbar_wait_limit(bar, parity, kWaitCycles);
 }
 
+// Non-suspending poll (mbarrier.test_wait): for waits that sit on a kernel's critical path and are short, where the
+// wake-up time of a suspended try_wait would be paid on every hand-over.  Bounded like the others.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  int polls = 0;
+  while (true) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if ((++polls & 1023) == 0 && clock64() - t0 > kWaitCycles) return false;
+  }
+}
+
 // Same, for waits that are expected to last long (an epilogue warp waiting for a whole main loop): sleeps
 // between polls so that the barrier word is not hammered while the MMA and TMA units use shared memory.
 __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity) {
@@ -71,6 +94,26 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+// L2 eviction-priority policies for the loads below: weight tiles are streamed once (by the few CTAs that share
+// them at that moment) and should leave L2 first; activation rows are re-read by every column tile and should stay.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+// 2-D tiled TMA load with an L2 cache policy.
+__device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y,
+                                                 uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "l"(policy)
       : "memory");
 }
 // TMA gather: four rows (y0..y3, any order, repeats allowed) of a 2-D tensor whose map has a one-row box

@@ -363,6 +363,11 @@ int fmoe_debug_stage_events(void* const* events, int n);
  * 256 CTAs) to HOST memory.  No counterpart in the reference.
  */
 int fmoe_debug_tcgen05_wait_profile(int64_t* host_out, int n);
+/* Same for the kernel family `variant`: FMOE_VARIANT_TCGEN05 (bf16), FMOE_VARIANT_TCGEN05_PAIR, or -FMOE_VARIANT_TCGEN05
+ * for the e4m3 kernel, whose columns are {tiles, MMA waits for a TMEM partial, MMA waits for data, producer waits,
+ * fold waits, fold busy, kernel cycles, epilogue cycles}: 256 x 8 values of the last down GEMM, then 256 x 8 of the
+ * last gate/up GEMM (n up to 4096). */
+int fmoe_debug_wait_profile(int variant, int64_t* host_out, int n);
 
 #ifdef __cplusplus
 }

@@ -595,6 +595,13 @@ def main():
         return
 
     rank, world, local = dist_env()
+    # a rank that blocks (a collective a peer never joins) ends the run with a Python traceback of every thread
+    # instead of holding the GPUs until an outer limit: FMOE_BENCH_WATCHDOG seconds (default 780 for N > 1)
+    watchdog = int(os.environ.get("FMOE_BENCH_WATCHDOG", "780" if world > 1 else "0"))
+    if watchdog > 0:
+        import faulthandler
+
+        faulthandler.dump_traceback_later(watchdog, exit=True)
     if world > 1:
         from flaggems_sglang_b200 import ep_bench
 

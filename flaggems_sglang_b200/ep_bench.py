@@ -55,22 +55,22 @@ def _make_step(ep, cfg, wts, tok, xc):
     return step
 
 
-def _parity_rank0(cfg, tok, out, rank, n=64):
-    """Rank 0: the single-GPU operator on the FULL layer (all experts, built here for the check) on the first
-    tokens of this rank's batch, against the expert-parallel output.  Outside every timed region."""
+def _parity_rank0(cfg, tok, out, rank):
+    """Rank 0: the single-GPU operator on the FULL layer (all experts, built here for the check) on this rank's
+    whole batch, so that both sides pick the same kernel family, against the expert-parallel output.  Outside
+    every timed region; the other ranks wait in the barrier."""
     res = None
     if rank == 0:
         import flaggems_sglang_b200 as fg
         from . import workloads as W
 
-        n = min(n, out.shape[0])
         full = W.make_weights(cfg, out.device, seed=0)
-        ref = fg.fused_moe(tok["hidden"][:n], full["w1"], full["w2"], tok["logits"][:n], cfg.top_k, True,
+        ref = fg.fused_moe(tok["hidden"], full["w1"], full["w2"], tok["logits"], cfg.top_k, True,
                            use_grouped_topk=cfg.router == "grouped", num_expert_group=cfg.n_group,
                            topk_group=cfg.topk_group, correction_bias=tok.get("correction_bias"),
                            routed_scaling_factor=cfg.routed_scaling_factor, **_layer_kwargs(cfg, full)).float()
-        got = out[:n].float()
-        res = {"tokens": n, "against": "single-GPU fused_moe on the full layer, same tokens",
+        got = out.float()
+        res = {"tokens": int(out.shape[0]), "against": "single-GPU fused_moe on the full layer, same tokens",
                "rel_l2": float((got - ref).norm() / ref.norm()),
                "max_abs_frac": float((got - ref).abs().max() / ref.abs().max()), "bit_equal": bool(torch.equal(got, ref))}
         del full
@@ -101,7 +101,7 @@ def c5_block(args, rank, world, dev):
     e_local = cfg.E // world
     wts = W.make_weights(cfg, dev, seed=0, num_experts=e_local, expert_offset=rank * e_local)
     steps = max(5, args.steps // 2)
-    points, parity = [], None
+    points, parity, parity_done = [], None, False
     for T in (128, 4096):
         for mode in ("p2p", "nccl"):
             xc, used = _exchange(ep, mode, T, cfg, torch.bfloat16, rank)
@@ -111,8 +111,9 @@ def c5_block(args, rank, world, dev):
                 ms = _timed(step, steps, 3, dev)
                 points.append({"T_local": T, "routing": "zipf-1.2" if skew else "uniform", "exchange": used,
                                "ms": round(ms, 4), "tokens_per_s": round(world * T / (ms * 1e-3), 1)})
-                if parity is None and T == 4096 and not skew:
+                if not parity_done and T == 4096 and not skew:  # once, on every rank (only rank 0 gets a result)
                     parity = _parity_rank0(cfg, tok, step(), rank)
+                    parity_done = True
             if xc is not None:
                 xc.close()
     del wts

@@ -101,13 +101,13 @@ SIGNATURES = {
     "fmoe_ep_buffer_open": (c_int, [c_void_p, POINTER(c_void_p)]),
     "fmoe_ep_buffer_close": (c_int, [c_void_p]),
     "fmoe_ep_buffer_destroy": (c_int, [c_void_p]),
-    "fmoe_ep_route": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
-    "fmoe_ep_dispatch": (c_int, [c_void_p, c_int, c_int64, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                 c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
-    "fmoe_ep_mask_tail": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_int64, c_void_p, c_int64,
-                                  c_void_p, c_void_p]),
-    "fmoe_ep_combine": (c_int, [c_void_p, c_int, c_int64, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
-                                c_void_p, c_void_p]),
+    "fmoe_ep_expert_counts": (c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
+    "fmoe_ep_dispatch_sorted": (c_int, [c_void_p, c_int64, c_void_p, c_int, c_int64, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_int64, c_void_p, c_int64, c_void_p]),
+    "fmoe_ep_recv_tables": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64, c_void_p, c_int64, c_void_p,
+                                    c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p]),
+    "fmoe_ep_scatter_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p]),
     "fmoe_selftest_bounded_wait": (c_int, [c_int64, c_void_p]),
     "fmoe_debug_tcgen05_wait_profile": (c_int, [c_void_p, c_int]),
     "fmoe_debug_stage_events": (c_int, [c_void_p, c_int]),

@@ -14,10 +14,12 @@ Per layer call, every rank
   5. combine: all-to-all of the result rows back, un-permute to slot order, sum the k slots.
 Two exchanges are built.  The default one is NCCL all-to-all (steps 3 and 5 as library calls; it needs the split
 sizes on the host, i.e. one device-to-host read per call).  With a `PeerExchange` (receive areas that the peers
-map through CUDA IPC) steps 2-5 run without any host read: this package's kernels store the rows straight into
-the destination rank's receive area and the expert outputs straight into the source rank's slot buffer over
-NVLink, and the only library calls left are a tiny count all-gather and two barriers that order the phases.
-Those kernels never wait on a peer and never read peer memory.
+map through CUDA IPC) steps 2-5 run without any host read: the ranks all-gather their per-expert row counts, and
+this package's kernels store every row straight into the owner's receive area AT ITS PLACE IN THE PADDED
+EXPERT-SORTED ORDER the grouped GEMMs read (for e4m3 layers as e4m3 bytes + scales, quantised once by the
+sender), so the receiver runs neither moe_align, nor a row copy, nor a quantisation pass; the expert outputs go
+straight into the source rank's slot buffer over NVLink, and the only library calls left are the count
+all-gather and two barriers that order the phases.  Those kernels never wait on a peer and never read peer memory.
 
 The data movement is written against a small backend interface so that the exchange logic runs
 unchanged on CPU ranks (gloo) in the tests, where the backend is the CPU oracle.
@@ -135,14 +137,21 @@ def _up256(n: int) -> int:
 class PeerExchange:
     """Receive areas of one process group for the P2P exchange (see fmoe_ep_* in include/fmoe_b200.h).
 
-    Created collectively (every rank of `group`, same arguments).  `capacity` = rows this rank can receive per
-    call; the default world * max_tokens * top_k can never overflow, a smaller value saves memory and an
-    overflow is then reported by `_C.check_device_status` (rows beyond it are dropped, nothing is overwritten).
+    Created collectively (every rank of `group`, same arguments) for one layer shape: `num_local_experts` experts
+    per rank with intermediate size `intermediate_size`; `fp8=True` for e4m3 weights (token rows then travel as
+    e4m3 bytes + 128-channel scales, quantised once by the sender).  Rows arrive in the padded expert-sorted order
+    of the grouped GEMMs, so the kernel family and its row block are fixed here, from `max_tokens * top_k` slots
+    per rank (`variant=` overrides the choice).
+
+    `capacity` = rows this rank can receive per call; the default world * max_tokens * top_k (+ block padding per
+    expert) can never overflow, a smaller value saves memory and an overflow is then reported by
+    `_C.check_device_status` (rows beyond it are dropped, their result rows read as zero, nothing is overwritten).
     One instance serves one layer call at a time (calls on it must be stream-ordered).
     """
 
     def __init__(self, group, max_tokens: int, top_k: int, hidden_size: int, dtype=torch.bfloat16,
-                 capacity: Optional[int] = None, device=None, _lib=None):
+                 capacity: Optional[int] = None, device=None, _lib=None, num_local_experts: int = 1,
+                 intermediate_size: int = 128, fp8: bool = False, variant: Optional[str] = None):
         """`_lib`: stand-in for the C library (tests inject allocation / mapping failures on chosen ranks)."""
         import ctypes
 
@@ -152,7 +161,7 @@ class PeerExchange:
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
-        self._layout(max_tokens, top_k, hidden_size, dtype, capacity)
+        self._layout(max_tokens, top_k, hidden_size, dtype, capacity, num_local_experts, intermediate_size, fp8, variant)
         lib = self._lib = _lib if _lib is not None else _C.lib()
         base = ctypes.c_void_p()
         handle = (ctypes.c_ubyte * 64)()
@@ -196,13 +205,22 @@ class PeerExchange:
             agree(problem, "mapping the peers' receive areas (CUDA IPC)")
         self._bind(bases, torch.as_tensor(_DeviceBytes(base.value, self.nbytes), device=self.device))
         self._flag = torch.zeros(1, dtype=torch.float32, device=self.device)
-        self.ids.fill_(-1)
+        self._bytes.zero_()  # padding rows of the area are read by the GEMMs (and ignored): keep them finite
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)
 
     # -- shared with the single-process emulation used by the tests -------------------------------------
-    def _layout(self, max_tokens, top_k, hidden_size, dtype, capacity):
+    def _layout(self, max_tokens, top_k, hidden_size, dtype, capacity, num_local_experts, intermediate_size, fp8,
+                variant):
+        from .ops.fused_moe import _pick_variant
+
         self.max_tokens, self.top_k, self.H, self.dtype = int(max_tokens), int(top_k), int(hidden_size), dtype
+        self.e_local, self.I, self.fp8 = int(num_local_experts), int(intermediate_size), bool(fp8)
+        self.total_experts = self.e_local * self.world
+        # kernel family and row block of the expert computation, the same on every rank (the senders lay the rows out)
+        wdt = torch.float8_e4m3fn if fp8 else dtype
+        self.variant, self.block = _pick_variant(wdt, max(self.max_tokens * self.top_k, 1), self.e_local, self.I,
+                                                 self.H, variant)
         # Result rows go back either from inside the down-projection kernel (its epilogue stores to the peer) or by a
         # separate copy kernel.  None = by kernel family: the bf16 tcgen05 kernel has dedicated epilogue warps, so the
         # slower peer stores overlap the next tile (measured 2.50 against 2.55 ms, Mixtral, 2 GPUs); in the fp8
@@ -211,13 +229,17 @@ class PeerExchange:
         env = os.environ.get("FMOE_EP_FUSE_RETURN")
         self.fuse_return = None if env is None else env != "0"
         eb = torch.empty(0, dtype=dtype).element_size()
-        if (self.H * eb) % 16:
-            raise ValueError("hidden rows must be a multiple of 16 bytes")
+        if (self.H * eb) % 16 or (fp8 and self.H % 128):
+            raise ValueError("hidden rows must be a multiple of 16 bytes (128 channels for e4m3)")
+        self.row_bytes = self.H if fp8 else self.H * eb
         self.z_slots = self.max_tokens * self.top_k
-        self.capacity = int(capacity) if capacity is not None else self.world * self.z_slots
+        worst = self.world * self.z_slots + self.e_local * (self.block - 1)
+        cap = int(capacity) if capacity is not None else worst
+        self.capacity = (cap + self.block - 1) // self.block * self.block
         off = 0
         self._off = {}
-        for name, nbytes in (("rows", self.capacity * self.H * eb), ("ids", self.capacity * 4),
+        for name, nbytes in (("rows", self.capacity * self.row_bytes),
+                             ("scales", self.capacity * (self.H // 128) * 4 if fp8 else 0),
                              ("weights", self.capacity * 4), ("src", self.capacity * 8),
                              ("z", self.z_slots * self.H * eb)):
             self._off[name] = (off, nbytes)
@@ -226,22 +248,38 @@ class PeerExchange:
 
     def _bind(self, bases, own_bytes: torch.Tensor):
         self._bytes = own_bytes
+        dev = self.device
 
         def own(name, dt, shape):
             o, n = self._off[name]
             return own_bytes[o:o + n].view(dt).view(shape)
 
-        self.rows = own("rows", self.dtype, (self.capacity, self.H))
-        self.ids = own("ids", torch.int32, (self.capacity,))
+        self.rows = own("rows", torch.float8_e4m3fn if self.fp8 else self.dtype, (self.capacity, self.H))
+        self.scales = own("scales", torch.float32, (self.capacity, self.H // 128)) if self.fp8 else None
         self.weights = own("weights", torch.float32, (self.capacity,))
         self.src = own("src", torch.int32, (self.capacity, 2))
         self.z = own("z", self.dtype, (self.z_slots, self.H))
-        self.ptrs = {name: torch.tensor([b + self._off[name][0] for b in bases], dtype=torch.int64, device=self.device)
+        self.ptrs = {name: torch.tensor([b + self._off[name][0] for b in bases], dtype=torch.int64, device=dev)
                      for name in self._off}
+        # local tables and intermediates of the expert computation (never written by a peer)
+        cap, blk = self.capacity, self.block
+        self.sorted_ids = torch.empty(cap, dtype=torch.int32, device=dev)
+        self.expert_ids = torch.empty(cap // blk, dtype=torch.int32, device=dev)
+        self.npp = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.out_rows = torch.zeros(cap, dtype=torch.int64, device=dev)
+        tc = self.variant.startswith("tcgen05")
+        if self.fp8:
+            self.act = torch.empty(cap, self.I, dtype=torch.bfloat16 if tc else torch.float32, device=dev)
+            self.actq = torch.empty(cap, self.I, dtype=torch.float8_e4m3fn, device=dev)
+            self.act_scale = torch.empty(cap, self.I // 128, dtype=torch.float32, device=dev)
+        else:
+            self.act = torch.empty(cap, self.I, dtype=self.dtype, device=dev)
+        self._z_local = None  # [capacity, H], allocated on first use of the separate return
 
     @classmethod
     def emulated(cls, world: int, max_tokens: int, top_k: int, hidden_size: int, dtype=torch.bfloat16,
-                 capacity: Optional[int] = None, device="cuda"):
+                 capacity: Optional[int] = None, device="cuda", num_local_experts: int = 1,
+                 intermediate_size: int = 128, fp8: bool = False, variant: Optional[str] = None):
         """`world` exchanges living in ONE process and on one GPU, the "peers" being plain local tensors: the
         same kernels and pointer tables without IPC.  The caller runs every phase for all ranks before the next
         phase (there are no barriers to wait on)."""
@@ -249,13 +287,12 @@ class PeerExchange:
         for r in range(world):
             xc = cls.__new__(cls)
             xc.group, xc.world, xc.rank, xc.device = None, world, r, torch.device(device)
-            xc._layout(max_tokens, top_k, hidden_size, dtype, capacity)
+            xc._layout(max_tokens, top_k, hidden_size, dtype, capacity, num_local_experts, intermediate_size, fp8, variant)
             stores.append(torch.zeros(xc.nbytes, dtype=torch.uint8, device=xc.device))
             out.append(xc)
         bases = [st.data_ptr() for st in stores]
         for xc, st in zip(out, stores):
             xc._bind(bases, st)
-            xc.ids.fill_(-1)
             xc._opened, xc._own_base, xc._flag, xc._lib = [], None, None, None
         return out
 
@@ -291,65 +328,102 @@ class PeerExchange:
 
 
 def p2p_route(xc: PeerExchange, hidden_states, topk_weights, topk_ids, experts_per_rank: int) -> dict:
-    """Phase 1 (local): destination rank per (token, slot), rows per destination, destination-sorted order."""
+    """Phase 1 (local): rows per global expert, the expert-sorted order of this rank's (token, slot) pairs and,
+    for e4m3 layers, the token rows quantised once."""
     from . import _C
     from .ops.moe_align_block_size import moe_align_block_size
 
     T, H = hidden_states.shape
     k = topk_ids.shape[1]
-    if T > xc.max_tokens or k != xc.top_k or H != xc.H or hidden_states.dtype != xc.dtype:
-        raise ValueError(f"this PeerExchange was sized for <= {xc.max_tokens} tokens, top_k {xc.top_k}, H {xc.H}, {xc.dtype}")
+    if T > xc.max_tokens or k != xc.top_k or H != xc.H or hidden_states.dtype != xc.dtype or experts_per_rank != xc.e_local:
+        raise ValueError(f"this PeerExchange was sized for <= {xc.max_tokens} tokens, top_k {xc.top_k}, H {xc.H}, "
+                         f"{xc.dtype}, {xc.e_local} experts per rank")
     dev = hidden_states.device
+    lib, st = _C.lib(), _C.stream_ptr(dev)
     x = hidden_states.contiguous()
     ids = topk_ids.to(torch.int32).contiguous().view(-1)
     wts = topk_weights.to(torch.float32).contiguous().view(-1)
-    dest = torch.empty(T * k, dtype=torch.int32, device=dev)
-    counts = torch.empty(xc.world, dtype=torch.int32, device=dev)
-    _C.check(_C.lib().fmoe_ep_route(ids.data_ptr(), T * k, experts_per_rank, xc.world, dest.data_ptr(),
-                                    counts.data_ptr(), _C.stream_ptr(dev)))
-    perm, _, _ = moe_align_block_size(dest, 1, xc.world) if T > 0 else (dest, None, None)
-    return dict(x=x, ids=ids, wts=wts, perm=perm, counts=counts, T=T, k=k, e_local=experts_per_rank)
+    counts = torch.empty(xc.total_experts, dtype=torch.int32, device=dev)
+    _C.check(lib.fmoe_ep_expert_counts(ids.data_ptr(), T * k, xc.total_experts, counts.data_ptr(), st))
+    perm, _, _ = moe_align_block_size(ids, 1, xc.total_experts) if T > 0 else (ids, None, None)
+    state = dict(x=x, ids=ids, wts=wts, perm=perm, counts=counts, T=T, k=k, scales=None)
+    if xc.fp8 and T > 0:
+        xq = torch.empty(T, H, dtype=torch.float8_e4m3fn, device=dev)
+        xs = torch.empty(T, H // 128, dtype=torch.float32, device=dev)
+        _C.check(lib.fmoe_quant_fp8_group128(x.data_ptr(), _C.BF16, T, H, None, 1, 0, None, xq.data_ptr(), xs.data_ptr(), st))
+        state.update(x=xq, scales=xs)
+    return state
 
 
 def p2p_send(xc: PeerExchange, state: dict, matrix: torch.Tensor) -> None:
-    """Phase 2: store this rank's rows and their metadata into the destination ranks' receive areas."""
+    """Phase 2: store this rank's rows and their metadata into the owners' receive areas, at the positions the
+    count matrix [world * total_experts] assigns."""
     from . import _C
 
     state["matrix"] = matrix
-    x = state["x"]
-    _C.check(_C.lib().fmoe_ep_dispatch(
-        x.data_ptr(), x.element_size(), state["T"], xc.H, state["k"], state["ids"].data_ptr(), state["wts"].data_ptr(),
-        state["perm"].data_ptr(), matrix.data_ptr(), xc.rank, xc.world, state["e_local"], xc.ptrs["rows"].data_ptr(),
-        xc.ptrs["ids"].data_ptr(), xc.ptrs["weights"].data_ptr(), xc.ptrs["src"].data_ptr(), xc.capacity,
-        _C.stream_ptr(x.device)))
+    x, sc = state["x"], state["scales"]
+    _C.check(_C.lib().fmoe_ep_dispatch_sorted(
+        x.data_ptr(), xc.row_bytes, _C.ptr(sc), xc.H // 128 if sc is not None else 0, state["T"], state["k"],
+        state["ids"].data_ptr(), state["wts"].data_ptr(), state["perm"].data_ptr(), matrix.data_ptr(), xc.rank,
+        xc.world, xc.total_experts, xc.e_local, xc.block, xc.ptrs["rows"].data_ptr(),
+        xc.ptrs["scales"].data_ptr() if sc is not None else None, xc.ptrs["weights"].data_ptr(),
+        xc.ptrs["src"].data_ptr(), xc.capacity, xc.z.data_ptr(), xc.H * xc.z.element_size(), _C.stream_ptr(x.device)))
 
 
 def p2p_experts(xc: PeerExchange, state: dict, w1_local, w2_local, fuse_return: Optional[bool] = None,
-                **expert_kwargs) -> Optional[torch.Tensor]:
-    """Phase 3 (after the barrier): grouped GEMMs over the receive area; rows past the received count carry
-    id -1 and are skipped by moe_align_block_size.  With `fuse_return` (and a kernel family that takes row
-    addresses) the down-projection epilogue stores every result row straight into the slot buffer of the
-    rank the row came from, and None is returned; otherwise the rows come back for `p2p_return`.
+                activation: str = "silu", apply_router_weight_on_input: bool = False, use_fp8_w8a8: bool = False,
+                w1_scale=None, w2_scale=None, block_shape=None, variant=None) -> Optional[torch.Tensor]:
+    """Phase 3 (after the barrier): the grouped GEMMs straight over the receive area, whose rows already stand in
+    the padded expert-sorted order.  With `fuse_return` (and a kernel family that takes row addresses) the
+    down-projection epilogue stores every result row straight into the slot buffer of the rank the row came
+    from, and None is returned; otherwise the rows come back for `p2p_return`.
     `fuse_return=None` decides by kernel family (bf16: fused, fp8: separate)."""
     from . import _C
-    from .ops.fused_moe import _pick_variant, fused_experts
 
+    assert use_fp8_w8a8 == xc.fp8, "this PeerExchange was created for the other weight type"
+    assert variant in (None, xc.variant), "the kernel family is fixed when the PeerExchange is created"
+    if xc.fp8:
+        assert block_shape is not None and list(block_shape) == [128, 128] and w1_scale is not None and w2_scale is not None
+    E, twoI, H = w1_local.shape
+    assert E == xc.e_local and twoI == 2 * xc.I and H == xc.H, "local weights do not match the PeerExchange's layer shape"
     dev = xc.rows.device
-    fp8 = expert_kwargs.get("use_fp8_w8a8", False)
-    # kernel family for the rows a balanced routing would bring (this rank's own count), not for the capacity
-    name, _ = _pick_variant(torch.float8_e4m3fn if fp8 else w1_local.dtype, max(state["T"] * state["k"], 1),
-                            w1_local.shape[0], w2_local.shape[2], xc.H, expert_kwargs.get("variant"))
-    expert_kwargs = dict(expert_kwargs, variant=name)
+    lib, st = _C.lib(), _C.stream_ptr(dev)
     if fuse_return is None:
-        fuse_return = not fp8
-    fuse_return = fuse_return and name in ("stream", "tcgen05")
-    out_rows = torch.empty(xc.capacity, dtype=torch.int64, device=dev) if fuse_return else None
-    _C.check(_C.lib().fmoe_ep_mask_tail(xc.ids.data_ptr(), state["matrix"].data_ptr(), xc.rank, xc.world, xc.capacity,
-                                        xc.src.data_ptr(), xc.z_slots, xc.ptrs["z"].data_ptr(),
-                                        xc.H * xc.rows.element_size(), _C.ptr(out_rows), _C.stream_ptr(dev)))
-    z = fused_experts(xc.rows, w1_local, w2_local, xc.weights.view(-1, 1), xc.ids.view(-1, 1), no_combine=True,
-                      out_rows=out_rows, **expert_kwargs)
-    return None if fuse_return else z.view(xc.capacity, xc.H)
+        fuse_return = not xc.fp8
+    fuse_return = fuse_return and xc.variant in ("stream", "tcgen05")
+    cap, blk = xc.capacity, xc.block
+    _C.check(lib.fmoe_ep_recv_tables(state["matrix"].data_ptr(), xc.rank, xc.world, xc.total_experts, xc.e_local, blk, cap,
+                                     xc.src.data_ptr(), xc.z_slots, xc.ptrs["z"].data_ptr(), xc.H * xc.z.element_size(),
+                                     xc.sorted_ids.data_ptr(), xc.expert_ids.data_ptr(), xc.expert_ids.numel(),
+                                     xc.npp.data_ptr(), xc.out_rows.data_ptr(), st))
+    w1c, w2c = w1_local.contiguous(), w2_local.contiguous()
+    code = _C.E4M3 if xc.fp8 else _C.DTYPE_CODE[xc.dtype]
+    common = dict(variant=_C.VARIANTS[xc.variant], activation=_C.ACTIVATIONS[activation], num_experts=xc.e_local, top_k=1,
+                  block_size=blk, numel=cap, sorted_cap=cap, max_blocks=cap // blk, a_gather=0, a_rows=cap,
+                  sorted_token_ids=xc.sorted_ids.data_ptr(), expert_ids=xc.expert_ids.data_ptr(),
+                  num_tokens_post_padded=xc.npp.data_ptr())
+    row_w = xc.weights.data_ptr()
+    act_code = _C.DTYPE_CODE[xc.act.dtype]
+    g1 = _C.GemmArgs(dtype=code, out_dtype=act_code, n=xc.I, k=xc.H, a=xc.rows.data_ptr(), a_scale=_C.ptr(xc.scales),
+                     w=w1c.data_ptr(), w_scale=_C.ptr(w1_scale.float().contiguous()) if xc.fp8 else None,
+                     row_scale=row_w if apply_router_weight_on_input else None, out=xc.act.data_ptr(), **common)
+    _C.check(lib.fmoe_gemm1_silu(g1, st))
+    a2, a2_scale = xc.act, None
+    if xc.fp8:
+        _C.check(lib.fmoe_quant_fp8_group128(xc.act.data_ptr(), act_code, cap, xc.I, xc.sorted_ids.data_ptr(), 0, cap,
+                                             xc.npp.data_ptr(), xc.actq.data_ptr(), xc.act_scale.data_ptr(), st))
+        a2, a2_scale = xc.actq, xc.act_scale
+    z_local = None
+    if not fuse_return:
+        if xc._z_local is None:
+            xc._z_local = torch.empty(cap, xc.H, dtype=xc.dtype, device=dev)
+        z_local = xc._z_local
+    g2 = _C.GemmArgs(dtype=code, out_dtype=_C.DTYPE_CODE[xc.dtype], n=xc.H, k=xc.I, a=a2.data_ptr(), a_scale=_C.ptr(a2_scale),
+                     w=w2c.data_ptr(), w_scale=_C.ptr(w2_scale.float().contiguous()) if xc.fp8 else None,
+                     row_scale=None if apply_router_weight_on_input else row_w, out=_C.ptr(z_local),
+                     out_rows=xc.out_rows.data_ptr() if fuse_return else None, **common)
+    _C.check(lib.fmoe_gemm2(g2, st))
+    return z_local
 
 
 def p2p_return(xc: PeerExchange, state: dict, z_rows: Optional[torch.Tensor]) -> None:
@@ -359,10 +433,8 @@ def p2p_return(xc: PeerExchange, state: dict, z_rows: Optional[torch.Tensor]) ->
 
     if z_rows is None:
         return
-
-    _C.check(_C.lib().fmoe_ep_combine(z_rows.data_ptr(), z_rows.element_size(), xc.H, xc.src.data_ptr(),
-                                      state["matrix"].data_ptr(), xc.rank, xc.world, xc.capacity, xc.z_slots,
-                                      xc.ptrs["z"].data_ptr(), _C.stream_ptr(z_rows.device)))
+    _C.check(_C.lib().fmoe_ep_scatter_rows(z_rows.data_ptr(), xc.H * z_rows.element_size(), xc.out_rows.data_ptr(),
+                                           xc.npp.data_ptr(), xc.capacity, _C.stream_ptr(z_rows.device)))
 
 
 def p2p_finish(xc: PeerExchange, state: dict, routed_scaling_factor: Optional[float]) -> torch.Tensor:
@@ -407,7 +479,7 @@ def ep_fused_experts(
         with _phase("route", True):
             state = p2p_route(exchange, hidden_states, topk_weights, topk_ids, e_local)
         with _phase("counts", True):
-            matrix = torch.empty(world * world, dtype=torch.int32, device=hidden_states.device)
+            matrix = torch.empty(world * exchange.total_experts, dtype=torch.int32, device=hidden_states.device)
             dist.all_gather_into_tensor(matrix, state["counts"], group=group)
         with _phase("dispatch", True):
             p2p_send(exchange, state, matrix)

@@ -84,7 +84,9 @@ def _exchange(ep, mode, T, cfg, dtype, rank):
     if mode != "p2p":
         return None, "nccl"
     try:
-        return ep.PeerExchange(None, T, cfg.top_k, cfg.H, dtype), "p2p"
+        world = dist.get_world_size()
+        return ep.PeerExchange(None, T, cfg.top_k, cfg.H, dtype, num_local_experts=cfg.E // world,
+                               intermediate_size=cfg.I, fp8=cfg.dtype == "fp8"), "p2p"
     except RuntimeError as e:  # raised on every rank together (see PeerExchange): use the NCCL exchange
         if rank == 0:
             print(f"# P2P exchange unavailable, using NCCL all-to-all: {e}", flush=True)

@@ -286,20 +286,25 @@ int fmoe_fused_experts_static(const fmoe_fused_args* args, void* stream);
  * global batch".  Experts are sharded contiguously: rank j owns global experts [j*experts_per_rank,
  * (j+1)*experts_per_rank).
  *
- * Every rank owns a receive area that its peers write: rows [capacity, H], ids [capacity] (int32, local expert
- * id), weights [capacity] (f32), src [capacity] (two int32: source rank, source slot) and a result area
- * z [z_slots, H].  `peer_*` arguments are DEVICE arrays of `world` pointers, entry j = that area on rank j
- * (entry `rank` = this rank's own).  The kernels only store to peer memory and never wait on a peer; the caller
- * orders the phases across ranks with stream-ordered collectives:
+ * Every rank owns a receive area that its peers write: rows [capacity, row bytes] (bf16 rows, or e4m3 rows with
+ * scales [capacity, H/128] f32), weights [capacity] (f32), src [capacity] (two int32: source rank, source slot) and a
+ * result area z [z_slots, H].  `peer_*` arguments are DEVICE arrays of `world` pointers, entry j = that area on
+ * rank j (entry `rank` = this rank's own).  The kernels only store to peer memory and never wait on a peer; the
+ * caller orders the phases across ranks with stream-ordered collectives:
  *
- *   fmoe_ep_route -> sort by dest (fmoe_moe_align_block_size, block 1, E = world) -> all-gather of `counts` into
- *   matrix[world*world] (matrix[i*world+j] = rows i sends to j) -> fmoe_ep_dispatch -> barrier ->
- *   fmoe_ep_mask_tail -> expert computation over the receive area (top_k = 1, ids = -1 rows are skipped) ->
- *   fmoe_ep_combine (or none: out_rows of fmoe_ep_mask_tail) -> barrier -> fmoe_moe_sum over this rank's z.
+ *   fmoe_ep_expert_counts -> sort by expert (fmoe_moe_align_block_size, block 1, E = all experts) -> all-gather of
+ *   `counts` into matrix[world * total_experts] (matrix[r*E + e] = rows rank r holds for global expert e) ->
+ *   fmoe_ep_dispatch_sorted -> barrier -> fmoe_ep_recv_tables -> grouped GEMMs straight over the receive area
+ *   (fmoe_gemm1_silu / fmoe_gemm2 with top_k = 1, a_gather = 0, numel = capacity) -> fmoe_ep_scatter_rows (or
+ *   none: out_rows of fmoe_ep_recv_tables given to fmoe_gemm2) -> barrier -> fmoe_moe_sum over this rank's z.
  *
- * Misuse that only the device can see (an expert id outside [0, world*experts_per_rank), a row beyond
- * `capacity`, a corrupt return address) is skipped, recorded, and returned by fmoe_check_device_status as
- * FMOE_ERR_INVALID_ARG.
+ * Rows land in the owner's area already in the padded expert-sorted order the grouped GEMMs read: the owner's
+ * experts ascending, each starting at a multiple of `block`, inside an expert the ranks in rank order, inside a
+ * rank ascending flat slot; the receiver runs no moe_align and no row copy.
+ *
+ * Misuse that only the device can see (an expert id outside [0, total_experts), a row beyond `capacity`, a
+ * corrupt return address) is skipped, recorded, and returned by fmoe_check_device_status as
+ * FMOE_ERR_INVALID_ARG; the result rows of skipped slots read as zero.
  */
 #define FMOE_EP_IPC_HANDLE_BYTES 64
 /* cudaMalloc + IPC handle of a receive area / open and close a peer's / free the own one. */
@@ -307,26 +312,30 @@ int fmoe_ep_buffer_create(int64_t bytes, void** ptr, void* ipc_handle /* FMOE_EP
 int fmoe_ep_buffer_open(const void* ipc_handle, void** ptr);
 int fmoe_ep_buffer_close(void* ptr);
 int fmoe_ep_buffer_destroy(void* ptr);
-/* dest[i] = topk_ids[i] / experts_per_rank (world for an id out of range), counts[j] = rows for rank j. */
-int fmoe_ep_route(const int32_t* topk_ids, int64_t numel, int experts_per_rank, int world, int32_t* dest,
-                  int32_t* counts, void* stream);
-/* perm: the numel (token, slot) positions sorted by dest (stable).  Sends hidden[perm[p] / top_k] and its metadata. */
-int fmoe_ep_dispatch(const void* hidden, int elem_bytes, int64_t T, int64_t H, int top_k,
-                     const int32_t* topk_ids, const float* topk_weights, const int32_t* perm,
-                     const int32_t* matrix, int rank, int world, int experts_per_rank,
-                     void* const* peer_rows, int32_t* const* peer_ids, float* const* peer_weights,
-                     void* const* peer_src, int64_t capacity, void* stream);
-/* recv_ids[r] = -1 for r >= rows received (sum of column `rank` of the matrix).  With out_rows != NULL also
- * out_rows[r] = peer_z[src[r].rank] + src[r].slot * row_bytes for the received rows (NULL past them): the
- * table fmoe_gemm_args.out_rows takes, which makes the down-projection epilogue store every result row
- * straight into the slot buffer of the rank it came from (no fmoe_ep_combine pass). */
-int fmoe_ep_mask_tail(int32_t* recv_ids, const int32_t* matrix, int rank, int world, int64_t capacity,
-                      const void* recv_src, int64_t z_slots, void* const* peer_z, int64_t row_bytes,
-                      void** out_rows, void* stream);
-/* z_rows[r] (expert output of received row r) -> peer_z[src[r].rank] + src[r].slot * H. */
-int fmoe_ep_combine(const void* z_rows, int elem_bytes, int64_t H, const void* recv_src,
-                    const int32_t* matrix, int rank, int world, int64_t capacity, int64_t z_slots,
-                    void* const* peer_z, void* stream);
+/* counts[e] = number of entries of topk_ids equal to e, e in [0, total_experts) (<= 1024). */
+int fmoe_ep_expert_counts(const int32_t* topk_ids, int64_t numel, int total_experts, int32_t* counts, void* stream);
+/* perm: the T*top_k (token, slot) positions sorted by expert (stable; invalid ids dropped).  Sends row
+ * perm[p] / top_k of `rows` ([T, row_bytes]; with row_scales [T, scales_per_row] f32 for e4m3 rows) and its
+ * weight / return address to the owner of its expert.  own_z: this rank's result area, whose rows of slots that
+ * could not be sent are zeroed (NULL: not touched). */
+int fmoe_ep_dispatch_sorted(const void* rows, int64_t row_bytes, const float* row_scales, int scales_per_row,
+                            int64_t T, int top_k, const int32_t* topk_ids, const float* topk_weights,
+                            const int32_t* perm, const int32_t* matrix, int rank, int world, int total_experts,
+                            int experts_per_rank, int block, void* const* peer_rows, float* const* peer_scales,
+                            float* const* peer_weights, void* const* peer_src, int64_t capacity, void* own_z,
+                            int64_t z_row_bytes, void* stream);
+/* Tables of this rank's receive area for the grouped GEMMs: sorted_token_ids [capacity] (row index, `capacity` for
+ * padding rows), expert_ids [expert_cap >= capacity/block] (local expert of each used block, -1 after them),
+ * num_tokens_post_padded [1].  With out_rows != NULL also out_rows[r] = peer_z[src[r].rank] + src[r].slot *
+ * z_row_bytes for the received rows (NULL for padding): the table fmoe_gemm_args.out_rows takes, which makes the
+ * down-projection epilogue store every result row straight into the slot buffer of the rank it came from. */
+int fmoe_ep_recv_tables(const int32_t* matrix, int rank, int world, int total_experts, int experts_per_rank, int block,
+                        int64_t capacity, const void* recv_src, int64_t z_slots, void* const* peer_z,
+                        int64_t z_row_bytes, int32_t* sorted_token_ids, int32_t* expert_ids, int64_t expert_cap,
+                        int32_t* num_tokens_post_padded, void** out_rows, void* stream);
+/* z_rows[r] (expert output of received row r, r < *num_rows_dev) -> out_rows[r] (skipped when NULL). */
+int fmoe_ep_scatter_rows(const void* z_rows, int64_t row_bytes, void* const* out_rows, const int32_t* num_rows_dev,
+                         int64_t capacity, void* stream);
 
 /*
  * Reads and clears the device-side status word that bounded waits inside the

@@ -48,7 +48,7 @@ def _worker(rank, world, port, fp8, p2p, q):
         x = torch.randn(T, H, generator=g2).bfloat16().to(dev)
         logits = torch.randn(T, E, generator=g2).to(dev)
         # p2p: rows stored into the peers' IPC-mapped receive areas by this package's kernels; else NCCL all-to-all
-        xc = ep.PeerExchange(None, 300, k, H) if p2p else None
+        xc = ep.PeerExchange(None, 300, k, H, num_local_experts=el, intermediate_size=I, fp8=fp8) if p2p else None
         ref = fg.fused_moe(x, w1, w2, logits, k, True, **kw_full)
         err = 0.0
         for _ in range(3 if p2p else 1):  # repeated calls reuse the receive areas

@@ -1,5 +1,5 @@
 """Expert-parallel exchange over peer memory, exercised on ONE GPU: `PeerExchange.emulated` makes the "peers"
-plain local tensors, so the route / dispatch / mask / combine kernels and their pointer tables run exactly as
+plain local tensors, so the count / dispatch / table / return kernels and their pointer tables run exactly as
 between processes, phase by phase for all ranks (there is nothing to wait on).  Every emulated rank's output
 must match the single-GPU op on that rank's tokens with the full weights.  The IPC mapping itself is covered
 by test_gpu_ep.py on two GPUs."""
@@ -19,9 +19,11 @@ def _layer(E, H, I, seed):
 
 
 def _run_emulated(fg, ep, world, tokens, E, H, k, w1, w2, kw_of_rank, capacity=None, rsf=None, bad_id=False,
-                  fuse=None):
+                  fuse=None, variant=None):
     el = E // world
-    xcs = ep.PeerExchange.emulated(world, max(max(tokens), 1), k, H, torch.bfloat16, capacity=capacity)
+    fp8 = bool(kw_of_rank(0).get("use_fp8_w8a8"))
+    xcs = ep.PeerExchange.emulated(world, max(max(tokens), 1), k, H, torch.bfloat16, capacity=capacity,
+                                   num_local_experts=el, intermediate_size=w2.shape[2], fp8=fp8, variant=variant)
     xs, states = [], []
     for r in range(world):
         g = torch.Generator().manual_seed(100 + r)
@@ -55,7 +57,7 @@ def test_emulated_ranks_match_single_gpu_bf16(world, tokens, fuse):
     w1, w2 = _layer(E, H, I, 0)
     xs, outs, matrix, xcs = _run_emulated(fg, ep, world, tokens, E, H, k, w1, w2, lambda r: {}, rsf=1.5, fuse=fuse)
     _C.check_device_status()
-    m = matrix.view(world, world).cpu()
+    m = matrix.view(world, E).cpu()  # rows per (rank, global expert)
     assert m.sum(1).tolist() == [t * k for t in tokens]
     for r in range(world):
         x, tw, ti = xs[r]
@@ -65,9 +67,17 @@ def test_emulated_ranks_match_single_gpu_bf16(world, tokens, fuse):
         ref = fg.fused_experts(x, w1, w2, tw, ti, routed_scaling_factor=1.5)
         err = float((outs[r].float() - ref.float()).norm() / ref.float().norm())
         assert err < 5e-3, f"rank {r}: rel-L2 {err}"
-        # the receive area holds exactly the announced rows, the rest is masked
-        got = int(m[:, r].sum())
-        assert (xcs[r].ids[:got] >= 0).all() and (xcs[r].ids[got:] == -1).all()
+        # the receive area's tables describe exactly the announced rows: per local expert a block-aligned
+        # segment holding the rows of all ranks, padding marked by the sentinel
+        el, blk, cap = E // world, xcs[r].block, xcs[r].capacity
+        per_expert = m[:, r * el:(r + 1) * el].sum(0)
+        sid = xcs[r].sorted_ids.cpu()
+        assert int((sid < cap).sum()) == int(per_expert.sum())
+        assert int(xcs[r].npp.item()) == int(((per_expert + blk - 1) // blk * blk).sum())
+        eid = xcs[r].expert_ids.cpu()
+        used_blocks = int(xcs[r].npp.item()) // blk
+        assert eid[:used_blocks].tolist() == [e for e in range(el) for _ in range(int((per_expert[e] + blk - 1) // blk))]
+        assert (eid[used_blocks:] == -1).all()
 
 
 def test_emulated_ranks_forced_same_kernel_family_is_bit_exact():
@@ -78,7 +88,7 @@ def test_emulated_ranks_forced_same_kernel_family_is_bit_exact():
 
     world, tokens, E, H, I, k = 4, [200, 130, 90, 256], 8, 256, 128, 2
     w1, w2 = _layer(E, H, I, 1)
-    xs, outs, _, _ = _run_emulated(fg, ep, world, tokens, E, H, k, w1, w2, lambda r: dict(variant="tcgen05"))
+    xs, outs, _, _ = _run_emulated(fg, ep, world, tokens, E, H, k, w1, w2, lambda r: {}, variant="tcgen05")
     _C.check_device_status()
     for r in range(world):
         x, tw, ti = xs[r]
@@ -124,6 +134,11 @@ def test_capacity_overflow_and_bad_id_are_reported_not_fatal():
     with pytest.raises(_C.FmoeError) as ei:
         _C.check_device_status()
     assert "site code 0xa00" in str(ei.value).lower()
+    # a dropped slot (bad id) contributes zeros, not the previous call's values
+    xs_b, outs_b, _, xcs_b = _run_emulated(fg, ep, world, tokens, E, H, k, w1, w2, lambda r: {}, bad_id=True)
+    with pytest.raises(_C.FmoeError):
+        _C.check_device_status()
+    assert (xcs_b[1].z[0] == 0).all()
     # the context is still usable and the status is clear again
     xs, outs, _, _ = _run_emulated(fg, ep, world, tokens, E, H, k, w1, w2, lambda r: {})
     _C.check_device_status()

@@ -15,9 +15,11 @@ int pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forc
   if (dtype != FMOE_BF16 && dtype != FMOE_E4M3) return fail(FMOE_ERR_INVALID_ARG, "unknown dtype %d", dtype);
   const int64_t active = std::max<int64_t>(1, std::min<int64_t>(E, numel));
   const double rows = (double)numel / (double)active;  // rows per active expert if routing were uniform
-  const bool stream_ok = (H % 128 == 0) && (I % 128 == 0);
+  // bf16: the tensor-core kernels cut their last column tile / zero-fill their last K step, the streaming kernel
+  // masks its last 128-k chunk, so sizes such as 2880 (GPT-OSS) stay off the plain CUDA-core kernel
+  const bool stream_ok = dtype == FMOE_BF16 ? (H % 16 == 0 && I % 16 == 0) : (H % 128 == 0 && I % 128 == 0);
   // e4m3: a tile's block scales are staged in shared memory, which bounds the reduction length at 8192
-  const bool tc_ok = dtype == FMOE_BF16 ? (I % 128 == 0 && H % 32 == 0)
+  const bool tc_ok = dtype == FMOE_BF16 ? (I % 32 == 0 && H % 32 == 0)
                                         : (I % 128 == 0 && H % 128 == 0 && I <= 8192 && H <= 8192);
   int v = forced;
   if (v == FMOE_VARIANT_AUTO) {
@@ -30,15 +32,15 @@ int pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forc
   }
   switch (v) {
     case FMOE_VARIANT_TCGEN05:
-      if (!tc_ok) return fail(FMOE_ERR_UNSUPPORTED, "tcgen05 kernels need I %% 128 == 0 and H %% 32 == 0 (e4m3: H %% 128 == 0, H and I up to 8192)");
+      if (!tc_ok) return fail(FMOE_ERR_UNSUPPORTED, "tcgen05 kernels need I %% 32 == 0 and H %% 32 == 0 (e4m3: multiples of 128, up to 8192)");
       *block = 128;
       break;
     case FMOE_VARIANT_TCGEN05_PAIR:
-      if (!tc_ok || dtype != FMOE_BF16) return fail(FMOE_ERR_UNSUPPORTED, "the CTA-pair kernel needs bf16, I %% 128 == 0 and H %% 32 == 0");
+      if (!tc_ok || dtype != FMOE_BF16 || I % 128 != 0) return fail(FMOE_ERR_UNSUPPORTED, "the CTA-pair kernel needs bf16, I %% 128 == 0 and H %% 32 == 0");
       *block = 256;
       break;
     case FMOE_VARIANT_STREAM:
-      if (!stream_ok) return fail(FMOE_ERR_UNSUPPORTED, "stream kernels need H %% 128 == 0 and I %% 128 == 0");
+      if (!stream_ok) return fail(FMOE_ERR_UNSUPPORTED, "stream kernels need H and I to be multiples of 16 (128 for e4m3)");
       *block = rows <= 4.0 ? 8 : (rows <= 12.0 ? 16 : 32);
       break;
     case FMOE_VARIANT_SIMT:

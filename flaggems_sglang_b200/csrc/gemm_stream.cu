@@ -46,7 +46,9 @@ __device__ __forceinline__ void mma_e4m3_16832(float (&d)[4], uint32_t a0, uint3
 // CTAs per SM the register allocation must allow: the kernel hides HBM latency with resident warps
 constexpr int min_ctas(int eb, int ntg) { return (ntg == 1 || (ntg == 2 && eb == 2)) ? 2 : 1; }
 
-template <int EB, int NTG, bool GATED, typename OutT>
+// RAGGED (bf16 only): K is not a multiple of 128, the loads of the last chunk that fall past the row read as zero.
+// A separate instantiation, so that the predicates never touch the load schedule of the common case.
+template <int EB, int NTG, bool GATED, typename OutT, bool RAGGED>
 __global__ void __launch_bounds__(kThreads, min_ctas(EB, NTG))
 grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
   pdl_entry();
@@ -69,7 +71,8 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
   const int64_t K = p.k;
   const int64_t w_rows = GATED ? 2 * p.n : p.n;
   const int64_t n0 = (int64_t)slab * (GATED ? 16 : 32);
-  const int64_t kblocks = K / 128;
+  const int64_t kblocks = (K + 127) / 128;  // bf16: the last chunk may be partial (its loads past K read as zero)
+  const int64_t row_bytes = K * EB;
 
   float acc[RT][NTG][4];
 #pragma unroll
@@ -134,6 +137,9 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
     float sw_c[RT], sa_c[NTG][2];
     // wptr walks one chunk ahead of xptr: it always points at the chunk whose fragments are loaded next
     const int64_t step = (int64_t)W * 128 * EB;
+    // byte offset, inside a row, of the chunk the W pointers / the x pointers stand at (bounds of a partial last chunk)
+    int64_t w_off = (int64_t)part * 128 * EB + t * 16, x_off = w_off;
+    constexpr bool ragged = RAGGED;
 #pragma unroll
     for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
@@ -145,7 +151,8 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
 #pragma unroll
       for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) wq[rt][u][h] = ldg_stream_v4(wptr[rt][h] + u * 64);
+        for (int h = 0; h < 2; ++h)
+          wq[rt][u][h] = (!ragged || w_off + u * 64 < row_bytes) ? ldg_stream_v4(wptr[rt][h] + u * 64) : make_uint4(0, 0, 0, 0);
     };
     auto load_scales = [&](int64_t chunk) {
       if constexpr (EB == 1) {
@@ -162,6 +169,7 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
       for (int rt = 0; rt < RT; ++rt)
 #pragma unroll
         for (int h = 0; h < 2; ++h) wptr[rt][h] += step;
+      w_off += step;
     };
     if (part < kblocks) {
 #pragma unroll
@@ -185,7 +193,8 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
       for (int u = 0; u < U; ++u) {
 #pragma unroll
         for (int q = 0; q < NTG; ++q) {
-          uint4 xq = xptr[q] ? ldg_cached_v4(xptr[q] + u * 64) : make_uint4(0, 0, 0, 0);
+          uint4 xq = (xptr[q] && (!ragged || x_off + u * 64 < row_bytes)) ? ldg_cached_v4(xptr[q] + u * 64)
+                                                                            : make_uint4(0, 0, 0, 0);
 #pragma unroll
           for (int rt = 0; rt < RT; ++rt) {
             if constexpr (EB == 2) {
@@ -203,6 +212,7 @@ grouped_gemm_stream_kernel(GemmParams p, int W, int n_slabs) {
 #pragma unroll
       for (int q = 0; q < NTG; ++q)
         if (xptr[q]) xptr[q] += step;
+      x_off += step;
       if constexpr (EB == 1) {
         // acc += partial * (activation scale of the token) * (weight scale of the slab) for this 128-k block
 #pragma unroll
@@ -294,15 +304,25 @@ template <int EB, int NTG, bool GATED>
 int launch(const GemmParams& p, cudaStream_t st) {
   const int n_slabs = (int)ceil_div<int64_t>(p.n, GATED ? 16 : 32);
   const int64_t items = p.max_blocks * n_slabs;
-  const int W = pick_ksplit(items, p.k / 128, EB);
+  const int W = pick_ksplit(items, (p.k + 127) / 128, EB);
   const int64_t ctas = ceil_div<int64_t>(items, kWarps / W);
   if (ctas >= (1ll << 31)) return fail(FMOE_ERR_UNSUPPORTED, "stream gemm: too many work items");
   const size_t smem = W > 1 ? sizeof(float) * kWarps * RT * NTG * 4 * 32 : 0;
   dim3 grid((unsigned)ctas);
+  const bool ragged = EB == 2 && (p.k % 128) != 0;
+  if constexpr (EB == 2) {
+    if (ragged) {
+      if (p.out_dtype == FMOE_F32)
+        launch_pdl(grouped_gemm_stream_kernel<EB, NTG, GATED, float, true>, grid, dim3(kThreads), smem, st, p, W, n_slabs);
+      else
+        launch_pdl(grouped_gemm_stream_kernel<EB, NTG, GATED, __nv_bfloat16, true>, grid, dim3(kThreads), smem, st, p, W, n_slabs);
+      return launch_status("grouped_gemm_stream_kernel");
+    }
+  }
   if (p.out_dtype == FMOE_F32)
-    launch_pdl(grouped_gemm_stream_kernel<EB, NTG, GATED, float>, grid, dim3(kThreads), smem, st, p, W, n_slabs);
+    launch_pdl(grouped_gemm_stream_kernel<EB, NTG, GATED, float, false>, grid, dim3(kThreads), smem, st, p, W, n_slabs);
   else
-    launch_pdl(grouped_gemm_stream_kernel<EB, NTG, GATED, __nv_bfloat16>, grid, dim3(kThreads), smem, st, p, W, n_slabs);
+    launch_pdl(grouped_gemm_stream_kernel<EB, NTG, GATED, __nv_bfloat16, false>, grid, dim3(kThreads), smem, st, p, W, n_slabs);
   return launch_status("grouped_gemm_stream_kernel");
 }
 
@@ -322,7 +342,7 @@ bool gemm_stream_supports(const GemmParams& p, bool gated) {
   if (p.dtype != FMOE_BF16 && p.dtype != FMOE_E4M3) return false;
   if (p.out_dtype != FMOE_BF16 && p.out_dtype != FMOE_F32) return false;
   if (p.block_size != 8 && p.block_size != 16 && p.block_size != 32) return false;
-  if (p.k <= 0 || p.k % 128 != 0) return false;
+  if (p.k <= 0 || (p.dtype == FMOE_E4M3 ? p.k % 128 != 0 : p.k % 8 != 0)) return false;  // 16-byte loads; e4m3: scale blocks
   if (p.n <= 0 || p.n % 16 != 0) return false;
   if (gated && p.dtype == FMOE_E4M3 && p.n % 128 != 0) return false;  // up rows must start on a scale block
   if (!aligned16(p.a) || !aligned16(p.w)) return false;
@@ -332,7 +352,7 @@ bool gemm_stream_supports(const GemmParams& p, bool gated) {
 int gemm_stream(const GemmParams& p, bool gated, cudaStream_t st) {
   if (!gemm_stream_supports(p, gated))
     return fail(FMOE_ERR_UNSUPPORTED,
-                "stream gemm: needs bf16/e4m3 inputs, k %% 128 == 0, n %% 16 == 0, block_size in {8,16,32}, "
+                "stream gemm: needs bf16/e4m3 inputs, k %% 8 == 0 (e4m3: 128), n %% 16 == 0, block_size in {8,16,32}, "
                 "16-byte aligned a and w (got dtype=%d k=%lld n=%lld block=%d)",
                 p.dtype, (long long)p.k, (long long)p.n, p.block_size);
   if (p.max_blocks <= 0) return FMOE_OK;

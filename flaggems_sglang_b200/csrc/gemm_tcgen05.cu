@@ -325,7 +325,9 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           ptx::tmem_ld_32x32b_x32(taddr + c * 32, g);
           ptx::tmem_ld_32x32b_x32(taddr + 128 + c * 32, u);
           ptx::tmem_ld_wait();
-          if (pos < p.sorted_cap) {
+          // the last column tile of an intermediate size that is not a multiple of 128 is cut at I (its surplus
+          // accumulator columns hold products with rows of W that belong to the up half or to the next expert)
+          if (pos < p.sorted_cap && (int64_t)n_tile * 128 + c * 32 < p.n) {
             uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
@@ -536,7 +538,7 @@ bool gemm_tcgen05_supports(const GemmParams& p, bool gated) {
   if (p.a_gather && (!gated || p.top_k < 1 || !aligned16(p.sorted_token_ids))) return false;
   if (p.bias && !aligned16(p.bias)) return false;  // 16-byte bias loads in the epilogue (n % 32 == 0 holds already)
   if (p.k <= 0 || (p.k * 2) % 16 != 0) return false;            // TMA row stride must be a multiple of 16 bytes
-  if (p.n <= 0 || p.n % (gated ? 128 : 32) != 0) return false;  // gate/up pairing; 64-byte epilogue stores
+  if (p.n <= 0 || p.n % 32 != 0) return false;  // 64-byte epilogue stores; column tiles are cut at n in 32-column pieces
   if (!aligned16(p.a) || !aligned16(p.w) || !(aligned16(p.out) && (p.out || (!gated && p.out_rows)))) return false;
   if ((int64_t)p.num_experts * (gated ? 2 * p.n : p.n) >= (1ll << 31) || p.a_rows >= (1ll << 31)) return false;
   if (p.max_blocks >= (1ll << 24) || p.num_experts > 1024) return false;
@@ -548,7 +550,7 @@ int gemm_tcgen05(const GemmParams& p, bool gated, cudaStream_t st) {
     return fail(FMOE_ERR_UNSUPPORTED,
                 "tcgen05 gemm: needs bf16 in/out, block_size 128, input-row gather only for the gate/up gemm, "
                 "n %% %d == 0, 16-byte aligned pointers (got dtype=%d block=%d a_gather=%d n=%lld k=%lld)",
-                gated ? 128 : 32, p.dtype, p.block_size, p.a_gather, (long long)p.n, (long long)p.k);
+                32, p.dtype, p.block_size, p.a_gather, (long long)p.n, (long long)p.k);
   if (p.max_blocks <= 0) return FMOE_OK;
   const bool extra = p.bias != nullptr || (gated && p.activation == FMOE_ACT_SWIGLU_OAI);
   if (p.a_gather) return extra ? launch<true, 128, true, true>(p, st) : launch<true, 128, true, false>(p, st);

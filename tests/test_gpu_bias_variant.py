@@ -37,7 +37,8 @@ def _layer(T, H, I, E, seed, dtype=torch.bfloat16):
 
 
 @pytest.mark.parametrize("variant", ["simt", "stream", "tcgen05"])
-@pytest.mark.parametrize("T,H,I,E,k", [(40, 256, 384, 8, 2), (1, 128, 128, 4, 2), (300, 512, 256, 16, 4)])
+@pytest.mark.parametrize("T,H,I,E,k", [(40, 256, 384, 8, 2), (1, 128, 128, 4, 2), (300, 512, 256, 16, 4),
+                                       (150, 352, 160, 8, 2)])  # last: sizes that are not multiples of 128
 @pytest.mark.parametrize("limit", [None, 1.25])
 def test_bias_and_swiglu_serving_layouts(fg, variant, T, H, I, E, k, limit):
     x, w1, w2, b1, b2, logits = _layer(T, H, I, E, 31 + T)

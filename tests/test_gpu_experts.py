@@ -449,3 +449,34 @@ def test_integration_stub_runs(fg):
     out = ns["fused_experts_bf16"](x.cuda(), w1.cuda(), w2.cuda(), tw.cuda(), ti.cuda().to(torch.int32))
     _C.check_device_status()
     assert_close_moe(out, OE.fused_experts(x, w1, w2, tw, ti), "bf16", "INTEGRATION.md stub")
+
+
+# ------------------------------------------------------------------ sizes that are not multiples of 128
+@pytest.mark.parametrize("variant", ["stream", "tcgen05", None])
+@pytest.mark.parametrize("T,H,I,E,k", [(40, 320, 192, 8, 2), (9, 96, 160, 4, 2), (300, 352, 96, 8, 2)])
+def test_bf16_sizes_not_multiple_of_128(fg, variant, T, H, I, E, k):
+    """Hidden / intermediate sizes such as GPT-OSS's 2880: the tensor-core kernels cut their last column tile and
+    zero-fill the last K step, the streaming kernel masks its last 128-k chunk; none falls back to the plain kernel."""
+    from flaggems_sglang_b200.ops.fused_moe import _pick_variant
+
+    x, w1, w2, logits = _layer(T, H, I, E, k, torch.bfloat16, T + H + I)
+    tw, ti = OR.softmax_topk(logits, k, True)
+    name, _ = _pick_variant(torch.bfloat16, T * k, E, I, H, variant)
+    assert name in ("stream", "tcgen05")
+    out = _run(fg, x, w1, w2, tw, ti, variant=variant)
+    assert_close_moe(out, OE.fused_experts(x, w1, w2, tw, ti), "bf16", f"{name} T={T} H={H} I={I}")
+
+
+@pytest.mark.parametrize("T", [4, 64, 600])
+def test_gpt_oss_layer_shape(fg, T):
+    """H = I = 2880, 32 experts, top-4 (the model the reference's bias variant exists for), plain silu layer."""
+    H, I, E, k = 2880, 2880, 32, 4
+    g = torch.Generator(device="cuda").manual_seed(T)
+    x = torch.randn(T, H, generator=g, device="cuda").bfloat16()
+    w1 = (torch.randn(E, 2 * I, H, generator=g, device="cuda") / H ** 0.5).bfloat16()
+    w2 = (torch.randn(E, H, I, generator=g, device="cuda") / I ** 0.5).bfloat16()
+    tw, ti = OR.softmax_topk(torch.randn(T, E, generator=g, device="cuda").cpu(), k, True)
+    out = fg.fused_experts(x, w1, w2, tw.cuda(), ti.cuda())
+    idx = torch.linspace(0, T - 1, min(T, 16)).long().unique()
+    ref = OE.fused_experts(x[idx.cuda()].cpu(), w1, w2, tw[idx], ti[idx])
+    assert_close_moe(out[idx.cuda()], ref, "bf16", f"gpt-oss shape T={T}")

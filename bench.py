@@ -357,7 +357,7 @@ def measure_point(cfg, wts, T, steps, warmup, peaks, seed=0, skew=False):
 # DRAM traffic of the gate/up GEMM per launch (dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture; the
 # summaries with the full commands are under profiles/).  Keyed by (config, T).
 MEASURED_TRAFFIC = {
-    ("mixtral", 4096): (3.25e9 + 0.235e9, "profiles/grouped_gemm_tcgen05_bf16_mixtral.md, full-size capture"),
+    ("mixtral", 4096): (2.19e9, "profiles/grouped_gemm_tcgen05_bf16_mixtral.md, full-size capture of the same launch"),
 }
 
 

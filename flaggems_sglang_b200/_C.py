@@ -17,7 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libfmoe_b200.so")
 OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_TIMEOUT = 0, 1, 2, 3, 4
 F32, BF16, E4M3 = 0, 1, 2
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_STREAM, VARIANT_TCGEN05 = 0, 1, 2, 3
-VARIANTS = {"auto": 0, "simt": 1, "stream": 2, "tcgen05": 3, "tcgen05_pair": 4}
+VARIANTS = {"auto": 0, "simt": 1, "stream": 2, "tcgen05": 3}
 ACTIVATIONS = {"silu": 0, "gelu": 1, "swiglu_oai": 2}
 VARIANT_NAMES = {v: k for k, v in VARIANTS.items()}
 

@@ -77,7 +77,6 @@ int dispatch_gemm(const fmoe_gemm_args* args, bool gated, void* stream, const ch
     case FMOE_VARIANT_STREAM: return gemm_stream(a, gated, st);
     case FMOE_VARIANT_TCGEN05:
       return a.dtype == FMOE_E4M3 ? gemm_tcgen05_fp8(a, gated, st) : gemm_tcgen05(a, gated, st);
-    case FMOE_VARIANT_TCGEN05_PAIR: return gemm_tcgen05_pair(a, gated, st);
   }
   return fail(FMOE_ERR_INVALID_ARG, "%s: unknown variant %d", who, a.variant);
 }
@@ -112,7 +111,6 @@ extern "C" int fmoe_gemm2(const fmoe_gemm_args* args, void* stream) {
 
 namespace fmoe {
 int read_wait_profile(long long* host_out, int n);
-int read_wait_profile_pair(long long* host_out, int n);
 int read_wait_profile_fp8(long long* host_out, int n);
 int launch_bounded_wait_selftest(long long limit_cycles, cudaStream_t st);
 }  // namespace fmoe
@@ -130,7 +128,6 @@ extern "C" int fmoe_debug_tcgen05_wait_profile(int64_t* host_out, int n) {
 extern "C" int fmoe_debug_wait_profile(int variant, int64_t* host_out, int n) {
   if (!host_out || n < 0 || n > (variant == -FMOE_VARIANT_TCGEN05 ? 2 : 1) * 256 * 8) return fmoe::fail(FMOE_ERR_INVALID_ARG, "wait profile: bad buffer");
   if (variant == FMOE_VARIANT_TCGEN05) return fmoe::read_wait_profile(reinterpret_cast<long long*>(host_out), n);
-  if (variant == FMOE_VARIANT_TCGEN05_PAIR) return fmoe::read_wait_profile_pair(reinterpret_cast<long long*>(host_out), n);
   if (variant == -FMOE_VARIANT_TCGEN05) return fmoe::read_wait_profile_fp8(reinterpret_cast<long long*>(host_out), n);
   return fmoe::fail(FMOE_ERR_INVALID_ARG, "wait profile: variant %d keeps none", variant);
 }

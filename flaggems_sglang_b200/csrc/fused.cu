@@ -2,6 +2,8 @@
 // it carves the caller's workspace and enqueues the kernels of the other files on the given stream.
 #include "fused.cuh"
 
+#include <nvtx3/nvToolsExt.h>
+
 namespace fmoe {
 
 int pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forced, int* variant, int* block) {
@@ -34,10 +36,6 @@ int pick_variant(int dtype, int64_t numel, int E, int64_t I, int64_t H, int forc
     case FMOE_VARIANT_TCGEN05:
       if (!tc_ok) return fail(FMOE_ERR_UNSUPPORTED, "tcgen05 kernels need I %% 32 == 0 and H %% 32 == 0 (e4m3: multiples of 128, up to 8192)");
       *block = 128;
-      break;
-    case FMOE_VARIANT_TCGEN05_PAIR:
-      if (!tc_ok || dtype != FMOE_BF16 || I % 128 != 0) return fail(FMOE_ERR_UNSUPPORTED, "the CTA-pair kernel needs bf16, I %% 128 == 0 and H %% 32 == 0");
-      *block = 256;
       break;
     case FMOE_VARIANT_STREAM:
       if (!stream_ok) return fail(FMOE_ERR_UNSUPPORTED, "stream kernels need H and I to be multiples of 16 (128 for e4m3)");
@@ -91,7 +89,7 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
   p.max_blocks = std::min<int64_t>(p.cap / p.block, p.numel);
   const int64_t eb = a.dtype == FMOE_F32 ? 4 : 2;  // element size of hidden / out / z
   const bool fp8 = a.dtype == FMOE_E4M3;
-  const bool tc = p.variant == FMOE_VARIANT_TCGEN05 || p.variant == FMOE_VARIANT_TCGEN05_PAIR;
+  const bool tc = p.variant == FMOE_VARIANT_TCGEN05;
   int64_t off = 0;
   auto take = [&](int64_t bytes) {
     int64_t o = off;
@@ -130,6 +128,22 @@ namespace {
 // Optional per-stage timing (fmoe_debug_stage_events): events of the calling thread's NEXT fused call.
 thread_local void* const* t_stage_events = nullptr;
 thread_local int t_stage_count = 0;
+
+// NVTX range per stage of the layer (header-only NVTX 3: a no-op branch unless a profiler is attached).  The range that
+// is open when the function returns, on an error too, is closed by the destructor.
+struct StageRange {
+  bool open = false;
+  void next(const char* name) {
+    if (open) nvtxRangePop();
+    nvtxRangePushA(name);
+    open = true;
+  }
+  ~StageRange() {
+    if (open) nvtxRangePop();
+  }
+};
+const char* const kStageNames[7] = {"fmoe.align",       "fmoe.gather_quant", "fmoe.gemm1_act", "fmoe.act_quant",
+                                    "fmoe.gemm2",       "fmoe.moe_sum",      "fmoe.done"};
 }  // namespace
 
 int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* stream) {
@@ -137,8 +151,10 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
   const int stage_n = t_stage_count;
   t_stage_events = nullptr;
   t_stage_count = 0;
+  StageRange range;
   auto mark = [&](int i) {
     if (stage_ev && i < stage_n && stage_ev[i]) cudaEventRecord((cudaEvent_t)stage_ev[i], (cudaStream_t)stream);
+    if (i < 6) range.next(kStageNames[i]);
   };
   if (a.T == 0) return FMOE_OK;
   FMOE_REQUIRE(a.hidden && a.w1 && a.w2 && a.topk_weights && a.topk_ids && (a.out || a.out_rows), "fused_experts: null pointer");
@@ -148,7 +164,7 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
       return fail(FMOE_ERR_UNSUPPORTED, "fused_experts: out_rows is taken by the STREAM and TCGEN05 kernels only");
   }
   const bool fp8 = a.dtype == FMOE_E4M3;
-  const bool tc = p.variant == FMOE_VARIANT_TCGEN05 || p.variant == FMOE_VARIANT_TCGEN05_PAIR;
+  const bool tc = p.variant == FMOE_VARIANT_TCGEN05;
   if (fp8) FMOE_REQUIRE(a.w1_scale && a.w2_scale, "fused_experts: e4m3 needs w1_scale and w2_scale");
   const int io = fp8 ? FMOE_BF16 : a.dtype;  // dtype of hidden / z / out
   const int64_t eb = io == FMOE_F32 ? 4 : 2;

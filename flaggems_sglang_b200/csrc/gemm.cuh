@@ -16,13 +16,11 @@ int gemm_simt(const GemmParams& p, bool gated, cudaStream_t st);
 int gemm_stream(const GemmParams& p, bool gated, cudaStream_t st);
 int gemm_tcgen05(const GemmParams& p, bool gated, cudaStream_t st);
 int gemm_tcgen05_fp8(const GemmParams& p, bool gated, cudaStream_t st);
-int gemm_tcgen05_pair(const GemmParams& p, bool gated, cudaStream_t st);
 
 // true when the variant can run these arguments (shape / alignment / dtype rules)
 bool gemm_stream_supports(const GemmParams& p, bool gated);
 bool gemm_tcgen05_supports(const GemmParams& p, bool gated);
 bool gemm_tcgen05_fp8_supports(const GemmParams& p, bool gated);
-bool gemm_tcgen05_pair_supports(const GemmParams& p, bool gated);
 
 // Tile order of the persistent kernels: expert by expert, and inside an expert in groups of at most
 // `group_m` row blocks; inside a group the row block varies fastest, then the column tile.  The tiles

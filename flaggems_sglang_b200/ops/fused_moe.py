@@ -276,7 +276,7 @@ def fused_experts(
     z_args = dict(out=_C.ptr(z), out_rows=_C.ptr(out_rows))
 
     if not use_fp8_w8a8:
-        if name == "tcgen05_pair" or (name == "tcgen05" and not os.environ.get("FMOE_TC_GATHER4")):
+        if name == "tcgen05" and not os.environ.get("FMOE_TC_GATHER4"):
             # sorted copy of the input rows (FMOE_TC_GATHER4=1: the single-CTA kernel gathers them by TMA instead)
             xs = torch.empty((cap, H), dtype=out_dtype, device=dev)
             with _stage("gather_rows"):

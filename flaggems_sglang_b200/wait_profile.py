@@ -1,6 +1,6 @@
 """Where the cycles of a tcgen05 grouped GEMM go: per-role wait counters kept by the instrumented kernels.
 
-    FMOE_TC_PROFILE=1 python -m flaggems_sglang_b200.wait_profile [--config mixtral] [--tokens 4096] [--variant tcgen05|tcgen05_pair]
+    FMOE_TC_PROFILE=1 python -m flaggems_sglang_b200.wait_profile [--config mixtral] [--tokens 4096]
 
 Runs the layer's expert computation a few times with the library's stage events, then reads the counters of the
 LAST launches with `fmoe_debug_wait_profile` and prints them per tile (bf16 kernels: MMA warp waiting for its
@@ -24,7 +24,6 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--config", default="mixtral")
     ap.add_argument("--tokens", type=int, default=4096)
-    ap.add_argument("--variant", default="tcgen05", choices=["tcgen05", "tcgen05_pair"])
     ap.add_argument("--steps", type=int, default=10)
     args = ap.parse_args()
     if not (os.environ.get("FMOE_TC_PROFILE") or os.environ.get("FMOE_FP8_DEBUG")):
@@ -49,11 +48,11 @@ def main():
     arr = (ctypes.c_void_p * n)(*[e.cuda_event for e in evs])
     for _ in range(args.steps):
         _C.check(lib.fmoe_debug_stage_events(arr, n))
-        fg.fused_experts(tok["hidden"], wts["w1"], wts["w2"], tw, ti, variant=args.variant, **kw)
+        fg.fused_experts(tok["hidden"], wts["w1"], wts["w2"], tw, ti, variant="tcgen05", **kw)
     torch.cuda.synchronize()
     _C.check_device_status()
     g1, g2 = evs[2].elapsed_time(evs[3]), evs[4].elapsed_time(evs[5])
-    print(f"{cfg.name} T={args.tokens} {args.variant}: gate/up GEMM {g1:.3f} ms, down GEMM {g2:.3f} ms (last of {args.steps} calls)")
+    print(f"{cfg.name} T={args.tokens} tcgen05: gate/up GEMM {g1:.3f} ms, down GEMM {g2:.3f} ms (last of {args.steps} calls)")
     if not os.environ.get("FMOE_TC_PROFILE"):
         return
     sms = lib.fmoe_sm_count()
@@ -68,7 +67,7 @@ def main():
                   % (a[:, 1].sum() / tiles / kb, a[:, 2].sum() / tiles / kb, a[:, 3].sum() / tiles, a[:, 4].sum() / tiles))
         return
     buf = (ctypes.c_int64 * (sms * 8))()
-    _C.check(lib.fmoe_debug_wait_profile(_C.VARIANTS[args.variant], buf, sms * 8))  # the last launch: the down GEMM
+    _C.check(lib.fmoe_debug_wait_profile(_C.VARIANTS["tcgen05"], buf, sms * 8))  # the last launch: the down GEMM
     a = np.array(buf).reshape(sms, 8)
     lead = a[a[:, 0] > 0]
     tiles = lead[:, 0].sum()

@@ -49,7 +49,6 @@ extern "C" {
 #define FMOE_VARIANT_SIMT 1    /* plain CUDA-core kernel; any shape; validation and fp32 */
 #define FMOE_VARIANT_STREAM 2  /* small-M weight-streaming kernel, split-K over warps */
 #define FMOE_VARIANT_TCGEN05 3 /* TMA + tcgen05/TMEM persistent kernel for large M */
-#define FMOE_VARIANT_TCGEN05_PAIR 4 /* same on CTA pairs (cta_group::2), 256-row blocks, bf16 */
 
 /* ABI version: 2 = argument structs begin with struct_size. */
 int fmoe_version(void);
@@ -372,8 +371,7 @@ int fmoe_debug_stage_events(void* const* events, int n);
  * 256 CTAs) to HOST memory.  No counterpart in the reference.
  */
 int fmoe_debug_tcgen05_wait_profile(int64_t* host_out, int n);
-/* Same for the kernel family `variant`: FMOE_VARIANT_TCGEN05 (bf16), FMOE_VARIANT_TCGEN05_PAIR, or -FMOE_VARIANT_TCGEN05
- * for the e4m3 kernel, whose columns are {tiles, MMA waits for a TMEM partial, MMA waits for data, producer waits,
+/* Same for the kernel family `variant`: FMOE_VARIANT_TCGEN05 (bf16) or -FMOE_VARIANT_TCGEN05 for the e4m3 kernel, whose columns are {tiles, MMA waits for a TMEM partial, MMA waits for data, producer waits,
  * fold waits, fold busy, kernel cycles, epilogue cycles}: 256 x 8 values of the last down GEMM, then 256 x 8 of the
  * last gate/up GEMM (n up to 4096). */
 int fmoe_debug_wait_profile(int variant, int64_t* host_out, int n);

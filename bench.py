@@ -504,6 +504,25 @@ def parity_vs_oracle(cfg, wts, tok, T):
     return {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}, parity
 
 
+def _interleaved_ms(fns, rounds=40, warmup=5):
+    """Median device time of each callable when they are called in turn (a, b, a, b, ...), every call preceded by an
+    L2 flush outside its timed interval: both sides see the same clocks, temperature and power state, which
+    back-to-back blocks of calls do not (the GPU sheds speed within a second of sustained load)."""
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(rounds)]
+           for _ in fns]
+    for i in range(warmup + rounds):
+        for j, fn in enumerate(fns):
+            flush.zero_()
+            if i >= warmup:
+                evs[j][i - warmup][0].record()
+            fn()
+            if i >= warmup:
+                evs[j][i - warmup][1].record()
+    torch.cuda.synchronize()
+    return [statistics.median(a.elapsed_time(b) for a, b in ev) for ev in evs]
+
+
 def vs_triton(cfg, wts, tokens):
     """Same box, same inputs: the REAL reference operator (`flaggems_sglang.triton_kernel_fused_experts` from the
     offline install under baseline/_ref, running the `triton_kernels` copy vLLM vendors) against this package,
@@ -533,7 +552,10 @@ def vs_triton(cfg, wts, tokens):
     from flaggems_sglang_b200 import workloads as W
 
     out = {"reference": "flaggems_sglang.triton_kernel_fused_experts (baseline/_ref) on vLLM's triton_kernels",
-           "timing": "triton.testing.do_bench median, L2 flushed between calls", "points": []}
+           "timing": "triton.testing.do_bench median, L2 flushed between calls (blocks of calls: reference, reference "
+                     "with routing, this package); 'interleaved': alternating calls, median of 40 each; "
+                     "'same_arguments': this package's triton_kernel_fused_experts called with the reference's own "
+                     "argument list ([E,H,2I] / [E,I,H] weights, its routing objects)", "points": []}
     w1r = wts["w1"].transpose(1, 2).contiguous()  # the reference's [E,H,2I] / [E,I,H] layouts, prepared once
     w2r = wts["w2"].transpose(1, 2).contiguous()
     for T in tokens:
@@ -554,14 +576,22 @@ def vs_triton(cfg, wts, tokens):
             def ours():
                 return fg.fused_experts(x, wts["w1"], wts["w2"], tw, ti)
 
+            def ours_entry():  # the drop-in call: the reference's own arguments, weights [E,H,2I] / [E,I,H] read in place
+                return fg.triton_kernel_fused_experts(x, w1r, w2r, *tables)
+
             r, g = ref_experts().float(), ours().float()
             rec["rel_l2"] = float((g - r).norm() / r.norm())
             rec["reference_experts_ms"] = triton.testing.do_bench(ref_experts, warmup=20, rep=100, return_mode="median")
             rec["reference_routing_plus_experts_ms"] = triton.testing.do_bench(ref_with_routing, warmup=20, rep=100,
                                                                                 return_mode="median")
             rec["ours_ms"] = triton.testing.do_bench(ours, warmup=20, rep=100, return_mode="median")
+            rec["rel_l2_same_arguments"] = float((ours_entry().float() - r).norm() / r.norm())
+            rec["ours_same_arguments_ms"] = triton.testing.do_bench(ours_entry, warmup=20, rep=100, return_mode="median")
             rec["speedup_experts"] = rec["reference_experts_ms"] / rec["ours_ms"]
             rec["speedup_with_routing"] = rec["reference_routing_plus_experts_ms"] / rec["ours_ms"]
+            a, b, c = _interleaved_ms([ref_experts, ours, ours_entry])
+            rec["interleaved"] = {"reference_experts_ms": a, "ours_ms": b, "ours_same_arguments_ms": c,
+                                  "speedup_experts": a / b, "speedup_same_arguments": a / c}
         except Exception as e:  # noqa: BLE001  (the vendored third-party copy is not pinned by the reference)
             rec["error"] = f"{type(e).__name__}: {e}"[:300]
         out["points"].append(rec)
@@ -580,6 +610,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-T sweeps (this configuration's and the others')")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity leg")
     ap.add_argument("--no-triton", action="store_true", help="skip the same-box timing of the reference's Triton path")
+    ap.add_argument("--triton-tokens", default="", help="comma-separated batch sizes for that comparison (default 64,1024,4096)")
     ap.add_argument("--skew", action="store_true", help="Zipf(1.2)-skewed routing for the headline point")
     ap.add_argument("--ep-exchange", default="p2p", choices=["p2p", "nccl"],
                     help="N>1: token exchange by this package's P2P-store kernels (default) or by NCCL all-to-all")
@@ -633,7 +664,8 @@ def main():
 
     triton_cmp = None
     if not args.no_triton and cfg.dtype == "bf16":
-        triton_cmp = vs_triton(cfg, wts, [t for t in (64, 1024, 4096) if t in cfg.sweep_T] or [T])
+        triton_T = [int(t) for t in args.triton_tokens.split(",") if t] or [t for t in (64, 1024, 4096) if t in cfg.sweep_T]
+        triton_cmp = vs_triton(cfg, wts, triton_T or [T])
 
     others = {}
     if not args.no_sweep and args.config == "mixtral":

@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libfmoe_b200.so")
 OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_TIMEOUT = 0, 1, 2, 3, 4
 F32, BF16, E4M3 = 0, 1, 2
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_STREAM, VARIANT_TCGEN05 = 0, 1, 2, 3
+W_K_MAJOR, W_N_MAJOR = 0, 1
 VARIANTS = {"auto": 0, "simt": 1, "stream": 2, "tcgen05": 3}
 ACTIVATIONS = {"silu": 0, "gelu": 1, "swiglu_oai": 2}
 VARIANT_NAMES = {v: k for k, v in VARIANTS.items()}
@@ -42,7 +43,7 @@ class GemmArgs(_SizedStructure):
     """Mirror of struct fmoe_gemm_args."""
 
     _fields_ = [
-        ("struct_size", c_uint32), ("reserved0", c_int32),
+        ("struct_size", c_uint32), ("w_layout", c_int32),
         ("dtype", c_int32), ("out_dtype", c_int32), ("variant", c_int32), ("num_experts", c_int32),
         ("top_k", c_int32), ("block_size", c_int32), ("a_gather", c_int32), ("activation", c_int32),
         ("numel", c_int64), ("n", c_int64), ("k", c_int64), ("a_rows", c_int64),
@@ -58,7 +59,7 @@ class FusedArgs(_SizedStructure):
     """Mirror of struct fmoe_fused_args."""
 
     _fields_ = [
-        ("struct_size", c_uint32), ("reserved0", c_int32),
+        ("struct_size", c_uint32), ("w_layout", c_int32),
         ("dtype", c_int32), ("variant", c_int32), ("num_experts", c_int32), ("top_k", c_int32),
         ("apply_router_weight_on_input", c_int32), ("no_combine", c_int32), ("zero_dropped", c_int32),
         ("activation", c_int32),

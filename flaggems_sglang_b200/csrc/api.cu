@@ -26,6 +26,11 @@ int validate_gemm(const GemmParams& a, bool gated, const char* who) {
   FMOE_REQUIRE(a.num_experts >= 1 && a.top_k >= 1 && a.block_size >= 1, "%s: bad E/top_k/block_size", who);
   FMOE_REQUIRE(a.activation == FMOE_ACT_SILU || a.activation == FMOE_ACT_GELU || a.activation == FMOE_ACT_SWIGLU_OAI,
                "%s: unknown activation %d", who, a.activation);
+  FMOE_REQUIRE(a.w_layout == FMOE_W_K_MAJOR || a.w_layout == FMOE_W_N_MAJOR, "%s: unknown w_layout %d", who, a.w_layout);
+  if (a.w_layout == FMOE_W_N_MAJOR) {
+    if (a.dtype != FMOE_BF16 || (a.variant != FMOE_VARIANT_AUTO && a.variant != FMOE_VARIANT_TCGEN05))
+      return fail(FMOE_ERR_UNSUPPORTED, "%s: [E,K,N] weights (FMOE_W_N_MAJOR) are read by the bf16 TCGEN05 kernel only", who);
+  }
   if (a.bias || a.activation == FMOE_ACT_SWIGLU_OAI)
     FMOE_REQUIRE(a.dtype != FMOE_E4M3, "%s: bias and the swiglu_oai activation are not available with e4m3 weights", who);
   FMOE_REQUIRE(a.numel >= 0 && a.n >= 1 && a.k >= 1, "%s: bad sizes numel=%lld n=%lld k=%lld", who,
@@ -64,7 +69,9 @@ int dispatch_gemm(const fmoe_gemm_args* args, bool gated, void* stream, const ch
   if (a.max_blocks == 0 || a.numel == 0) return FMOE_OK;
   auto st = (cudaStream_t)stream;
   int variant = a.variant;
-  if (variant == FMOE_VARIANT_AUTO) {
+  if (a.w_layout == FMOE_W_N_MAJOR) {
+    variant = FMOE_VARIANT_TCGEN05;
+  } else if (variant == FMOE_VARIANT_AUTO) {
     if (gemm_tcgen05_supports(a, gated) || gemm_tcgen05_fp8_supports(a, gated))
       variant = FMOE_VARIANT_TCGEN05;
     else if (gemm_stream_supports(a, gated))

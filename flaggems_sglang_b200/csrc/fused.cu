@@ -80,9 +80,16 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
                  "fused_experts: bias and the swiglu_oai activation are not available with e4m3 weights");
   if (a.dtype == FMOE_E4M3)
     FMOE_REQUIRE(a.H % 128 == 0 && a.I % 128 == 0, "fused_experts: e4m3 needs H and I to be multiples of 128");
+  FMOE_REQUIRE(a.w_layout == FMOE_W_K_MAJOR || a.w_layout == FMOE_W_N_MAJOR, "fused_experts: unknown w_layout %d", a.w_layout);
+  const bool n_major = a.w_layout == FMOE_W_N_MAJOR;
+  if (n_major && (a.dtype != FMOE_BF16 || a.b1 || a.b2 || a.activation == FMOE_ACT_SWIGLU_OAI ||
+                  (a.variant != FMOE_VARIANT_AUTO && a.variant != FMOE_VARIANT_TCGEN05)))
+    return fail(FMOE_ERR_UNSUPPORTED, "fused_experts: [E,H,2I] / [E,I,H] weights (FMOE_W_N_MAJOR) need bf16, the TCGEN05 "
+                "kernels, no bias and no swiglu_oai");
   FusedPlan& p = *pl;
   p.numel = a.T * a.top_k;
-  int rc = pick_variant(a.dtype, p.numel, a.num_experts, a.I, a.H, a.variant, &p.variant, &p.block);
+  int rc = pick_variant(a.dtype, p.numel, a.num_experts, a.I, a.H, n_major ? FMOE_VARIANT_TCGEN05 : a.variant, &p.variant,
+                        &p.block);
   if (rc) return rc;
   p.cap = p.numel + (int64_t)a.num_experts * (p.block - 1);
   p.nblk = ceil_div<int64_t>(p.cap, p.block);
@@ -115,7 +122,7 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
     p.off_actq = take(p.cap * a.I);
     p.off_actq_scale = take(p.cap * (a.I / 128) * 4);
   } else {
-    if (tc && !tc_gathers_input(p.variant, a.dtype)) p.off_xs = take(p.cap * a.H * eb);
+    if (tc && !(tc_gathers_input(p.variant, a.dtype) && !n_major)) p.off_xs = take(p.cap * a.H * eb);
     p.act_elem = (int)eb;
     p.off_act = take(p.cap * a.I * eb);
   }
@@ -184,6 +191,7 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
 
   fmoe_gemm_args g{};
   g.struct_size = (uint32_t)sizeof(fmoe_gemm_args);
+  g.w_layout = a.w_layout;
   g.variant = p.variant;
   g.num_experts = a.num_experts;
   g.top_k = a.top_k;
@@ -218,7 +226,7 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
 
   if (!fp8) {
     g1.dtype = g1.out_dtype = g2.dtype = a.dtype;
-    if (tc && !tc_gathers_input(p.variant, a.dtype)) {
+    if (tc && p.off_xs >= 0) {
       void* xs = ws + p.off_xs;
       rc = fmoe_gather_rows(a.hidden, (int)eb, p.cap, a.H, sorted, a.top_k, p.numel, npp, xs, stream);
       if (rc) return rc;

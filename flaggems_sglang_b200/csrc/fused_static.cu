@@ -1,8 +1,7 @@
 // fmoe_fused_experts_static: the one-call expert computation for callers that must not allocate.
 //
-// Some callers of this library cannot call cudaMalloc at the point where they run an MoE layer: code that
-// runs while a stream is being captured into a CUDA graph, a real-time serving loop that forbids
-// allocator calls on its hot thread, or an embedding process whose memory pool is owned by someone else
+// Some callers of this library cannot call cudaMalloc at the point where they run an MoE layer: a real-time
+// serving loop that forbids allocator calls on its hot thread, or an embedding process whose memory pool is owned by someone else
 // and hands out no scratch.  For them the intermediates of fmoe_fused_experts (sorted index buffers, the
 // activation between the two GEMMs, the per-slot outputs) live in a fixed array in device memory that is
 // part of this library's image instead of a caller-provided workspace.

@@ -71,7 +71,11 @@ struct TcParams {
   int32_t group_m;
   int32_t profile;
   int32_t l2_hints;    // 1: TMA loads carry L2 eviction priorities (weights evict_first, activation rows evict_last)
-  int32_t debug;       // timing experiment only (results are wrong): 1 = no TMA loads, the MMA warp never waits for data
+  int32_t debug;       // timing experiments only (results are wrong).  bit 0: no TMA loads, the MMA warp never waits for
+                       // data; bit 1: no MMAs (the ring and its barriers alone); bit 2: B read as an N-major operand;
+                       // bit 3: every load fetches the first tile (all L2 hits); bit 4: the ring re-arms a stage as soon as
+                       // its own data has landed and the MMA warp never waits (both run, uncoupled)
+  int32_t ring_depth;  // experiment: stages of the ring in use (default all)
   int32_t top_k;       // gather mode: input row of slot s is s / top_k
   int32_t a_rows;      // gather mode: rows of the input tensor (a row index >= a_rows reads zeros)
 };
@@ -93,7 +97,12 @@ __device__ __forceinline__ bool warp_wait_relaxed(uint64_t* bar, uint32_t parity
 // padding positions read row a_rows, which is outside the tensor and arrives as zeros.
 // EXTRA: the epilogue adds a bias and/or applies the swiglu_oai unit; a separate instantiation, so that the plain
 // silu/gelu kernels keep their register allocation.
-template <bool GATED, int KB, bool GATHER, bool EXTRA>
+// BNMAJ: the weights are [E, K, N] (N contiguous: the layout the reference operator takes, w1 [E,H,2I] / w2 [E,I,H])
+// and are read in place as an N-major B operand.  A stage's B part is four TMA boxes of 64 K rows x 64 columns
+// (128 bytes, one swizzle atom wide) from a 3-D map [E, K, N]: K rows past the expert's last and columns past N are
+// zero-filled by TMA.  In shared memory the boxes are 8 KB apart (the descriptor's leading byte offset), groups of
+// 8 K rows 1 KB apart (its stride byte offset), and one MMA's 16 K rows are 2 KB.
+template <bool GATED, int KB, bool GATHER, bool EXTRA, bool BNMAJ>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                             const TcParams p) {
@@ -151,8 +160,13 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       int m_blk, n_tile, e;
       cursor.locate(tile, p.n_tiles, p.group_m, p.num_experts, p.expert_ids, expert_table, &m_blk, &n_tile, &e);
       *row_a = m_blk * BM;
-      *row_b0 = (int32_t)((int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256));
-      *row_b1 = GATED ? (int32_t)(*row_b0 + p.n) : *row_b0 + 128;
+      if constexpr (BNMAJ) {  // first column of the tile, expert
+        *row_b0 = GATED ? n_tile * 128 : n_tile * 256;
+        *row_b1 = e;
+      } else {
+        *row_b0 = (int32_t)((int64_t)e * p.w_rows + (GATED ? (int64_t)n_tile * 128 : (int64_t)n_tile * 256));
+        *row_b1 = GATED ? (int32_t)(*row_b0 + p.n) : *row_b0 + 128;
+      }
     };
     // gather mode: the four input rows this lane fetches for sorted positions row_a + 4*lane .. +3
     auto lane_rows = [&](int32_t row_a) {
@@ -167,11 +181,11 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       tile_rows(blockIdx.x, &row_a, &row_b0, &row_b1);
       if constexpr (GATHER) src_rows = lane_rows(row_a);
     }
-    for (int64_t tile = blockIdx.x; tile < total_tiles && alive && p.debug != 1; tile += gridDim.x) {
+    for (int64_t tile = blockIdx.x; tile < total_tiles && alive && !(p.debug & 1); tile += gridDim.x) {
       const bool has_next = tile + gridDim.x < total_tiles;
       for (int ks = 0; ks < k_steps; ++ks) {
         const long long tp0 = p.profile ? clock64() : 0;
-        const bool okp = warp_wait(&empty_bar[stage], phase ^ 1);
+        const bool okp = warp_wait((p.debug & 16) ? &full_bar[stage] : &empty_bar[stage], phase ^ 1);
         if (p.profile) prof_a += clock64() - tp0;
         if (!okp) {
           report(0x100 | stage);
@@ -183,7 +197,15 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           uint8_t* sb = sa + A_BYTES;
           ptx::mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
           const int32_t x = ks * (KBYTES / 2);  // element coordinate (bf16)
-          if (p.l2_hints) {
+          if (p.debug & 8) row_a = row_b0 = row_b1 = 0;  // experiment: every CTA loads the same tiles (L2 hits)
+          if constexpr (BNMAJ) {
+            ptx::tma_load_2d(sa, &map_a, x, row_a, &full_bar[stage]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int32_t col = GATED ? row_b0 + (j & 1) * 64 + (j >> 1) * (int32_t)p.n : row_b0 + j * 64;
+              ptx::tma_load_3d(sb + j * (B_BYTES / 4), &map_b, col, x, row_b1, &full_bar[stage]);
+            }
+          } else if (p.l2_hints) {
             if constexpr (!GATHER) ptx::tma_load_2d_hint(sa, &map_a, x, row_a, &full_bar[stage], pol_a);
             ptx::tma_load_2d_hint(sb, &map_b, x, row_b0, &full_bar[stage], pol_w);
             ptx::tma_load_2d_hint(sb + B_BYTES / 2, &map_b, x, row_b1, &full_bar[stage], pol_w);
@@ -203,7 +225,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           tile_rows(tile + gridDim.x, &nrow_a, &nrow_b0, &nrow_b1);
           if constexpr (GATHER) nsrc_rows = lane_rows(nrow_a);
         }
-        if (++stage == STAGES) {
+        if (++stage == p.ring_depth) {
           stage = 0;
           phase ^= 1;
         }
@@ -215,15 +237,15 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     }
     if (p.profile && lane == 0 && blockIdx.x < 256) g_wait_prof[blockIdx.x * 8 + 3] = prof_a;
     // drain: do not leave while our own bulk copies may still be landing in shared memory
-    if (alive && p.debug != 1) {
-      for (int s = 0; s < STAGES; ++s) {
+    if (alive && !(p.debug & 1)) {
+      for (int s = 0; s < p.ring_depth; ++s) {
         // the consumer releases a stage only after its data arrived, so waiting for every
         // stage to be free again covers all outstanding copies
-        if (!warp_wait(&empty_bar[stage], phase ^ 1)) {
+        if (!warp_wait((p.debug & 16) ? &full_bar[stage] : &empty_bar[stage], phase ^ 1)) {
           report(0x180 | stage);
           break;
         }
-        if (++stage == STAGES) {
+        if (++stage == p.ring_depth) {
           stage = 0;
           phase ^= 1;
         }
@@ -231,7 +253,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     }
   } else if (warp == 5) {
     // ---------------- MMA issuer ----------------
-    constexpr uint32_t idesc = ptx::make_idesc(/*bf16*/ 1, BM, BN);
+    constexpr uint32_t idesc = ptx::make_idesc(/*bf16*/ 1, BM, BN) | (BNMAJ ? (1u << 16) : 0u);  // bit 16: B is N-major
     int stage = 0;
     uint32_t phase = 0;
     int local = 0;
@@ -253,7 +275,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       const uint32_t d_tmem = tmem_base + acc * BN;
       for (int ks = 0; ks < k_steps; ++ks) {
         const long long tm1 = p.profile ? clock64() : 0;
-        const bool okd = p.debug == 1 ? true : warp_wait(&full_bar[stage], phase);
+        const bool okd = (p.debug & 17) ? true : warp_wait(&full_bar[stage], phase);
         if (p.profile) prof_data += clock64() - tm1;
         if (!okd) {
           report(0x240 | stage);
@@ -265,15 +287,33 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           const uint32_t sa = ptx::smem_u32(smem + stage * STAGE_BYTES);
           const uint64_t da = ptx::smem_desc_sw128(sa);
           const uint64_t db = ptx::smem_desc_sw128(sa + A_BYTES);
+          if constexpr (BNMAJ) {
+            const uint64_t dbn = ptx::smem_desc_sw128_lbo(sa + A_BYTES, B_BYTES / 4, 1024);
 #pragma unroll
-          for (int kk = 0; kk < KBYTES / 32; ++kk) {
-            // 32 bytes of K per MMA (16 bf16): advance the start address by 32 B = 2 units
-            ptx::mma_f16_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (ks | kk) != 0);
+            for (int kk = 0; kk < KBYTES / 32; ++kk)
+              ptx::mma_f16_ss(d_tmem, da + 2 * kk, dbn + (2048 >> 4) * kk, idesc, (ks | kk) != 0);
+            ptx::mma_commit(&empty_bar[stage]);
+          } else if (p.debug & 2) {
+            ptx::mbar_arrive(&empty_bar[stage]);
+          } else if (p.debug & 4) {
+            // B as an N-major operand: 64 columns (128 B) x 8 K rows per swizzle atom, atoms of the next 8 K rows
+            // 1024 B on, of the next 64 columns 8192 B on; 16 K rows per MMA = 2048 B
+            const uint64_t dbn = ptx::smem_desc_sw128_lbo(sa + A_BYTES, 8192, 1024);
+#pragma unroll
+            for (int kk = 0; kk < KBYTES / 32; ++kk)
+              ptx::mma_f16_ss(d_tmem, da + 2 * kk, dbn + 128 * kk, idesc | (1u << 16), (ks | kk) != 0);
+            if (!(p.debug & 1)) ptx::mma_commit(&empty_bar[stage]);
+          } else {
+#pragma unroll
+            for (int kk = 0; kk < KBYTES / 32; ++kk) {
+              // 32 bytes of K per MMA (16 bf16): advance the start address by 32 B = 2 units
+              ptx::mma_f16_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (ks | kk) != 0);
+            }
+            if (!(p.debug & 17)) ptx::mma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
           }
-          if (p.debug != 1) ptx::mma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
         }
         __syncwarp();
-        if (++stage == STAGES) {
+        if (++stage == p.ring_depth) {
           stage = 0;
           phase ^= 1;
         }
@@ -475,9 +515,24 @@ int make_tensor_map_2d(CUtensorMap* map, const void* base, int64_t rows, int64_t
   return FMOE_OK;
 }
 
+// bf16 weights [E, K, N] with N contiguous; box = 64 columns (128 bytes, the swizzle width) x 64 K rows of one expert.
+int make_tensor_map_nmajor(CUtensorMap* map, const void* base, int64_t experts, int64_t k, int64_t n) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[3] = {(cuuint64_t)n, (cuuint64_t)k, (cuuint64_t)experts};
+  cuuint64_t strides[2] = {(cuuint64_t)n * 2, (cuuint64_t)n * (cuuint64_t)k * 2};
+  cuuint32_t box[3] = {64, 64, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FMOE_ERR_CUDA, "cuTensorMapEncodeTiled (N-major weights) failed with code %d", (int)r);
+  return FMOE_OK;
+}
+
 namespace {
 
-template <bool GATED, int KB, bool GATHER, bool EXTRA>
+template <bool GATED, int KB, bool GATHER, bool EXTRA, bool BNMAJ = false>
 int launch(const GemmParams& g, cudaStream_t st) {
   constexpr int KBYTES = KB;
   constexpr int MAX_SMEM = Ring<KB>::SMEM_BYTES + expert_table_bytes(1024);
@@ -485,7 +540,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
   const int sm_count = device_sm_count();
   static PerDeviceOnce once_attr;  // the opt-in to > 48 KB of dynamic shared memory is per device
   const cudaError_t attr_err = per_device_once(once_attr, [] {
-    return cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA>,
+    return cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA, BNMAJ>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
   });
   if (attr_err != cudaSuccess)
@@ -495,7 +550,8 @@ int launch(const GemmParams& g, cudaStream_t st) {
   CUtensorMap map_a, map_b;
   int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 2, GATHER ? 1 : BM, false, KB);
   if (rc) return rc;
-  rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 2, 128, true, KB);
+  if constexpr (BNMAJ) rc = make_tensor_map_nmajor(&map_b, g.w, g.num_experts, g.k, w_rows);
+  else rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 2, 128, true, KB);
   if (rc) return rc;
 
   TcParams p;
@@ -521,12 +577,15 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.a_rows = (int32_t)g.a_rows;
 
   const int64_t max_tiles = g.max_blocks * p.n_tiles;
-  const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sm_count > 0 ? sm_count : 148, max_tiles));
+  unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sm_count > 0 ? sm_count : 148, max_tiles));
+  if (const char* cap = getenv("FMOE_TC_MAX_CTAS")) grid = std::max(1u, std::min(grid, (unsigned)atoi(cap)));  // experiment
   p.group_m = pick_group_m(BM, g.k * 2);
   p.profile = getenv("FMOE_TC_PROFILE") != nullptr;
   p.debug = getenv("FMOE_TC_DEBUG") ? atoi(getenv("FMOE_TC_DEBUG")) : 0;
   p.l2_hints = getenv("FMOE_TC_L2_HINTS") ? atoi(getenv("FMOE_TC_L2_HINTS")) : 0;
-  grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
+  p.ring_depth = Ring<KB>::STAGES;
+  if (const char* d = getenv("FMOE_TC_RING_DEPTH")) p.ring_depth = std::max(1, std::min(Ring<KB>::STAGES, atoi(d)));
+  grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA, BNMAJ><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_kernel");
 }
 
@@ -537,6 +596,9 @@ bool gemm_tcgen05_supports(const GemmParams& p, bool gated) {
   if (p.block_size != BM) return false;
   // gather mode: gate/up GEMM only; one int4 of sorted ids per lane
   if (p.a_gather && (!gated || p.top_k < 1 || !aligned16(p.sorted_token_ids))) return false;
+  if (p.w_layout != FMOE_W_K_MAJOR && p.w_layout != FMOE_W_N_MAJOR) return false;
+  // weights in the reference operator's [E, K, N] layout: plain kernels only (no row gather, bias or swiglu_oai)
+  if (p.w_layout == FMOE_W_N_MAJOR && (p.a_gather || p.bias || (gated && p.activation == FMOE_ACT_SWIGLU_OAI))) return false;
   if (p.bias && !aligned16(p.bias)) return false;  // 16-byte bias loads in the epilogue (n % 32 == 0 holds already)
   if (p.k <= 0 || (p.k * 2) % 16 != 0) return false;            // TMA row stride must be a multiple of 16 bytes
   if (p.n <= 0 || p.n % 32 != 0) return false;  // 64-byte epilogue stores; column tiles are cut at n in 32-column pieces
@@ -554,6 +616,8 @@ int gemm_tcgen05(const GemmParams& p, bool gated, cudaStream_t st) {
                 32, p.dtype, p.block_size, p.a_gather, (long long)p.n, (long long)p.k);
   if (p.max_blocks <= 0) return FMOE_OK;
   const bool extra = p.bias != nullptr || (gated && p.activation == FMOE_ACT_SWIGLU_OAI);
+  if (p.w_layout == FMOE_W_N_MAJOR)
+    return gated ? launch<true, 128, false, false, true>(p, st) : launch<false, 128, false, false, true>(p, st);
   if (p.a_gather) return extra ? launch<true, 128, true, true>(p, st) : launch<true, 128, true, false>(p, st);
   if (gated) return extra ? launch<true, 128, false, true>(p, st) : launch<true, 128, false, false>(p, st);
   return extra ? launch<false, 128, false, true>(p, st) : launch<false, 128, false, false>(p, st);

@@ -96,6 +96,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// 3-D tiled TMA load (x innermost).
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int32_t x, int32_t y, int32_t z,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
 // L2 eviction-priority policies for the loads below: weight tiles are streamed once (by the few CTAs that share
 // them at that moment) and should leave L2 first; activation rows are re-read by every column tile and should stay.
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
@@ -209,6 +217,18 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset between 8-row groups
   d |= (uint64_t)1 << 46;                        // descriptor version for sm_100
   d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+  return d;
+}
+
+// Same with explicit leading / stride byte offsets (MN-major operands: leading = distance between swizzle atoms along
+// M or N, stride = distance between groups of 8 K rows).
+__device__ __forceinline__ uint64_t smem_desc_sw128_lbo(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
   return d;
 }
 

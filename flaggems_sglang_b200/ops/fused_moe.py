@@ -155,6 +155,7 @@ def fused_experts(
     b2: Optional[torch.Tensor] = None,
     gemm1_alpha: Optional[float] = None,
     gemm1_clamp_limit: Optional[float] = None,
+    weights_n_major: bool = False,
 ) -> torch.Tensor:
     """Expert computation for already-routed tokens.
 
@@ -172,6 +173,9 @@ def fused_experts(
     `activation="swiglu_oai"` with `gemm1_alpha` (default 1.702) and `gemm1_clamp_limit` (None = no clamp) is
     the gated unit of the reference's bias variant (src/flaggems_sglang/ops/fused_moe.py:235-325): bias, then
     activation, then top-k weight.  bf16 / fp32 weights only.
+    `weights_n_major=True`: w1 is [E,H,2I] and w2 [E,I,H] (the layout the reference operator takes,
+    src/flaggems_sglang/ops/fused_moe.py:192-199), read in place by the bf16 tensor-core kernels as an N-major
+    operand; see `n_major_supported` for the shapes this covers.
     """
     logger.debug("FLAGGEMS_SGLANG_B200 FUSED_EXPERTS")
     assert inplace is False, "Inplace is not supported"
@@ -183,7 +187,15 @@ def fused_experts(
     dev = _C.require_cuda(hidden_states, w1, w2, topk_weights, topk_ids, w1_scale, w2_scale, expert_map)
     assert hidden_states.ndim == 2, "hidden_states must be 2D"
     T, H = hidden_states.shape
-    E, twoI, Hw = w1.shape
+    if weights_n_major:
+        E, Hw, twoI = w1.shape
+        assert tuple(w2.shape) == (E, twoI // 2, H), "intermediate size mismatch"
+        assert n_major_supported(w1, w2, activation) and b1 is None and b2 is None and not use_fp8_w8a8, \
+            "weights_n_major needs contiguous bf16 weights with H % 32 == 0 and I % 32 == 0, silu or gelu, no bias"
+        assert STAGE_EVENTS is None, "the per-stage profiling path takes [E,2I,H] / [E,H,I] weights only"
+        w2 = w2.transpose(1, 2)  # shape bookkeeping below; the memory is never touched in this order
+    else:
+        E, twoI, Hw = w1.shape
     I = twoI // 2
     assert Hw == H, "hidden size mismatch"
     assert w2.shape[0] == E and w2.shape[1] == H and w2.shape[2] == I, "intermediate size mismatch"
@@ -207,8 +219,9 @@ def fused_experts(
         assert w1.dtype == hidden_states.dtype and w2.dtype == hidden_states.dtype, "w1/w2 dtype must match hidden_states"
     out_dtype = hidden_states.dtype
     x = hidden_states.contiguous()
-    w1 = w1.contiguous()
-    w2 = w2.contiguous()
+    if not weights_n_major:
+        w1 = w1.contiguous()
+        w2 = w2.contiguous()
     wts = topk_weights.float().contiguous()
     ids = topk_ids
     if expert_map is not None:
@@ -241,6 +254,7 @@ def fused_experts(
         out = None if out_rows is not None else torch.empty((T, k, H) if no_combine else (T, H), dtype=out_dtype,
                                                             device=dev)
         fa = _C.FusedArgs(
+            w_layout=_C.W_N_MAJOR if weights_n_major else _C.W_K_MAJOR,
             dtype=_C.E4M3 if use_fp8_w8a8 else _C.DTYPE_CODE[out_dtype], variant=_C.VARIANTS[forced], num_experts=E,
             top_k=k, apply_router_weight_on_input=int(apply_router_weight_on_input), no_combine=int(no_combine),
             zero_dropped=int(expert_map is not None), activation=_C.ACTIVATIONS[activation], T=T, H=H, I=I,
@@ -379,6 +393,17 @@ def fused_moe(
 # --------------------------------------------------------------------------
 # reference-layout entry points
 # --------------------------------------------------------------------------
+def n_major_supported(w1: torch.Tensor, w2: torch.Tensor, activation: str = "silu") -> bool:
+    """True when w1 [E,H,2I] / w2 [E,I,H] can be read in place (no transposed copy): contiguous bf16 tensors whose
+    H and I are multiples of 32 (the tensor-core kernels' column pieces), silu or gelu."""
+    if w1.dtype != torch.bfloat16 or w2.dtype != torch.bfloat16 or w1.ndim != 3 or w2.ndim != 3:
+        return False
+    if not (w1.is_contiguous() and w2.is_contiguous()) or activation not in ("silu", "gelu"):
+        return False
+    H, twoI = w1.shape[1], w1.shape[2]
+    return H % 32 == 0 and twoI % 64 == 0 and w1.data_ptr() % 16 == 0 and w2.data_ptr() % 16 == 0
+
+
 def _k_major(w: torch.Tensor) -> torch.Tensor:
     """[E, K, N] (reference layout) -> [E, N, K] contiguous.  Free when the caller passes
     the transposed view of a serving-side weight, a copy otherwise."""
@@ -444,8 +469,12 @@ def triton_kernel_fused_experts(
     ids_flat[topk_indx] = expert_of_pos.to(torch.int32)
     w_flat = torch.empty(M, dtype=torch.float32, device=dev)
     w_flat[topk_indx] = routing_data.gate_scal.float()
+    # contiguous reference-layout weights (what the reference's own tests and benchmarks pass) are read in place;
+    # transposed views of serving-side weights are used as they are; anything else costs a transposed copy
+    in_place = n_major_supported(w1, w2, activation) and os.environ.get("FMOE_N_MAJOR", "1") != "0"
     z_or_out = fused_experts(
-        hidden_states, _k_major(w1), _k_major(w2), w_flat.view(T, k), ids_flat.view(T, k),
+        hidden_states, w1 if in_place else _k_major(w1), w2 if in_place else _k_major(w2), w_flat.view(T, k),
+        ids_flat.view(T, k), weights_n_major=in_place,
         activation=activation, apply_router_weight_on_input=apply_router_weight_on_input,
         no_combine=scatter_indx is None,
     )

@@ -7,7 +7,9 @@ LAST launches with `fmoe_debug_wait_profile` and prints them per tile (bf16 kern
 accumulator / for TMA data, producer waiting for a free stage, epilogue wait and busy) or per K block (e4m3 kernel:
 fold warps waiting for the MMAs / busy, per tile: wait for staged scales, epilogue).  With `FMOE_TC_DEBUG=1` the bf16
 kernels skip their TMA loads and the MMA warp never waits for data (results are wrong; the time is the pure MMA
-stream); `FMOE_FP8_DEBUG=<bits>` does the same kind of experiment on the e4m3 kernel (see gemm_tcgen05_fp8.cu).
+stream), with bit 1 (`=2`) they issue no MMAs (the TMA ring alone), with bit 2 (`=4`, `=5`) B is read as an N-major
+operand; `FMOE_TC_MAX_CTAS=<n>` caps the grid.  `FMOE_FP8_DEBUG=<bits>` does the same kind of experiment on the e4m3
+kernel (see gemm_tcgen05_fp8.cu).
 Reading the clock inside the e4m3 fold loop distorts it: use those figures for proportions, the stage times for speed.
 """
 from __future__ import annotations
@@ -26,8 +28,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--steps", type=int, default=10)
     args = ap.parse_args()
-    if not (os.environ.get("FMOE_TC_PROFILE") or os.environ.get("FMOE_FP8_DEBUG")):
-        raise SystemExit("set FMOE_TC_PROFILE=1 (counters) or FMOE_FP8_DEBUG=<bits> (timing experiment) first")
+    if not any(os.environ.get(v) for v in ("FMOE_TC_PROFILE", "FMOE_FP8_DEBUG", "FMOE_TC_DEBUG", "FMOE_TC_MAX_CTAS")):
+        raise SystemExit("set FMOE_TC_PROFILE=1 (counters) or FMOE_TC_DEBUG / FMOE_FP8_DEBUG=<bits> / FMOE_TC_MAX_CTAS=<n> "
+                         "(timing experiments) first")
 
     import flaggems_sglang_b200 as fg
     from flaggems_sglang_b200 import _C, workloads as W
@@ -52,7 +55,11 @@ def main():
     torch.cuda.synchronize()
     _C.check_device_status()
     g1, g2 = evs[2].elapsed_time(evs[3]), evs[4].elapsed_time(evs[5])
-    print(f"{cfg.name} T={args.tokens} tcgen05: gate/up GEMM {g1:.3f} ms, down GEMM {g2:.3f} ms (last of {args.steps} calls)")
+    try:
+        mhz = f", SM clock now {torch.cuda.clock_rate()} MHz"
+    except Exception:  # noqa: BLE001  (needs NVML)
+        mhz = ""
+    print(f"{cfg.name} T={args.tokens} tcgen05: gate/up GEMM {g1:.3f} ms, down GEMM {g2:.3f} ms (last of {args.steps} calls){mhz}")
     if not os.environ.get("FMOE_TC_PROFILE"):
         return
     sms = lib.fmoe_sm_count()

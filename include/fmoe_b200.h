@@ -146,10 +146,12 @@ int fmoe_gather_rows(const void* x, int elem_bytes, int64_t rows_out, int64_t K,
  * the two matmul_ogs calls and the activation pass of
  * src/flaggems_sglang/ops/fused_moe.py:205-231.
  */
+#define FMOE_W_K_MAJOR 0
+#define FMOE_W_N_MAJOR 1
 typedef struct fmoe_gemm_args {
   uint32_t struct_size;/* sizeof(fmoe_gemm_args) as the CALLER compiled it; a size the library does not know is
                           refused with FMOE_ERR_INVALID_ARG before any other field is read   */
-  int32_t reserved0;   /* 0                                                               */
+  int32_t w_layout;    /* FMOE_W_K_MAJOR (0) | FMOE_W_N_MAJOR: see `w`                   */
   int32_t dtype;       /* FMOE_F32 | FMOE_BF16 | FMOE_E4M3: type of a and w            */
   int32_t out_dtype;   /* FMOE_F32 | FMOE_BF16 | FMOE_E4M3 (gemm1+TCGEN05 fp8 only)     */
   int32_t variant;     /* FMOE_VARIANT_*                                                 */
@@ -167,7 +169,10 @@ typedef struct fmoe_gemm_args {
   int64_t max_blocks;  /* upper bound on used blocks the launch must cover               */
   const void* a;       /* [a_rows, k]                                                    */
   const float* a_scale;/* e4m3: [a_rows, k/128]                                          */
-  const void* w;       /* gemm1 [E, 2I, H]; gemm2 [E, H, I]; reduction dim contiguous    */
+  const void* w;       /* FMOE_W_K_MAJOR: gemm1 [E, 2I, H]; gemm2 [E, H, I]; reduction dim contiguous (the
+                          serving-side layout).  FMOE_W_N_MAJOR: gemm1 [E, H, 2I]; gemm2 [E, I, H], the layout
+                          the reference operator takes (fused_moe.py:192-199), read in place by the bf16
+                          TCGEN05 kernel as an N-major B operand; other kernels refuse it              */
   const float* w_scale;/* e4m3: [E, rows/128, k/128]                                     */
   const int32_t* sorted_token_ids;
   const int32_t* expert_ids;
@@ -215,7 +220,8 @@ int fmoe_moe_sum_add(const void* z, int dtype, int64_t T, int k, int64_t H, floa
  */
 typedef struct fmoe_fused_args {
   uint32_t struct_size; /* sizeof(fmoe_fused_args) as the caller compiled it (checked like fmoe_gemm_args.struct_size) */
-  int32_t reserved0;    /* 0                                                                              */
+  int32_t w_layout;     /* FMOE_W_K_MAJOR: w1 [E,2I,H], w2 [E,H,I]; FMOE_W_N_MAJOR: w1 [E,H,2I], w2 [E,I,H] (bf16,
+                           TCGEN05 kernels, no bias / swiglu_oai)                                          */
   int32_t dtype;        /* FMOE_F32 | FMOE_BF16: type of hidden/w1/w2/out; FMOE_E4M3: e4m3 weights with
                            128x128 scales, bf16 hidden/out, activations quantised per token per 128 channels */
   int32_t variant;      /* FMOE_VARIANT_* (AUTO: chosen from the shape)                                   */
@@ -258,8 +264,8 @@ int fmoe_fused_experts(const fmoe_fused_args* args, void* stream);
  * reference, which allocates its intermediates with torch on every call.
  *
  * Who needs it: code that runs the layer where cudaMalloc (or any allocator built on it) is off limits —
- * inside a stream capture, on a latency-critical thread that may not take the allocator's locks, or inside
- * a host application that owns all device memory and offers no scratch.  Same arguments and results as
+ * on a latency-critical thread that may not take the allocator's locks, or inside a host application that
+ * owns all device memory and offers no scratch.  Same arguments and results as
  * fmoe_fused_experts, except that `workspace` / `workspace_bytes` are ignored: the intermediates go to an
  * array of FMOE_STATIC_SCRATCH_BYTES that is part of the library image, so every GPU that loads the
  * library gives up that much memory until the process exits.
@@ -267,7 +273,7 @@ int fmoe_fused_experts(const fmoe_fused_args* args, void* stream);
  *   - Problems whose workspace (fmoe_fused_experts_workspace_bytes) exceeds FMOE_STATIC_SCRATCH_BYTES are
  *     refused with FMOE_ERR_UNSUPPORTED; nothing is launched.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
- *     device current) and remembers it.  Make that first call before any stream capture begins.
+ *     device current) and remembers it.
  *   - No cudaMalloc, cudaFree or allocating library routine is called, on the first call or later.
  *   - All calls on a device share the one array, and it keeps whatever the previous call left in it.  The
  *     kernels rewrite every index buffer they read and clear the per-slot outputs when `zero_dropped` is

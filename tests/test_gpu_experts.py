@@ -480,3 +480,45 @@ def test_gpt_oss_layer_shape(fg, T):
     idx = torch.linspace(0, T - 1, min(T, 16)).long().unique()
     ref = OE.fused_experts(x[idx.cuda()].cpu(), w1, w2, tw[idx], ti[idx])
     assert_close_moe(out[idx.cuda()], ref, "bf16", f"gpt-oss shape T={T}")
+
+
+# ------------------------------------------------------------------ weights in the reference operator's own layout
+@pytest.mark.parametrize("on_input", [False, True])
+@pytest.mark.parametrize("T,H,I,E,k", [(1, 256, 128, 8, 2), (40, 320, 192, 8, 2), (300, 352, 96, 8, 2),
+                                       (700, 512, 384, 16, 4), (64, 1280, 3072, 64, 8)])
+def test_reference_layout_weights_read_in_place(fg, T, H, I, E, k, on_input):
+    """w1 [E,H,2I] / w2 [E,I,H] (what the reference's tests and benchmarks pass, ref tests/test_fused_moe.py:64-72)
+    are read in place as an N-major tensor-core operand: same bits as the [E,2I,H] / [E,H,I] kernels, since the
+    products and the accumulation order are the same."""
+    x, w1, w2, logits = _layer(T, H, I, E, k, torch.bfloat16, T + H + I + 1)
+    tw, ti = OR.softmax_topk(logits, k, True)
+    w1n, w2n = w1.cuda().transpose(1, 2).contiguous(), w2.cuda().transpose(1, 2).contiguous()
+    got = fg.fused_experts(x.cuda(), w1n, w2n, tw.cuda(), ti.cuda(), weights_n_major=True,
+                           apply_router_weight_on_input=on_input)
+    same = _run(fg, x, w1, w2, tw, ti, variant="tcgen05", apply_router_weight_on_input=on_input)
+    assert torch.equal(got, same)
+    if T * k * H * I <= 3e9:
+        assert_close_moe(got, OE.fused_experts(x, w1, w2, tw, ti, apply_router_weight_on_input=on_input), "bf16",
+                         f"n-major T={T} H={H} I={I}")
+
+
+def test_reference_entry_point_makes_no_transposed_copy(fg):
+    """`triton_kernel_fused_experts` with contiguous [E,H,2I] / [E,I,H] weights: the peak of device memory during the
+    call stays below the size of one weight tensor (a transposed copy would need both)."""
+    T, H, I, E, k = 128, 1024, 2048, 16, 4
+    x, w1, w2, logits = _layer(T, H, I, E, k, torch.bfloat16, 5)
+    tw, ti = OR.softmax_topk(logits, k, True)
+    xd, w1n, w2n = x.cuda(), w1.cuda().transpose(1, 2).contiguous(), w2.cuda().transpose(1, 2).contiguous()
+    rd, gi, si = fg.standard_topk_to_routing(tw.cuda(), ti.cuda(), E)
+    fg.triton_kernel_fused_experts(xd, w1n, w2n, rd, gi, si)  # first call: lazy initialisation
+    torch.cuda.synchronize()
+    torch.cuda.reset_peak_memory_stats()
+    base = torch.cuda.memory_allocated()
+    out = fg.triton_kernel_fused_experts(xd, w1n, w2n, rd, gi, si)
+    torch.cuda.synchronize()
+    assert torch.cuda.max_memory_allocated() - base < w2n.numel() * 2
+    assert_close_moe(out, OE.fused_experts(x, w1, w2, tw, ti), "bf16", "reference entry, weights in place")
+    # a transposed VIEW of serving-side weights keeps taking the [E,2I,H] kernels, also without a copy
+    torch.cuda.reset_peak_memory_stats()
+    out2 = fg.triton_kernel_fused_experts(xd, w1.cuda().transpose(1, 2), w2.cuda().transpose(1, 2), rd, gi, si)
+    assert_close_moe(out2, OE.fused_experts(x, w1, w2, tw, ti), "bf16", "reference entry, transposed views")

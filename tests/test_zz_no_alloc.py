@@ -3,8 +3,8 @@
 Collected last on purpose (file name): a failure here cannot hide the other GPU tests from a run that
 stops at the first failure.
 
-The entry point is for callers that may not allocate device memory where they run the layer (a stream
-capture in progress, a thread that must not touch the allocator, a host that owns all GPU memory); it keeps
+The entry point is for callers that may not allocate device memory where they run the layer (a thread
+that must not touch the allocator, a host that owns all GPU memory); it keeps
 its intermediates in an array inside the library image.  The test drives both entry points through the
 C ABI with ctypes, twice in a row with different inputs, because the array keeps the previous call's
 contents and the second call must not be affected by them.

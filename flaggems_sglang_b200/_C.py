@@ -52,6 +52,7 @@ class GemmArgs(_SizedStructure):
         ("sorted_token_ids", c_void_p), ("expert_ids", c_void_p), ("num_tokens_post_padded", c_void_p),
         ("row_scale", c_void_p), ("out", c_void_p), ("out_scale", c_void_p),
         ("bias", c_void_p), ("act_alpha", c_float), ("act_limit", c_float), ("out_rows", c_void_p),
+        ("split_ws", c_void_p), ("split_ws_bytes", c_int64),
     ]
 
 
@@ -75,6 +76,7 @@ class FusedArgs(_SizedStructure):
 # name -> (restype, argtypes); every symbol include/fmoe_b200.h declares
 SIGNATURES = {
     "fmoe_version": (c_int, []),
+    "fmoe_gemm_split_workspace_bytes": (c_int64, []),
     "fmoe_last_error": (c_char_p, []),
     "fmoe_sm_count": (c_int, []),
     "fmoe_topk_softmax": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),

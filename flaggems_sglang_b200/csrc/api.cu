@@ -91,7 +91,9 @@ int dispatch_gemm(const fmoe_gemm_args* args, bool gated, void* stream, const ch
 }  // namespace
 }  // namespace fmoe
 
-extern "C" int fmoe_version(void) { return 2; }
+extern "C" int fmoe_version(void) { return 3; }
+
+extern "C" int64_t fmoe_gemm_split_workspace_bytes(void) { return fmoe::gemm_tcgen05_split_workspace_bytes(); }
 
 extern "C" const char* fmoe_last_error(void) { return fmoe::last_error_buffer(); }
 

@@ -108,7 +108,8 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
   p.off_npp = take(16);
   p.align_ws_bytes = fmoe_moe_align_workspace_bytes(p.numel, a.num_experts);
   p.off_align_ws = take(p.align_ws_bytes);
-  p.off_xs = p.off_xs_scale = p.off_xt = p.off_xt_scale = p.off_actq = p.off_actq_scale = -1;
+  p.off_xs = p.off_xs_scale = p.off_xt = p.off_xt_scale = p.off_actq = p.off_actq_scale = p.off_split = -1;
+  p.split_bytes = 0;
   if (fp8) {
     const int64_t xrows = tc ? p.cap : a.T;
     p.off_xs = take(xrows * a.H);
@@ -123,6 +124,10 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
     p.off_actq_scale = take(p.cap * (a.I / 128) * 4);
   } else {
     if (tc && !(tc_gathers_input(p.variant, a.dtype) && !n_major)) p.off_xs = take(p.cap * a.H * eb);
+    if (tc && a.dtype == FMOE_BF16) {
+      p.split_bytes = fmoe_gemm_split_workspace_bytes();
+      p.off_split = take(p.split_bytes);
+    }
     p.act_elem = (int)eb;
     p.off_act = take(p.cap * a.I * eb);
   }
@@ -203,6 +208,10 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
   g.expert_ids = experts;
   g.num_tokens_post_padded = npp;
 
+  if (p.off_split >= 0) {  // both GEMMs use it in turn (stream order)
+    g.split_ws = ws + p.off_split;
+    g.split_ws_bytes = p.split_bytes;
+  }
   fmoe_gemm_args g1 = g, g2 = g;
   g1.n = a.I;
   g1.activation = a.activation;

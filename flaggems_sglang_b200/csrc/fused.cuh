@@ -9,6 +9,7 @@ struct FusedPlan {
   int64_t numel, cap, nblk, max_blocks, total;
   // byte offsets into the workspace (-1: not used)
   int64_t off_sorted, off_expert, off_npp, off_align_ws, align_ws_bytes, off_xs, off_xs_scale, off_xt, off_xt_scale, off_act, off_actq, off_actq_scale, off_z;
+  int64_t off_split, split_bytes;  // tail-split scratch of the bf16 tcgen05 GEMMs
 };
 
 // e4m3 with the tcgen05 kernels: quantise each token row once ([T,H]) and copy bytes and scales into the sorted

@@ -20,6 +20,7 @@ int gemm_tcgen05_fp8(const GemmParams& p, bool gated, cudaStream_t st);
 // true when the variant can run these arguments (shape / alignment / dtype rules)
 bool gemm_stream_supports(const GemmParams& p, bool gated);
 bool gemm_tcgen05_supports(const GemmParams& p, bool gated);
+int64_t gemm_tcgen05_split_workspace_bytes();
 bool gemm_tcgen05_fp8_supports(const GemmParams& p, bool gated);
 
 // Tile order of the persistent kernels: expert by expert, and inside an expert in groups of at most

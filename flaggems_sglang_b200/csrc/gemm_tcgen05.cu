@@ -76,6 +76,9 @@ struct TcParams {
                        // bit 3: every load fetches the first tile (all L2 hits); bit 4: the ring re-arms a stage as soon as
                        // its own data has landed and the MMA warp never waits (both run, uncoupled)
   int32_t ring_depth;  // experiment: stages of the ring in use (default all)
+  float* split_partials;    // tail split: [CTAs][128][256] f32 partial accumulators (NULL: no split)
+  int32_t* split_counters;  // tail split: [CTAs] arrivals per split tile, zero at launch
+  int32_t split_max;        // tail split: most K slices per tile (< 2: no split)
   int32_t top_k;       // gather mode: input row of slot s is s / top_k
   int32_t a_rows;      // gather mode: rows of the input tensor (a row index >= a_rows reads zeros)
 };
@@ -90,6 +93,71 @@ __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity) {
 
 __device__ __forceinline__ bool warp_wait_relaxed(uint64_t* bar, uint32_t parity) {
   return __all_sync(0xffffffffu, ptx::mbar_wait_relaxed(bar, parity));
+}
+
+// Work units of one CTA.  Tiles are dealt round-robin; when the last round has work for at most half of the CTAs
+// (the CTAs are bound by their own rate, so a part-filled round costs as much as a full one), each of its tiles is
+// cut into S slices along K (S a power of two) that S neighbouring CTAs compute.  The S partial accumulators are then
+// summed by all S CTAs together: CTA s owns the s-th strip of the tile's columns, publishes the other strips of its
+// partial in global memory, waits until all S have done so, adds the other CTAs' partials of its strip in slice
+// order (a fixed order: results do not depend on timing) and runs the epilogue on the strip.
+struct UnitPlan {
+  int64_t total, rounds, left;
+  int grid, b, S, k_steps;
+  __device__ __forceinline__ void init(int64_t total_tiles, int k_steps_, int max_split) {
+    total = total_tiles;
+    k_steps = k_steps_;
+    grid = (int)gridDim.x;
+    b = (int)blockIdx.x;
+    S = 1;
+    rounds = (total + grid - 1) / grid;
+    left = total - (rounds - 1) * grid;
+    if (total > 0 && max_split >= 2 && left * 2 <= grid) {
+      int s = (int)min((int64_t)max_split, grid / left);
+      s = min(s, k_steps / 8);
+      while (s & (s - 1)) s &= s - 1;  // largest power of two below
+      if (s >= 2) S = s;
+    }
+  }
+  // unit `it` of this CTA: tile, K steps [ks0, ks1), slice (always 0 for whole tiles); false past the last unit
+  __device__ __forceinline__ bool get(int64_t it, int64_t* tile, int* ks0, int* ks1, int* slice) const {
+    *ks0 = 0;
+    *ks1 = k_steps;
+    *slice = 0;
+    if (S == 1 || it < rounds - 1) {
+      *tile = b + it * grid;
+      return *tile < total;
+    }
+    if (it > rounds - 1 || b >= left * S) return false;
+    *tile = (rounds - 1) * grid + b / S;
+    *slice = b % S;
+    *ks0 = (int)((int64_t)k_steps * *slice / S);
+    *ks1 = (int)((int64_t)k_steps * (*slice + 1) / S);
+    return true;
+  }
+  __device__ __forceinline__ bool is_split(int64_t it) const { return S > 1 && it == rounds - 1; }
+};
+
+__device__ __forceinline__ void store_partial32(const uint32_t (&r)[32], float* dst) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q)
+    __stcg(reinterpret_cast<float4*>(dst) + q, make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                           __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
+}
+__device__ __forceinline__ void add_partial32(uint32_t (&r)[32], const float* src) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    const float4 v = __ldcg(reinterpret_cast<const float4*>(src) + q);
+    r[4 * q] = __float_as_uint(__uint_as_float(r[4 * q]) + v.x);
+    r[4 * q + 1] = __float_as_uint(__uint_as_float(r[4 * q + 1]) + v.y);
+    r[4 * q + 2] = __float_as_uint(__uint_as_float(r[4 * q + 2]) + v.z);
+    r[4 * q + 3] = __float_as_uint(__uint_as_float(r[4 * q + 3]) + v.w);
+  }
+}
+__device__ __forceinline__ int32_t ld_acquire_gpu(const int32_t* p) {
+  int32_t v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
 }
 
 // GATHER: the A operand is the un-permuted [a_rows, K] input; the producer warp fetches row
@@ -148,6 +216,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
   TileCursor cursor;
   const int k_steps = p.k_steps;
+  UnitPlan plan;
+  plan.init(total_tiles, k_steps, p.split_partials ? min(p.split_max, GATED ? 4 : 8) : 0);
 
   if (warp == 4) {
     // ---------------- TMA producer ----------------
@@ -177,13 +247,16 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const uint64_t pol_w = ptx::l2_policy_evict_first(), pol_a = ptx::l2_policy_evict_last();
     int32_t row_a = 0, row_b0 = 0, row_b1 = 0, nrow_a = 0, nrow_b0 = 0, nrow_b1 = 0;
     int4 src_rows = make_int4(0, 0, 0, 0), nsrc_rows = src_rows;
-    if ((int64_t)blockIdx.x < total_tiles) {
-      tile_rows(blockIdx.x, &row_a, &row_b0, &row_b1);
+    int64_t tile, ntile;
+    int ks0, ks1, slice, nks0 = 0, nks1 = 0, nslice;
+    bool have = plan.get(0, &tile, &ks0, &ks1, &slice);
+    if (have) {
+      tile_rows(tile, &row_a, &row_b0, &row_b1);
       if constexpr (GATHER) src_rows = lane_rows(row_a);
     }
-    for (int64_t tile = blockIdx.x; tile < total_tiles && alive && !(p.debug & 1); tile += gridDim.x) {
-      const bool has_next = tile + gridDim.x < total_tiles;
-      for (int ks = 0; ks < k_steps; ++ks) {
+    for (int64_t it = 0; have && alive && !(p.debug & 1); ++it) {
+      const bool has_next = plan.get(it + 1, &ntile, &nks0, &nks1, &nslice);
+      for (int ks = ks0; ks < ks1; ++ks) {
         const long long tp0 = p.profile ? clock64() : 0;
         const bool okp = warp_wait((p.debug & 16) ? &full_bar[stage] : &empty_bar[stage], phase ^ 1);
         if (p.profile) prof_a += clock64() - tp0;
@@ -221,8 +294,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           ptx::tma_gather4_2d(smem + stage * STAGE_BYTES + lane * (4 * KBYTES), &map_a, ks * (KBYTES / 2), src_rows.x,
                               src_rows.y, src_rows.z, src_rows.w, &full_bar[stage]);
         }
-        if (ks == 0 && has_next) {
-          tile_rows(tile + gridDim.x, &nrow_a, &nrow_b0, &nrow_b1);
+        if (ks == ks0 && has_next) {
+          tile_rows(ntile, &nrow_a, &nrow_b0, &nrow_b1);
           if constexpr (GATHER) nsrc_rows = lane_rows(nrow_a);
         }
         if (++stage == p.ring_depth) {
@@ -234,6 +307,9 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       row_b0 = nrow_b0;
       row_b1 = nrow_b1;
       src_rows = nsrc_rows;
+      have = has_next;
+      ks0 = nks0;
+      ks1 = nks1;
     }
     if (p.profile && lane == 0 && blockIdx.x < 256) g_wait_prof[blockIdx.x * 8 + 3] = prof_a;
     // drain: do not leave while our own bulk copies may still be landing in shared memory
@@ -259,7 +335,9 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     int local = 0;
     bool alive = true;
     long long prof_acc = 0, prof_data = 0;
-    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+    int64_t tile;
+    int ks0, ks1, slice;
+    for (int64_t it = 0; alive && plan.get(it, &tile, &ks0, &ks1, &slice); ++it) {
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       ++local;
@@ -273,7 +351,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       }
       ptx::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + acc * BN;
-      for (int ks = 0; ks < k_steps; ++ks) {
+      for (int ks = ks0; ks < ks1; ++ks) {
         const long long tm1 = p.profile ? clock64() : 0;
         const bool okd = (p.debug & 17) ? true : warp_wait(&full_bar[stage], phase);
         if (p.profile) prof_data += clock64() - tm1;
@@ -291,7 +369,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const uint64_t dbn = ptx::smem_desc_sw128_lbo(sa + A_BYTES, B_BYTES / 4, 1024);
 #pragma unroll
             for (int kk = 0; kk < KBYTES / 32; ++kk)
-              ptx::mma_f16_ss(d_tmem, da + 2 * kk, dbn + (2048 >> 4) * kk, idesc, (ks | kk) != 0);
+              ptx::mma_f16_ss(d_tmem, da + 2 * kk, dbn + (2048 >> 4) * kk, idesc, ((ks - ks0) | kk) != 0);
             ptx::mma_commit(&empty_bar[stage]);
           } else if (p.debug & 2) {
             ptx::mbar_arrive(&empty_bar[stage]);
@@ -301,13 +379,13 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             const uint64_t dbn = ptx::smem_desc_sw128_lbo(sa + A_BYTES, 8192, 1024);
 #pragma unroll
             for (int kk = 0; kk < KBYTES / 32; ++kk)
-              ptx::mma_f16_ss(d_tmem, da + 2 * kk, dbn + 128 * kk, idesc | (1u << 16), (ks | kk) != 0);
+              ptx::mma_f16_ss(d_tmem, da + 2 * kk, dbn + 128 * kk, idesc | (1u << 16), ((ks - ks0) | kk) != 0);
             if (!(p.debug & 1)) ptx::mma_commit(&empty_bar[stage]);
           } else {
 #pragma unroll
             for (int kk = 0; kk < KBYTES / 32; ++kk) {
               // 32 bytes of K per MMA (16 bf16): advance the start address by 32 B = 2 units
-              ptx::mma_f16_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, (ks | kk) != 0);
+              ptx::mma_f16_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, ((ks - ks0) | kk) != 0);
             }
             if (!(p.debug & 17)) ptx::mma_commit(&empty_bar[stage]);  // stage is free once these MMAs have read it
           }
@@ -332,7 +410,9 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     bool alive = true;
     long long prof_wait = 0, prof_busy = 0;
     const int row = warp * 32 + lane;
-    for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x) {
+    int64_t tile;
+    int ks0, ks1, slice;
+    for (int64_t it = 0; alive && plan.get(it, &tile, &ks0, &ks1, &slice); ++it) {
       int m_blk, n_tile, tile_e;
       cursor.locate(tile, p.n_tiles, p.group_m, p.num_experts, p.expert_ids, expert_table, &m_blk, &n_tile, &tile_e);
       const int acc = local & 1;
@@ -358,14 +438,62 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       }
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(warp * 32) << 16);
+      // tail split: this CTA runs the epilogue on chunks [c_begin, c_end) of the tile's columns (32 accumulator
+      // columns per chunk; gated: gate chunk c and up chunk c together); bufs + o * BM * BN is row `row` of the
+      // partial accumulator that slice o published
+      constexpr int NCH = GATED ? 4 : 8;
+      const bool split = plan.is_split(it);
+      const int S = split ? plan.S : 1;
+      const int c_begin = slice * NCH / S, c_end = (slice + 1) * NCH / S;
+      const int tail_index = plan.b / plan.S;
+      const float* bufs = p.split_partials + ((int64_t)tail_index * S * BM + row) * BN;
+      if (split) {
+        float* mine = p.split_partials + (((int64_t)tail_index * S + slice) * BM + row) * BN;
+#pragma unroll 1
+        for (int c = 0; c < NCH; ++c) {
+          if (c >= c_begin && c < c_end) continue;
+          uint32_t r[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
+          ptx::tmem_ld_wait();
+          store_partial32(r, mine + c * 32);
+          if constexpr (GATED) {
+            ptx::tmem_ld_32x32b_x32(taddr + 128 + c * 32, r);
+            ptx::tmem_ld_wait();
+            store_partial32(r, mine + 128 + c * 32);
+          }
+        }
+        __threadfence();  // the strips are visible device-wide before this warp counts as arrived
+        __syncwarp();
+        if (lane == 0) atomicAdd(p.split_counters + tail_index, 1);
+        // every epilogue warp of every slice has published: 4 * S arrivals
+        const long long t0 = clock64();
+        bool ok = true;
+        while (ld_acquire_gpu(p.split_counters + tail_index) < 4 * S) {
+          if (clock64() - t0 > 2000000000ll) {
+            ok = false;
+            break;
+          }
+          __nanosleep(64);
+        }
+        if (!__all_sync(0xffffffffu, ok)) {
+          report(0x380 | acc);
+          alive = false;
+          break;
+        }
+      }
       if constexpr (GATED) {
         __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(p.out) + pos * p.n + (int64_t)n_tile * 128;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = c_begin; c < c_end; ++c) {
           uint32_t g[32], u[32];
           ptx::tmem_ld_32x32b_x32(taddr + c * 32, g);
           ptx::tmem_ld_32x32b_x32(taddr + 128 + c * 32, u);
           ptx::tmem_ld_wait();
+          for (int o = 0; o < S; ++o) {
+            if (o == slice) continue;
+            add_partial32(g, bufs + (int64_t)o * BM * BN + c * 32);
+            add_partial32(u, bufs + (int64_t)o * BM * BN + 128 + c * 32);
+          }
           // the last column tile of an intermediate size that is not a multiple of 128 is cut at I (its surplus
           // accumulator columns hold products with rows of W that belong to the up half or to the next expert)
           if (pos < p.sorted_cap && (int64_t)n_tile * 128 + c * 32 < p.n) {
@@ -412,10 +540,12 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                                             : reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)slot * p.n;
         __nv_bfloat16* orow = obase + (int64_t)n_tile * 256;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = c_begin; c < c_end; ++c) {
           uint32_t r[32];
           ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
           ptx::tmem_ld_wait();
+          for (int o = 0; o < S; ++o)
+            if (o != slice) add_partial32(r, bufs + (int64_t)o * BM * BN + c * 32);
           if (obase && (int64_t)n_tile * 256 + c * 32 < p.n) {
             uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
 #pragma unroll
@@ -495,6 +625,11 @@ int device_sm_count() {
   std::lock_guard<std::mutex> lock(mu);
   if (sm_count[dev] == 0) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
   return sm_count[dev];
+}
+
+int64_t gemm_tcgen05_split_workspace_bytes() {
+  const int sms = device_sm_count();
+  return 1024 + (int64_t)std::min(std::max(sms, 1), 256) * BM * BN * 4;
 }
 
 // 2-D row-major [rows, cols] tensor of `elem_bytes` elements; box = kbytes (128 or 64) x box_rows, swizzle of the same width.
@@ -583,6 +718,18 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.profile = getenv("FMOE_TC_PROFILE") != nullptr;
   p.debug = getenv("FMOE_TC_DEBUG") ? atoi(getenv("FMOE_TC_DEBUG")) : 0;
   p.l2_hints = getenv("FMOE_TC_L2_HINTS") ? atoi(getenv("FMOE_TC_L2_HINTS")) : 0;
+  // tail split: counters (1 KB, cleared before every launch) + one 128x256 f32 partial per CTA
+  p.split_partials = nullptr;
+  p.split_counters = nullptr;
+  p.split_max = 0;
+  const char* split_env = getenv("FMOE_TC_SPLIT_TAIL");  // "0": off (read per launch, tests flip it)
+  const bool split_off = split_env && atoi(split_env) == 0;
+  if (g.split_ws && !split_off && g.split_ws_bytes >= gemm_tcgen05_split_workspace_bytes() && aligned16(g.split_ws)) {
+    p.split_counters = reinterpret_cast<int32_t*>(g.split_ws);
+    p.split_partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(g.split_ws) + 1024);
+    p.split_max = 8;
+    FMOE_CUDA_OK(cudaMemsetAsync(g.split_ws, 0, 1024, st));
+  }
   p.ring_depth = Ring<KB>::STAGES;
   if (const char* d = getenv("FMOE_TC_RING_DEPTH")) p.ring_depth = std::max(1, std::min(Ring<KB>::STAGES, atoi(d)));
   grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA, BNMAJ><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);

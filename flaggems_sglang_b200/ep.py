@@ -275,6 +275,7 @@ class PeerExchange:
         else:
             self.act = torch.empty(cap, self.I, dtype=self.dtype, device=dev)
         self._z_local = None  # [capacity, H], allocated on first use of the separate return
+        self._split_ws = None  # tail-split scratch of the bf16 tcgen05 GEMMs, allocated on first use
 
     @classmethod
     def emulated(cls, world: int, max_tokens: int, top_k: int, hidden_size: int, dtype=torch.bfloat16,
@@ -402,6 +403,10 @@ def p2p_experts(xc: PeerExchange, state: dict, w1_local, w2_local, fuse_return: 
                   block_size=blk, numel=cap, sorted_cap=cap, max_blocks=cap // blk, a_gather=0, a_rows=cap,
                   sorted_token_ids=xc.sorted_ids.data_ptr(), expert_ids=xc.expert_ids.data_ptr(),
                   num_tokens_post_padded=xc.npp.data_ptr())
+    if xc.variant == "tcgen05" and not xc.fp8:
+        if xc._split_ws is None:
+            xc._split_ws = torch.empty(int(lib.fmoe_gemm_split_workspace_bytes()), dtype=torch.uint8, device=xc.device)
+        common.update(split_ws=xc._split_ws.data_ptr(), split_ws_bytes=xc._split_ws.numel())
     row_w = xc.weights.data_ptr()
     act_code = _C.DTYPE_CODE[xc.act.dtype]
     g1 = _C.GemmArgs(dtype=code, out_dtype=act_code, n=xc.I, k=xc.H, a=xc.rows.data_ptr(), a_scale=_C.ptr(xc.scales),

@@ -283,6 +283,10 @@ def fused_experts(
     common = dict(variant=vcode, activation=_C.ACTIVATIONS[activation], num_experts=E, top_k=k, block_size=block, numel=numel, sorted_cap=cap,
                   max_blocks=max_blocks, sorted_token_ids=sorted_ids.data_ptr(), expert_ids=expert_ids.data_ptr(),
                   num_tokens_post_padded=num_post.data_ptr())
+    if name == "tcgen05" and not use_fp8_w8a8:
+        # the scratch that lets the kernel cut the tiles of a part-filled last round along K, as the one-call path has
+        split_ws = torch.empty(int(lib.fmoe_gemm_split_workspace_bytes()), dtype=torch.uint8, device=dev)
+        common.update(split_ws=split_ws.data_ptr(), split_ws_bytes=split_ws.numel())
 
     # Z holds one output row per flat slot; slots that no kernel writes (dropped ids) must read as zero
     z_alloc = torch.zeros if expert_map is not None else torch.empty

@@ -50,7 +50,7 @@ extern "C" {
 #define FMOE_VARIANT_STREAM 2  /* small-M weight-streaming kernel, split-K over warps */
 #define FMOE_VARIANT_TCGEN05 3 /* TMA + tcgen05/TMEM persistent kernel for large M */
 
-/* ABI version: 2 = argument structs begin with struct_size. */
+/* ABI version: 2 = argument structs begin with struct_size; 3 = fmoe_gemm_args ends with split_ws / split_ws_bytes. */
 int fmoe_version(void);
 /* Message of the last error returned on the calling thread ("" if none). */
 const char* fmoe_last_error(void);
@@ -189,7 +189,13 @@ typedef struct fmoe_gemm_args {
                             at out_rows[slot] instead of out + slot*H (NULL entry: row skipped).  The
                             addresses may be peer memory (expert-parallel combine fused into the
                             epilogue).  STREAM and TCGEN05 variants only.                          */
+  void* split_ws;        /* optional scratch of fmoe_gemm_split_workspace_bytes() bytes (16-byte aligned, contents
+                            irrelevant): lets the bf16 TCGEN05 kernel cut the tiles of a part-filled last round
+                            along K over the idle CTAs.  NULL: every tile is computed by one CTA.  Results are
+                            deterministic either way but differ in the last bits between the two.        */
+  int64_t split_ws_bytes;
 } fmoe_gemm_args;
+int64_t fmoe_gemm_split_workspace_bytes(void);
 
 /* gemm1: out[p, c] = act(acc[p, c]) * acc[p, I + c], acc = (a_row(p) . w[e(p)]^T) * row_scale. */
 int fmoe_gemm1_silu(const fmoe_gemm_args* args, void* stream);

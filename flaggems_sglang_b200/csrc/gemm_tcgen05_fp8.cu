@@ -20,6 +20,8 @@
 //               (the kernel runs at its 96-register limit, every spill lands in the fold loop).
 // Same tile schedule, bounded waits and status word as the bf16 kernel; cluster size 1, every CTA loads its own tiles.
 #include "gemm.cuh"
+
+#include <type_traits>
 #include "ptx_sm100.cuh"
 
 #include <cstdlib>
@@ -39,20 +41,21 @@ namespace {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int KBYTES = 128;
-// Three 48 KB stages: the kernel is bound by its fold warps, not by TMA latency, and the space is better spent on
-// the staged scales.
-constexpr int STAGES = 3;
+// Ring of NS 48 KB stages (template parameter of the kernel): four when both scale buffers still fit beside them
+// (short reductions), else three.  The kernel is bound by its fold warps and by the shared-memory traffic of TMA
+// fill + MMA operand reads, not by TMA latency: the fourth stage gains 3 %.
+constexpr int kMaxStages = 4;
 constexpr int A_BYTES = BM * KBYTES;
 constexpr int B_BYTES = BN * KBYTES;
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLS = 512;
 constexpr int kEpiWarps = 16;
 constexpr int kThreads = (kEpiWarps + 4) * 32;
-constexpr int SMEM_BASE_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int kMaxSmem = 227 * 1024;
 constexpr int kMaxStagedKBlocks = 64;  // two scale buffers of (128 + 2) * kblocks floats + 16 bytes must fit beside the ring
 constexpr int scale_buf_bytes(int kblocks) { return (BM + 2) * kblocks * 4 + 16; }
-constexpr int smem_bytes(int kblocks, int num_experts) {
-  return SMEM_BASE_BYTES + expert_table_bytes(num_experts) + 2 * scale_buf_bytes(kblocks);
+constexpr int smem_bytes(int stages, int nbuf, int kblocks, int num_experts) {
+  return stages * STAGE_BYTES + 1024 + 256 + expert_table_bytes(num_experts) + nbuf * scale_buf_bytes(kblocks);
 }
 
 struct Fp8Params {
@@ -75,6 +78,7 @@ struct Fp8Params {
   int32_t activation;
   int32_t group_m;
   int32_t spin;   // 1: the partial hand-overs are polled with test_wait instead of try_wait
+  int32_t nbuf;        // scale buffers in shared memory: 2 (a tile's scales are staged while the previous tile folds) or 1
   int32_t debug;  // instrumented build only, timing experiments (results are wrong): bit 0 = the fold skips the TMEM
                   // read-out and the FMAs, bit 1 = no MMAs are issued, bit 2 = read-out without FMAs
 };
@@ -106,12 +110,13 @@ __device__ __forceinline__ void unpack2(unsigned long long v, float& a, float& b
 
 // MODE 0: production.  MODE 1: instrumented build with wait-time counters (reading the clock is slow enough to distort
 // the fold loop; use it for proportions only).  MODE 2: timing experiments selected by Fp8Params::debug, no counters.
-template <bool GATED, int MODE>
+template <bool GATED, int MODE, int NS>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                                 const Fp8Params p) {
   constexpr bool PROF = MODE == 1;
   constexpr bool DBG = MODE == 2;
+  constexpr int STAGES = NS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -265,11 +270,11 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     bool alive = true;
     long long prof_fw = 0, prof_fb = 0, prof_sw = 0, prof_epi = 0;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++ltile) {
-      const int tb = (int)(ltile & 1);
+      const int tb = (int)(ltile % p.nbuf);
       const float* s_a = reinterpret_cast<const float*>(scale_base + tb * scale_buf_bytes(kblocks)) + row;
       const float* s_w = reinterpret_cast<const float*>(scale_base + tb * scale_buf_bytes(kblocks)) + BM * kblocks;
       const long long tq0 = PROF ? clock64() : 0;
-      if (!warp_wait(&scale_full[tb], (ltile >> 1) & 1)) {
+      if (!warp_wait(&scale_full[tb], (ltile / p.nbuf) & 1)) {
         report(0x740 | tb);
         alive = false;
         break;
@@ -394,10 +399,10 @@ grouped_gemm_tcgen05_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const
     uint32_t ltile = 0;
     bool alive = true;
     for (int64_t tile = blockIdx.x; tile < total_tiles && alive; tile += gridDim.x, ++ltile) {
-      const int tb = (int)(ltile & 1);
+      const int tb = (int)(ltile % p.nbuf);
       int m_blk, n_tile, e;
       cursor.locate(tile, p.n_tiles, p.group_m, p.num_experts, p.expert_ids, expert_table, &m_blk, &n_tile, &e);
-      if (!warp_wait(&scale_empty[tb], ((ltile >> 1) & 1) ^ 1)) {
+      if (!warp_wait(&scale_empty[tb], ((ltile / p.nbuf) & 1) ^ 1)) {
         report(0x780 | tb);
         alive = false;
         break;
@@ -470,18 +475,18 @@ int device_sm_count();
 
 namespace {
 
-template <bool GATED, int MODE>
-int launch(const GemmParams& g, cudaStream_t st) {
-  constexpr int MAX_SMEM = smem_bytes(kMaxStagedKBlocks, 1024);
-  static_assert(MAX_SMEM <= 227 * 1024, "scale buffers do not fit beside the ring");
+template <bool GATED, int MODE, int NS>
+int launch(const GemmParams& g, int nbuf, cudaStream_t st) {
+  constexpr int MAX_SMEM = kMaxSmem;
+  static_assert(smem_bytes(3, 2, kMaxStagedKBlocks, 1024) <= kMaxSmem, "scale buffers do not fit beside the ring");
   static PerDeviceOnce once_attr;  // the opt-in to > 48 KB of dynamic shared memory is per device
   const cudaError_t attr_err = per_device_once(once_attr, [] {
-    return cudaFuncSetAttribute(grouped_gemm_tcgen05_fp8_kernel<GATED, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                MAX_SMEM);
+    return cudaFuncSetAttribute(grouped_gemm_tcgen05_fp8_kernel<GATED, MODE, NS>,
+                                cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
   });
   if (attr_err != cudaSuccess)
     return fail(FMOE_ERR_CUDA, "cudaFuncSetAttribute(smem=%d) failed: %s", MAX_SMEM, cudaGetErrorString(attr_err));
-  const int SMEM_BYTES = smem_bytes((int)(g.k / 128), g.num_experts);
+  const int SMEM_BYTES = smem_bytes(NS, nbuf, (int)(g.k / 128), g.num_experts);
   const int64_t w_rows = GATED ? 2 * g.n : g.n;
   CUtensorMap map_a, map_b;
   int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 1, BM, false, 128);
@@ -506,6 +511,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.n_tiles = (int)ceil_div<int64_t>(g.n, GATED ? 128 : 256);
   p.max_blocks = (int)g.max_blocks;
   p.activation = g.activation;
+  p.nbuf = nbuf;
   p.spin = getenv("FMOE_FP8_SPIN") ? atoi(getenv("FMOE_FP8_SPIN")) : 0;
   p.debug = (MODE == 2 && getenv("FMOE_FP8_DEBUG")) ? atoi(getenv("FMOE_FP8_DEBUG")) : 0;
 
@@ -513,7 +519,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
   const int sms = device_sm_count();
   const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sms > 0 ? sms : 148, max_tiles));
   p.group_m = pick_group_m(BM, g.k);
-  grouped_gemm_tcgen05_fp8_kernel<GATED, MODE><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
+  grouped_gemm_tcgen05_fp8_kernel<GATED, MODE, NS><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_fp8_kernel");
 }
 
@@ -551,9 +557,25 @@ int gemm_tcgen05_fp8(const GemmParams& p, bool gated, cudaStream_t st) {
                 "k a multiple of 128 up to 8192");
   if (p.max_blocks <= 0) return FMOE_OK;
   static const int mode = getenv("FMOE_FP8_DEBUG") ? 2 : (getenv("FMOE_TC_PROFILE") ? 1 : 0);
-  if (mode == 2) return gated ? launch<true, 2>(p, st) : launch<false, 2>(p, st);
-  if (mode == 1) return gated ? launch<true, 1>(p, st) : launch<false, 1>(p, st);
-  return gated ? launch<true, 0>(p, st) : launch<false, 0>(p, st);
+  // ring depth and scale buffers by what fits in shared memory (FMOE_FP8_STAGES=3 forces the three-stage ring)
+  const int kblocks = (int)(p.k / 128);
+  const char* force = getenv("FMOE_FP8_STAGES");
+  int stages = 3, nbuf = 2;
+  if (!(force && atoi(force) == 3)) {
+    // measured on DeepSeek-V3 T=16384: down GEMM (K = 2048) 3.89 -> 3.78 ms with the fourth stage; the gate/up GEMM
+    // (K = 7168) has room for it only with a single scale buffer and was slower that way (5.94 -> 6.27 ms)
+    if (smem_bytes(4, 2, kblocks, p.num_experts) <= kMaxSmem) stages = 4;
+  }
+  auto go = [&](auto gated_c, auto mode_c) {
+    constexpr bool G = decltype(gated_c)::value;
+    constexpr int M = decltype(mode_c)::value;
+    return stages == 4 ? launch<G, M, 4>(p, nbuf, st) : launch<G, M, 3>(p, nbuf, st);
+  };
+  using T = std::true_type;
+  using F = std::false_type;
+  if (mode == 2) return gated ? go(T{}, std::integral_constant<int, 2>{}) : go(F{}, std::integral_constant<int, 2>{});
+  if (mode == 1) return gated ? go(T{}, std::integral_constant<int, 1>{}) : go(F{}, std::integral_constant<int, 1>{});
+  return gated ? go(T{}, std::integral_constant<int, 0>{}) : go(F{}, std::integral_constant<int, 0>{});
 }
 
 }  // namespace fmoe

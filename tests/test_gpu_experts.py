@@ -335,6 +335,26 @@ def test_fp8_tcgen05_both_input_quant_routes(fg, H):
     assert_close_moe(out, ref, "fp8", f"fp8 H={H}")
 
 
+@pytest.mark.parametrize("H,I", [(512, 256), (7168, 256)])
+def test_fp8_tcgen05_ring_depths_agree(fg, monkeypatch, H, I):
+    """The e4m3 tensor-core kernel runs a four-stage ring when the staged scales fit beside it (two scale buffers
+    for short reductions, one for long ones such as H = 7168) and a three-stage ring otherwise; the depth changes the
+    timing only, so the results are the same bits."""
+    T, E, k = 300, 8, 2
+    x, w1, w2, logits = _layer(T, H, I, E, k, torch.bfloat16, 78)
+    w1q, w1s = OQ.quant_weight_block128(w1)
+    w2q, w2s = OQ.quant_weight_block128(w2)
+    tw, ti = OR.softmax_topk(logits, k, True)
+    args = (x.cuda(), w1q.cuda(), w2q.cuda(), tw.cuda(), ti.cuda())
+    kw = dict(use_fp8_w8a8=True, w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), block_shape=[128, 128], variant="tcgen05")
+    out4 = fg.fused_experts(*args, **kw)
+    monkeypatch.setenv("FMOE_FP8_STAGES", "3")
+    out3 = fg.fused_experts(*args, **kw)
+    assert torch.equal(out4, out3)
+    if H <= 512:
+        assert_close_moe(out4, OE.fused_experts_fp8(x, w1q, w1s, w2q, w2s, tw, ti), "fp8", f"fp8 ring depth H={H}")
+
+
 def test_fp8_quantise_once_then_copy_equals_quantising_sorted_rows(fg):
     from flaggems_sglang_b200 import _C
 

@@ -18,6 +18,7 @@ OK, ERR_INVALID_ARG, ERR_CUDA, ERR_UNSUPPORTED, ERR_DEVICE_TIMEOUT = 0, 1, 2, 3,
 F32, BF16, E4M3 = 0, 1, 2
 VARIANT_AUTO, VARIANT_SIMT, VARIANT_STREAM, VARIANT_TCGEN05 = 0, 1, 2, 3
 W_K_MAJOR, W_N_MAJOR = 0, 1
+SCALE_BLOCK128, SCALE_CHANNEL = 0, 1
 VARIANTS = {"auto": 0, "simt": 1, "stream": 2, "tcgen05": 3}
 ACTIVATIONS = {"silu": 0, "gelu": 1, "swiglu_oai": 2}
 VARIANT_NAMES = {v: k for k, v in VARIANTS.items()}
@@ -52,7 +53,7 @@ class GemmArgs(_SizedStructure):
         ("sorted_token_ids", c_void_p), ("expert_ids", c_void_p), ("num_tokens_post_padded", c_void_p),
         ("row_scale", c_void_p), ("out", c_void_p), ("out_scale", c_void_p),
         ("bias", c_void_p), ("act_alpha", c_float), ("act_limit", c_float), ("out_rows", c_void_p),
-        ("split_ws", c_void_p), ("split_ws_bytes", c_int64),
+        ("split_ws", c_void_p), ("split_ws_bytes", c_int64), ("scale_mode", c_int32), ("reserved1", c_int32),
     ]
 
 
@@ -65,7 +66,7 @@ class FusedArgs(_SizedStructure):
         ("apply_router_weight_on_input", c_int32), ("no_combine", c_int32), ("zero_dropped", c_int32),
         ("activation", c_int32),
         ("T", c_int64), ("H", c_int64), ("I", c_int64),
-        ("routed_scaling_factor", c_float), ("reserved_f", c_float),
+        ("routed_scaling_factor", c_float), ("scale_mode", c_int32),
         ("hidden", c_void_p), ("w1", c_void_p), ("w2", c_void_p), ("w1_scale", c_void_p), ("w2_scale", c_void_p),
         ("topk_weights", c_void_p), ("topk_ids", c_void_p), ("out", c_void_p), ("workspace", c_void_p),
         ("workspace_bytes", c_int64), ("b1", c_void_p), ("b2", c_void_p), ("act_alpha", c_float),
@@ -89,6 +90,8 @@ SIGNATURES = {
                                              c_void_p, c_void_p, c_int64, c_void_p]),
     "fmoe_quant_fp8_group128": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p,
                                         c_void_p, c_void_p, c_void_p]),
+    "fmoe_quant_fp8_per_token": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p,
+                                         c_void_p, c_void_p, c_void_p]),
     "fmoe_gather_rows": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p, c_void_p,
                                  c_void_p]),
     "fmoe_gemm1_silu": (c_int, [POINTER(GemmArgs), c_void_p]),

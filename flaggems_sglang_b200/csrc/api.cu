@@ -47,7 +47,15 @@ int validate_gemm(const GemmParams& a, bool gated, const char* who) {
                  "%s: out_rows is taken by gemm2 with the STREAM or TCGEN05 variant only", who);
   if (a.dtype == FMOE_E4M3) {
     FMOE_REQUIRE(a.a_scale && a.w_scale, "%s: e4m3 needs a_scale and w_scale", who);
-    FMOE_REQUIRE(a.k % 128 == 0 && a.n % 128 == 0, "%s: e4m3 needs k and n to be multiples of 128", who);
+    FMOE_REQUIRE(a.scale_mode == FMOE_SCALE_BLOCK128 || a.scale_mode == FMOE_SCALE_CHANNEL, "%s: unknown scale_mode %d",
+                 who, a.scale_mode);
+    if (a.scale_mode == FMOE_SCALE_CHANNEL) {
+      if (a.variant != FMOE_VARIANT_AUTO && a.variant != FMOE_VARIANT_TCGEN05)
+        return fail(FMOE_ERR_UNSUPPORTED, "%s: per-channel e4m3 scales are taken by the TCGEN05 kernel only", who);
+      FMOE_REQUIRE(a.k % 16 == 0 && a.n % 32 == 0, "%s: per-channel e4m3 needs k %% 16 == 0 and n %% 32 == 0", who);
+    } else {
+      FMOE_REQUIRE(a.k % 128 == 0 && a.n % 128 == 0, "%s: e4m3 needs k and n to be multiples of 128", who);
+    }
   }
   if (!a.a_gather)
     FMOE_REQUIRE(a.a_rows >= a.max_blocks * a.block_size, "%s: a has %lld rows, the launch covers %lld", who,
@@ -69,7 +77,7 @@ int dispatch_gemm(const fmoe_gemm_args* args, bool gated, void* stream, const ch
   if (a.max_blocks == 0 || a.numel == 0) return FMOE_OK;
   auto st = (cudaStream_t)stream;
   int variant = a.variant;
-  if (a.w_layout == FMOE_W_N_MAJOR) {
+  if (a.w_layout == FMOE_W_N_MAJOR || (a.dtype == FMOE_E4M3 && a.scale_mode == FMOE_SCALE_CHANNEL)) {
     variant = FMOE_VARIANT_TCGEN05;
   } else if (variant == FMOE_VARIANT_AUTO) {
     if (gemm_tcgen05_supports(a, gated) || gemm_tcgen05_fp8_supports(a, gated))
@@ -83,7 +91,8 @@ int dispatch_gemm(const fmoe_gemm_args* args, bool gated, void* stream, const ch
     case FMOE_VARIANT_SIMT: return gemm_simt(a, gated, st);
     case FMOE_VARIANT_STREAM: return gemm_stream(a, gated, st);
     case FMOE_VARIANT_TCGEN05:
-      return a.dtype == FMOE_E4M3 ? gemm_tcgen05_fp8(a, gated, st) : gemm_tcgen05(a, gated, st);
+      return (a.dtype == FMOE_E4M3 && a.scale_mode == FMOE_SCALE_BLOCK128) ? gemm_tcgen05_fp8(a, gated, st)
+                                                                           : gemm_tcgen05(a, gated, st);
   }
   return fail(FMOE_ERR_INVALID_ARG, "%s: unknown variant %d", who, a.variant);
 }
@@ -91,7 +100,7 @@ int dispatch_gemm(const fmoe_gemm_args* args, bool gated, void* stream, const ch
 }  // namespace
 }  // namespace fmoe
 
-extern "C" int fmoe_version(void) { return 3; }
+extern "C" int fmoe_version(void) { return 4; }
 
 extern "C" int64_t fmoe_gemm_split_workspace_bytes(void) { return fmoe::gemm_tcgen05_split_workspace_bytes(); }
 

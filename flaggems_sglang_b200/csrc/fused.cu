@@ -78,8 +78,19 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
   if (a.b1 || a.b2 || a.activation == FMOE_ACT_SWIGLU_OAI)
     FMOE_REQUIRE(a.dtype != FMOE_E4M3,
                  "fused_experts: bias and the swiglu_oai activation are not available with e4m3 weights");
-  if (a.dtype == FMOE_E4M3)
-    FMOE_REQUIRE(a.H % 128 == 0 && a.I % 128 == 0, "fused_experts: e4m3 needs H and I to be multiples of 128");
+  const bool channel = a.dtype == FMOE_E4M3 && a.scale_mode == FMOE_SCALE_CHANNEL;
+  if (a.dtype == FMOE_E4M3) {
+    FMOE_REQUIRE(a.scale_mode == FMOE_SCALE_BLOCK128 || a.scale_mode == FMOE_SCALE_CHANNEL,
+                 "fused_experts: unknown scale_mode %d", a.scale_mode);
+    if (channel) {
+      FMOE_REQUIRE(a.H % 32 == 0 && a.I % 32 == 0 && a.H <= 16384 && a.I <= 16384,
+                   "fused_experts: per-channel e4m3 needs H and I to be multiples of 32, up to 16384");
+      if (a.variant != FMOE_VARIANT_AUTO && a.variant != FMOE_VARIANT_TCGEN05)
+        return fail(FMOE_ERR_UNSUPPORTED, "fused_experts: per-channel e4m3 runs on the TCGEN05 kernels only");
+    } else {
+      FMOE_REQUIRE(a.H % 128 == 0 && a.I % 128 == 0, "fused_experts: e4m3 needs H and I to be multiples of 128");
+    }
+  }
   FMOE_REQUIRE(a.w_layout == FMOE_W_K_MAJOR || a.w_layout == FMOE_W_N_MAJOR, "fused_experts: unknown w_layout %d", a.w_layout);
   const bool n_major = a.w_layout == FMOE_W_N_MAJOR;
   if (n_major && (a.dtype != FMOE_BF16 || a.b1 || a.b2 || a.activation == FMOE_ACT_SWIGLU_OAI ||
@@ -88,8 +99,14 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
                 "kernels, no bias and no swiglu_oai");
   FusedPlan& p = *pl;
   p.numel = a.T * a.top_k;
-  int rc = pick_variant(a.dtype, p.numel, a.num_experts, a.I, a.H, n_major ? FMOE_VARIANT_TCGEN05 : a.variant, &p.variant,
-                        &p.block);
+  int rc = FMOE_OK;
+  if (channel) {  // one kernel family: bf16-style tcgen05 pipeline on e4m3 operands, 128-row blocks
+    p.variant = FMOE_VARIANT_TCGEN05;
+    p.block = 128;
+  } else {
+    rc = pick_variant(a.dtype, p.numel, a.num_experts, a.I, a.H, n_major ? FMOE_VARIANT_TCGEN05 : a.variant, &p.variant,
+                      &p.block);
+  }
   if (rc) return rc;
   p.cap = p.numel + (int64_t)a.num_experts * (p.block - 1);
   p.nblk = ceil_div<int64_t>(p.cap, p.block);
@@ -110,7 +127,17 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
   p.off_align_ws = take(p.align_ws_bytes);
   p.off_xs = p.off_xs_scale = p.off_xt = p.off_xt_scale = p.off_actq = p.off_actq_scale = p.off_split = -1;
   p.split_bytes = 0;
-  if (fp8) {
+  if (channel) {
+    // every sorted row is quantised with its own scale; the activation likewise
+    p.off_xs = take(p.cap * a.H);
+    p.off_xs_scale = take(p.cap * 4);
+    p.act_elem = 2;
+    p.off_act = take(p.cap * a.I * 2);
+    p.off_actq = take(p.cap * a.I);
+    p.off_actq_scale = take(p.cap * 4);
+    p.split_bytes = fmoe_gemm_split_workspace_bytes();
+    p.off_split = take(p.split_bytes);
+  } else if (fp8) {
     const int64_t xrows = tc ? p.cap : a.T;
     p.off_xs = take(xrows * a.H);
     p.off_xs_scale = take(xrows * (a.H / 128) * 4);
@@ -251,7 +278,11 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
   } else {
     void* xq = ws + p.off_xs;
     float* xsc = reinterpret_cast<float*>(ws + p.off_xs_scale);
-    if (tc && p.off_xt >= 0) {
+    const bool channel = a.scale_mode == FMOE_SCALE_CHANNEL;
+    g1.scale_mode = g2.scale_mode = a.scale_mode;
+    if (channel) {
+      rc = fmoe_quant_fp8_per_token(a.hidden, FMOE_BF16, p.cap, a.H, sorted, a.top_k, p.numel, npp, xq, xsc, stream);
+    } else if (tc && p.off_xt >= 0) {
       void* xt = ws + p.off_xt;
       float* xtsc = reinterpret_cast<float*>(ws + p.off_xt_scale);
       rc = fmoe_quant_fp8_group128(a.hidden, FMOE_BF16, a.T, a.H, nullptr, 1, 0, nullptr, xt, xtsc, stream);
@@ -281,8 +312,12 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
   mark(3);
   if (fp8) {
     // padding positions of the sorted order (most of the rows at small T) are zero-filled, not quantised
-    rc = fmoe_quant_fp8_group128(act, g1.out_dtype, p.cap, a.I, sorted, 0, p.numel, npp, ws + p.off_actq,
-                                 reinterpret_cast<float*>(ws + p.off_actq_scale), stream);
+    if (a.scale_mode == FMOE_SCALE_CHANNEL)
+      rc = fmoe_quant_fp8_per_token(act, FMOE_BF16, p.cap, a.I, sorted, 0, p.numel, npp, ws + p.off_actq,
+                                    reinterpret_cast<float*>(ws + p.off_actq_scale), stream);
+    else
+      rc = fmoe_quant_fp8_group128(act, g1.out_dtype, p.cap, a.I, sorted, 0, p.numel, npp, ws + p.off_actq,
+                                   reinterpret_cast<float*>(ws + p.off_actq_scale), stream);
     if (rc) return rc;
   }
   mark(4);

@@ -55,6 +55,8 @@ struct TcParams {
   const int32_t* expert_ids;
   const int32_t* num_tokens_post_padded;
   const float* row_scale;
+  const float* a_scale;   // F8: [rows] f32, one scale per (sorted) input row
+  const float* w_scale;   // F8: [E, w_rows] f32, one scale per output channel
   const float* bias;      // optional [E, w_rows] f32
   float act_alpha, act_limit;
   void* out;
@@ -170,7 +172,10 @@ __device__ __forceinline__ int32_t ld_acquire_gpu(const int32_t* p) {
 // (128 bytes, one swizzle atom wide) from a 3-D map [E, K, N]: K rows past the expert's last and columns past N are
 // zero-filled by TMA.  In shared memory the boxes are 8 KB apart (the descriptor's leading byte offset), groups of
 // 8 K rows 1 KB apart (its stride byte offset), and one MMA's 16 K rows are 2 KB.
-template <bool GATED, int KB, bool GATHER, bool EXTRA, bool BNMAJ>
+// F8: e4m3 operands with per-row activation scales and per-output-channel weight scales (per-channel w8a8): the
+// same pipeline with 128 K elements per stage and kind::f8f6f4 MMAs; the scales multiply the finished accumulator
+// in the epilogue, so nothing is folded per K block.
+template <bool GATED, int KB, bool GATHER, bool EXTRA, bool BNMAJ, bool F8>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                             const TcParams p) {
@@ -269,7 +274,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           ptx::mbar_arrive_expect_tx(&full_bar[stage], STAGE_BYTES);
-          const int32_t x = ks * (KBYTES / 2);  // element coordinate (bf16)
+          const int32_t x = ks * (KBYTES / (F8 ? 1 : 2));  // element coordinate
           if (p.debug & 8) row_a = row_b0 = row_b1 = 0;  // experiment: every CTA loads the same tiles (L2 hits)
           if constexpr (BNMAJ) {
             ptx::tma_load_2d(sa, &map_a, x, row_a, &full_bar[stage]);
@@ -329,7 +334,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     }
   } else if (warp == 5) {
     // ---------------- MMA issuer ----------------
-    constexpr uint32_t idesc = ptx::make_idesc(/*bf16*/ 1, BM, BN) | (BNMAJ ? (1u << 16) : 0u);  // bit 16: B is N-major
+    constexpr uint32_t idesc =
+        ptx::make_idesc(F8 ? /*e4m3*/ 0 : /*bf16*/ 1, BM, BN) | (BNMAJ ? (1u << 16) : 0u);  // bit 16: B is N-major
     int stage = 0;
     uint32_t phase = 0;
     int local = 0;
@@ -365,7 +371,12 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           const uint32_t sa = ptx::smem_u32(smem + stage * STAGE_BYTES);
           const uint64_t da = ptx::smem_desc_sw128(sa);
           const uint64_t db = ptx::smem_desc_sw128(sa + A_BYTES);
-          if constexpr (BNMAJ) {
+          if constexpr (F8) {
+#pragma unroll
+            for (int kk = 0; kk < KBYTES / 32; ++kk)  // 32 bytes of K per MMA (32 e4m3)
+              ptx::mma_f8f6f4_ss(d_tmem, da + 2 * kk, db + 2 * kk, idesc, ((ks - ks0) | kk) != 0);
+            ptx::mma_commit(&empty_bar[stage]);
+          } else if constexpr (BNMAJ) {
             const uint64_t dbn = ptx::smem_desc_sw128_lbo(sa + A_BYTES, B_BYTES / 4, 1024);
 #pragma unroll
             for (int kk = 0; kk < KBYTES / 32; ++kk)
@@ -421,7 +432,9 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       const int64_t pos = (int64_t)m_blk * BM + row;
       const int32_t slot = (pos < p.sorted_cap) ? p.sorted_token_ids[pos] : -1;
       const bool valid = slot >= 0 && slot < p.numel;
-      const float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
+      float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
+      if constexpr (F8) rs *= (pos < p.sorted_cap) ? p.a_scale[pos] : 0.f;  // activation scale of this sorted row
+      const float* wsc = F8 ? p.w_scale + (int64_t)tile_e * p.w_rows + (int64_t)n_tile * (GATED ? 128 : 256) : nullptr;
       // bias entries of this tile's columns (the same for every row: broadcast loads)
       const float* bias = (EXTRA && p.bias)
                               ? p.bias + (int64_t)tile_e * p.w_rows +
@@ -503,9 +516,11 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
               uint32_t w[4];
               // bias of the 8 gate and 8 up columns of this piece: four 16-byte broadcast loads
               float bgv[8], buv[8];
-              if (EXTRA && bias) {
-                const float4* pg = reinterpret_cast<const float4*>(bias + c * 32 + v * 8);
-                const float4* pu = reinterpret_cast<const float4*>(bias + p.n + c * 32 + v * 8);
+              if ((EXTRA && bias) || F8) {
+                // bias (EXTRA) or channel scales (F8) of the 8 gate and 8 up columns: 16-byte broadcast loads
+                const float* vec = F8 ? wsc : bias;
+                const float4* pg = reinterpret_cast<const float4*>(vec + c * 32 + v * 8);
+                const float4* pu = reinterpret_cast<const float4*>(vec + p.n + c * 32 + v * 8);
                 const float4 g0 = __ldg(pg), g1 = __ldg(pg + 1), u0 = __ldg(pu), u1 = __ldg(pu + 1);
                 bgv[0] = g0.x; bgv[1] = g0.y; bgv[2] = g0.z; bgv[3] = g0.w;
                 bgv[4] = g1.x; bgv[5] = g1.y; bgv[6] = g1.z; bgv[7] = g1.w;
@@ -524,6 +539,12 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
                                           p.activation, p.act_alpha, p.act_limit);
                   o1 = gated_output<true>(__uint_as_float(g[i + 1]), __uint_as_float(u[i + 1]), bgv[2 * j + 1],
                                           buv[2 * j + 1], rs, p.activation, p.act_alpha, p.act_limit);
+                } else if constexpr (F8) {
+                  // (accumulator * row scale) * channel scale, then the activation
+                  o0 = act_mul_fast(__uint_as_float(g[i]) * rs * bgv[2 * j], __uint_as_float(u[i]) * rs * buv[2 * j],
+                                    p.activation);
+                  o1 = act_mul_fast(__uint_as_float(g[i + 1]) * rs * bgv[2 * j + 1],
+                                    __uint_as_float(u[i + 1]) * rs * buv[2 * j + 1], p.activation);
                 } else {
                   o0 = act_mul_fast(__uint_as_float(g[i]) * rs, __uint_as_float(u[i]) * rs, p.activation);
                   o1 = act_mul_fast(__uint_as_float(g[i + 1]) * rs, __uint_as_float(u[i + 1]) * rs, p.activation);
@@ -552,8 +573,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
             for (int v = 0; v < 4; ++v) {
               uint32_t w[4];
               float bv[8];
-              if (EXTRA && bias) {
-                const float4* pb = reinterpret_cast<const float4*>(bias + c * 32 + v * 8);
+              if ((EXTRA && bias) || F8) {
+                const float4* pb = reinterpret_cast<const float4*>((F8 ? wsc : bias) + c * 32 + v * 8);
                 const float4 b0 = __ldg(pb), b1 = __ldg(pb + 1);
                 bv[0] = b0.x; bv[1] = b0.y; bv[2] = b0.z; bv[3] = b0.w;
                 bv[4] = b1.x; bv[5] = b1.y; bv[6] = b1.z; bv[7] = b1.w;
@@ -564,7 +585,10 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int i = v * 8 + j * 2;
-                w[j] = pack_bf16x2((__uint_as_float(r[i]) + bv[2 * j]) * rs, (__uint_as_float(r[i + 1]) + bv[2 * j + 1]) * rs);
+                if constexpr (F8)
+                  w[j] = pack_bf16x2(__uint_as_float(r[i]) * rs * bv[2 * j], __uint_as_float(r[i + 1]) * rs * bv[2 * j + 1]);
+                else
+                  w[j] = pack_bf16x2((__uint_as_float(r[i]) + bv[2 * j]) * rs, (__uint_as_float(r[i + 1]) + bv[2 * j + 1]) * rs);
               }
               dst[v] = make_uint4(w[0], w[1], w[2], w[3]);
             }
@@ -667,15 +691,16 @@ int make_tensor_map_nmajor(CUtensorMap* map, const void* base, int64_t experts, 
 
 namespace {
 
-template <bool GATED, int KB, bool GATHER, bool EXTRA, bool BNMAJ = false>
+template <bool GATED, int KB, bool GATHER, bool EXTRA, bool BNMAJ = false, bool F8 = false>
 int launch(const GemmParams& g, cudaStream_t st) {
+  constexpr int ELEM = F8 ? 1 : 2;
   constexpr int KBYTES = KB;
   constexpr int MAX_SMEM = Ring<KB>::SMEM_BYTES + expert_table_bytes(1024);
   const int SMEM_BYTES = Ring<KB>::SMEM_BYTES + expert_table_bytes(g.num_experts);
   const int sm_count = device_sm_count();
   static PerDeviceOnce once_attr;  // the opt-in to > 48 KB of dynamic shared memory is per device
   const cudaError_t attr_err = per_device_once(once_attr, [] {
-    return cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA, BNMAJ>,
+    return cudaFuncSetAttribute(grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA, BNMAJ, F8>,
                                 cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
   });
   if (attr_err != cudaSuccess)
@@ -683,10 +708,10 @@ int launch(const GemmParams& g, cudaStream_t st) {
 
   const int64_t w_rows = GATED ? 2 * g.n : g.n;
   CUtensorMap map_a, map_b;
-  int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, 2, GATHER ? 1 : BM, false, KB);
+  int rc = make_tensor_map_2d(&map_a, g.a, g.a_rows, g.k, ELEM, GATHER ? 1 : BM, false, KB);
   if (rc) return rc;
   if constexpr (BNMAJ) rc = make_tensor_map_nmajor(&map_b, g.w, g.num_experts, g.k, w_rows);
-  else rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, 2, 128, true, KB);
+  else rc = make_tensor_map_2d(&map_b, g.w, (int64_t)g.num_experts * w_rows, g.k, ELEM, 128, true, KB);
   if (rc) return rc;
 
   TcParams p;
@@ -694,6 +719,8 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.expert_ids = g.expert_ids;
   p.num_tokens_post_padded = g.num_tokens_post_padded;
   p.row_scale = g.row_scale;
+  p.a_scale = g.a_scale;
+  p.w_scale = g.w_scale;
   p.bias = g.bias;
   p.act_alpha = g.act_alpha;
   p.act_limit = g.act_limit;
@@ -704,7 +731,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.w_rows = w_rows;
   p.sorted_cap = g.sorted_cap;
   p.num_experts = g.num_experts;
-  p.k_steps = (int)ceil_div<int64_t>(g.k * 2, KBYTES);
+  p.k_steps = (int)ceil_div<int64_t>(g.k * ELEM, KBYTES);
   p.n_tiles = (int)ceil_div<int64_t>(g.n, GATED ? 128 : 256);
   p.max_blocks = (int)g.max_blocks;
   p.activation = g.activation;
@@ -714,7 +741,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
   const int64_t max_tiles = g.max_blocks * p.n_tiles;
   unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>(sm_count > 0 ? sm_count : 148, max_tiles));
   if (const char* cap = getenv("FMOE_TC_MAX_CTAS")) grid = std::max(1u, std::min(grid, (unsigned)atoi(cap)));  // experiment
-  p.group_m = pick_group_m(BM, g.k * 2);
+  p.group_m = pick_group_m(BM, g.k * ELEM);
   p.profile = getenv("FMOE_TC_PROFILE") != nullptr;
   p.debug = getenv("FMOE_TC_DEBUG") ? atoi(getenv("FMOE_TC_DEBUG")) : 0;
   p.l2_hints = getenv("FMOE_TC_L2_HINTS") ? atoi(getenv("FMOE_TC_L2_HINTS")) : 0;
@@ -732,14 +759,19 @@ int launch(const GemmParams& g, cudaStream_t st) {
   }
   p.ring_depth = Ring<KB>::STAGES;
   if (const char* d = getenv("FMOE_TC_RING_DEPTH")) p.ring_depth = std::max(1, std::min(Ring<KB>::STAGES, atoi(d)));
-  grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA, BNMAJ><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
+  grouped_gemm_tcgen05_kernel<GATED, KB, GATHER, EXTRA, BNMAJ, F8><<<grid, kThreads, SMEM_BYTES, st>>>(map_a, map_b, p);
   return launch_status("grouped_gemm_tcgen05_kernel");
 }
 
 }  // namespace
 
 bool gemm_tcgen05_supports(const GemmParams& p, bool gated) {
-  if (p.dtype != FMOE_BF16 || p.out_dtype != FMOE_BF16) return false;
+  const bool f8 = p.dtype == FMOE_E4M3 && p.scale_mode == FMOE_SCALE_CHANNEL;
+  if ((p.dtype != FMOE_BF16 && !f8) || p.out_dtype != FMOE_BF16) return false;
+  // e4m3 with per-row / per-channel scales: plain kernels, K-major weights, sorted input rows
+  if (f8 && (p.a_gather || p.bias || p.w_layout != FMOE_W_K_MAJOR || !p.a_scale || !p.w_scale || !aligned16(p.w_scale) ||
+             (gated && p.activation == FMOE_ACT_SWIGLU_OAI)))
+    return false;
   if (p.block_size != BM) return false;
   // gather mode: gate/up GEMM only; one int4 of sorted ids per lane
   if (p.a_gather && (!gated || p.top_k < 1 || !aligned16(p.sorted_token_ids))) return false;
@@ -747,7 +779,7 @@ bool gemm_tcgen05_supports(const GemmParams& p, bool gated) {
   // weights in the reference operator's [E, K, N] layout: plain kernels only (no row gather, bias or swiglu_oai)
   if (p.w_layout == FMOE_W_N_MAJOR && (p.a_gather || p.bias || (gated && p.activation == FMOE_ACT_SWIGLU_OAI))) return false;
   if (p.bias && !aligned16(p.bias)) return false;  // 16-byte bias loads in the epilogue (n % 32 == 0 holds already)
-  if (p.k <= 0 || (p.k * 2) % 16 != 0) return false;            // TMA row stride must be a multiple of 16 bytes
+  if (p.k <= 0 || (p.k * (f8 ? 1 : 2)) % 16 != 0) return false;  // TMA row stride must be a multiple of 16 bytes
   if (p.n <= 0 || p.n % 32 != 0) return false;  // 64-byte epilogue stores; column tiles are cut at n in 32-column pieces
   if (!aligned16(p.a) || !aligned16(p.w) || !(aligned16(p.out) && (p.out || (!gated && p.out_rows)))) return false;
   if ((int64_t)p.num_experts * (gated ? 2 * p.n : p.n) >= (1ll << 31) || p.a_rows >= (1ll << 31)) return false;
@@ -758,11 +790,13 @@ bool gemm_tcgen05_supports(const GemmParams& p, bool gated) {
 int gemm_tcgen05(const GemmParams& p, bool gated, cudaStream_t st) {
   if (!gemm_tcgen05_supports(p, gated))
     return fail(FMOE_ERR_UNSUPPORTED,
-                "tcgen05 gemm: needs bf16 in/out, block_size 128, input-row gather only for the gate/up gemm, "
+                "tcgen05 gemm: needs bf16 in/out (or e4m3 in with per-channel scales), block_size 128, input-row gather only for the gate/up gemm, "
                 "n %% %d == 0, 16-byte aligned pointers (got dtype=%d block=%d a_gather=%d n=%lld k=%lld)",
                 32, p.dtype, p.block_size, p.a_gather, (long long)p.n, (long long)p.k);
   if (p.max_blocks <= 0) return FMOE_OK;
   const bool extra = p.bias != nullptr || (gated && p.activation == FMOE_ACT_SWIGLU_OAI);
+  if (p.dtype == FMOE_E4M3)
+    return gated ? launch<true, 128, false, false, false, true>(p, st) : launch<false, 128, false, false, false, true>(p, st);
   if (p.w_layout == FMOE_W_N_MAJOR)
     return gated ? launch<true, 128, false, false, true>(p, st) : launch<false, 128, false, false, true>(p, st);
   if (p.a_gather) return extra ? launch<true, 128, true, true>(p, st) : launch<true, 128, true, false>(p, st);

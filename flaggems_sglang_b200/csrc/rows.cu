@@ -119,6 +119,86 @@ quant_group128_kernel(const InT* __restrict__ x, int64_t rows_out, int64_t K, co
   }
 }
 
+// Per-token dynamic quantisation to e4m3 with ONE scale per row (the activation side of per-channel w8a8): a CTA per
+// output row, the row held in registers between the amax pass and the conversion (bf16 rows up to kRowVecs * 256 * 8
+// = 16384 channels).  scale = max(amax / 448, 1 / (448 * 512)), q = rne(x / scale) saturated: the rule of vLLM's
+// dynamic per-token quantiser.
+constexpr int kRowVecs = 8;
+__global__ void __launch_bounds__(256)
+quant_row_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows_out, int64_t K, const int32_t* __restrict__ row_map,
+                 int map_div, int64_t sentinel, const int32_t* __restrict__ num_rows_dev, uint8_t* __restrict__ q,
+                 float* __restrict__ scale) {
+  pdl_entry();
+  __shared__ float s_max[8];
+  const int64_t limit = num_rows_dev ? min((int64_t)*num_rows_dev, rows_out) : rows_out;
+  const int vecs = (int)(K / 8);  // 16-byte vectors per row
+  for (int64_t p = blockIdx.x; p < limit; p += gridDim.x) {
+    const int64_t r = mapped_row(row_map, map_div, sentinel, p);
+    uint2* dst = reinterpret_cast<uint2*>(q + p * K);
+    if (r < 0) {  // padding position: zeros with a unit scale
+      for (int c = threadIdx.x; c < vecs; c += 256) dst[c] = make_uint2(0, 0);
+      if (threadIdx.x == 0) scale[p] = 1.0f;
+      continue;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(x + r * K);
+    uint4 raw[kRowVecs];
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < kRowVecs; ++i) {
+      const int c = threadIdx.x + i * 256;
+      raw[i] = make_uint4(0, 0, 0, 0);
+      if (c < vecs) {
+        raw[i] = __ldg(src + c);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fmaxf(fabsf(__low2float(h[j])), fabsf(__high2float(h[j]))));
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    __syncthreads();  // s_max of the previous row has been read by everyone
+    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = s_max[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_max[w]);
+    const float s = fmaxf(__fdiv_rn(amax, 448.0f), 1.0f / (448.0f * 512.0f));
+    const float rcp = __frcp_rn(s);
+    const bool finite = amax <= 3.0e38f;
+#pragma unroll
+    for (int i = 0; i < kRowVecs; ++i) {
+      const int c = threadIdx.x + i * 256;
+      if (c >= vecs) continue;
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[2 * j] = __low2float(h[j]);
+        v[2 * j + 1] = __high2float(h[j]);
+      }
+      uint32_t lo = 0, hi = 0;
+      if (finite) {
+        float qv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) qv[j] = div_by_shared(v[j], s, rcp);
+        auto pair = [](float a, float b) {
+          return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+        };
+        lo = pair(qv[0], qv[1]) | (pair(qv[2], qv[3]) << 16);
+        hi = pair(qv[4], qv[5]) | (pair(qv[6], qv[7]) << 16);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          lo |= (uint32_t)f32_to_e4m3_bits(__fdiv_rn(v[j], s)) << (8 * j);
+          hi |= (uint32_t)f32_to_e4m3_bits(__fdiv_rn(v[4 + j], s)) << (8 * j);
+        }
+      }
+      dst[c] = make_uint2(lo, hi);
+    }
+    if (threadIdx.x == 0) scale[p] = s;
+  }
+}
+
 __global__ void __launch_bounds__(256)
 gather_rows_kernel(const uint4* __restrict__ x, int64_t rows_out, int64_t vec_per_row,
                    const int32_t* __restrict__ row_map, int map_div, int64_t sentinel,
@@ -193,6 +273,23 @@ extern "C" int fmoe_quant_fp8_group128(const void* x, int in_dtype, int64_t rows
     launch_pdl(quant_group128_kernel<float>, dim3(grid), dim3(256), 0, st, (const float*)x, rows_out, K, row_map,
                map_div, map_sentinel, num_rows_dev, (uint8_t*)q, scale);
   return launch_status("quant_group128_kernel");
+}
+
+extern "C" int fmoe_quant_fp8_per_token(const void* x, int in_dtype, int64_t rows_out, int64_t K,
+                                        const int32_t* row_map, int map_div, int64_t map_sentinel,
+                                        const int32_t* num_rows_dev, void* q, float* scale, void* stream) {
+  using namespace fmoe;
+  FMOE_REQUIRE(K > 0 && K % 8 == 0 && K <= (int64_t)kRowVecs * 256 * 8,
+               "quant_fp8_per_token: K must be a multiple of 8 up to %d (got %lld)", kRowVecs * 256 * 8, (long long)K);
+  FMOE_REQUIRE(in_dtype == FMOE_BF16, "quant_fp8_per_token: in_dtype must be bf16");
+  FMOE_REQUIRE(!row_map || map_div >= 0, "quant_fp8_per_token: map_div must be >= 0");
+  if (rows_out <= 0) return FMOE_OK;
+  FMOE_REQUIRE(x && q && scale, "quant_fp8_per_token: null pointer");
+  FMOE_REQUIRE(aligned16(x) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0, "quant_fp8_per_token: misaligned pointer");
+  unsigned grid = (unsigned)std::min<int64_t>(rows_out, 148 * 8);
+  launch_pdl(quant_row_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, rows_out, K,
+             row_map, map_div, map_sentinel, num_rows_dev, (uint8_t*)q, scale);
+  return launch_status("quant_row_kernel");
 }
 
 extern "C" int fmoe_gather_rows(const void* x, int elem_bytes, int64_t rows_out, int64_t K,

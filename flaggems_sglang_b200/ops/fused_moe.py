@@ -163,7 +163,9 @@ def fused_experts(
     topk_weights [T,k] float; topk_ids [T,k] int.  bf16 (or fp32) weights, or
     e4m3 weights with `use_fp8_w8a8=True`, `block_shape=[128,128]` and fp32
     block scales `w1_scale [E,2I/128,H/128]`, `w2_scale [E,H/128,I/128]`
-    (activations are quantised per token per 128 channels on the fly).
+    (activations are quantised per token per 128 channels on the fly), or with
+    `per_channel_quant=True` (no `block_shape`): `w1_scale [E,2I]`, `w2_scale [E,H]`, one scale per output
+    channel, activations quantised with one dynamic scale per token (tensor-core kernels only).
     Returns [T,H] (or [T,k,H] with `no_combine`).  `expert_map` maps global to
     local expert ids (-1 = not on this rank; such slots contribute zeros).
     `out_rows` (with `no_combine`): int64 [T*k] device addresses; the result row of every slot is stored
@@ -179,7 +181,6 @@ def fused_experts(
     """
     logger.debug("FLAGGEMS_SGLANG_B200 FUSED_EXPERTS")
     assert inplace is False, "Inplace is not supported"
-    assert per_channel_quant is False, _UNSUPPORTED_FEATURE_MSG.format(name="per_channel_quant")
     assert a1_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="a1_scale")
     assert a2_scale is None, _UNSUPPORTED_FEATURE_MSG.format(name="a2_scale")
     if activation not in _C.ACTIVATIONS:
@@ -203,7 +204,20 @@ def fused_experts(
     k = topk_ids.shape[1]
     numel = T * k
 
-    if use_fp8_w8a8:
+    if per_channel_quant:
+        # one scale per output channel of the weights, one dynamic scale per activation row
+        assert use_fp8_w8a8, "per_channel_quant needs use_fp8_w8a8=True"
+        assert block_shape is None, "per_channel_quant and block_shape are mutually exclusive"
+        assert w1.dtype == torch.float8_e4m3fn and w2.dtype == torch.float8_e4m3fn, "fp8 weights must be e4m3"
+        assert w1_scale is not None and w2_scale is not None, "fp8 needs w1_scale and w2_scale"
+        assert hidden_states.dtype == torch.bfloat16, "hidden_states must be bfloat16"
+        assert H % 32 == 0 and I % 32 == 0, "per-channel fp8 needs H and I to be multiples of 32"
+        assert w1_scale.numel() == E * twoI and w2_scale.numel() == E * H, "w1_scale must be [E,2I], w2_scale [E,H]"
+        assert b1 is None and b2 is None and activation != "swiglu_oai", "bias / swiglu_oai are not available with fp8"
+        assert STAGE_EVENTS is None, "the per-stage profiling path does not take per-channel fp8"
+        w1_scale = w1_scale.float().reshape(E, twoI).contiguous()
+        w2_scale = w2_scale.float().reshape(E, H).contiguous()
+    elif use_fp8_w8a8:
         assert block_shape is not None and list(block_shape) == [128, 128], "fp8 needs block_shape=[128, 128]"
         assert w1.dtype == torch.float8_e4m3fn and w2.dtype == torch.float8_e4m3fn, "fp8 weights must be e4m3"
         assert w1_scale is not None and w2_scale is not None, "fp8 needs w1_scale and w2_scale"
@@ -255,6 +269,7 @@ def fused_experts(
                                                             device=dev)
         fa = _C.FusedArgs(
             w_layout=_C.W_N_MAJOR if weights_n_major else _C.W_K_MAJOR,
+            scale_mode=_C.SCALE_CHANNEL if per_channel_quant else _C.SCALE_BLOCK128,
             dtype=_C.E4M3 if use_fp8_w8a8 else _C.DTYPE_CODE[out_dtype], variant=_C.VARIANTS[forced], num_experts=E,
             top_k=k, apply_router_weight_on_input=int(apply_router_weight_on_input), no_combine=int(no_combine),
             zero_dropped=int(expert_map is not None), activation=_C.ACTIVATIONS[activation], T=T, H=H, I=I,

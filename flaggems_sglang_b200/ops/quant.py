@@ -45,4 +45,29 @@ def quant_weight_block128(w: torch.Tensor):
     return q.to(torch.float8_e4m3fn), scale.contiguous()
 
 
-__all__ = ["per_token_group_quant_fp8", "quant_weight_block128"]
+def per_token_quant_fp8(x: torch.Tensor):
+    """x [rows, K] bf16 -> (q e4m3 [rows, K], scale f32 [rows]): one dynamic scale per row,
+    scale = max(amax / 448, 1 / (448 * 512)); CUDA kernel.  The activation side of per-channel w8a8."""
+    dev = _C.require_cuda(x)
+    if x.dim() != 2 or x.dtype != torch.bfloat16:
+        raise ValueError("x must be a 2-D bf16 tensor")
+    x = x.contiguous()
+    rows, K = x.shape
+    q = torch.empty(rows, K, dtype=torch.float8_e4m3fn, device=dev)
+    s = torch.empty(rows, dtype=torch.float32, device=dev)
+    _C.check(_C.lib().fmoe_quant_fp8_per_token(x.data_ptr(), _C.BF16, rows, K, None, 1, 0, None, q.data_ptr(),
+                                               s.data_ptr(), _C.stream_ptr(dev)))
+    return q, s
+
+
+def quant_weight_per_channel(w: torch.Tensor):
+    """One-time weight preparation (torch ops): w [..., N, K] -> (q e4m3, scale f32 [..., N]),
+    one scale per output channel, scale = amax(row)/448 (1 for an all-zero row)."""
+    wf = w.float()
+    amax = wf.abs().amax(dim=-1)
+    scale = torch.where(amax > 0, amax / torch.full_like(amax, FP8_MAX), torch.ones_like(amax))
+    qv = (wf / scale[..., None]).clamp(-FP8_MAX, FP8_MAX)
+    return qv.to(torch.float8_e4m3fn), scale.contiguous()
+
+
+__all__ = ["per_token_group_quant_fp8", "quant_weight_block128", "per_token_quant_fp8", "quant_weight_per_channel"]

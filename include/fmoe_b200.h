@@ -50,7 +50,8 @@ extern "C" {
 #define FMOE_VARIANT_STREAM 2  /* small-M weight-streaming kernel, split-K over warps */
 #define FMOE_VARIANT_TCGEN05 3 /* TMA + tcgen05/TMEM persistent kernel for large M */
 
-/* ABI version: 2 = argument structs begin with struct_size; 3 = fmoe_gemm_args ends with split_ws / split_ws_bytes. */
+/* ABI version: 2 = argument structs begin with struct_size; 3 = fmoe_gemm_args ends with split_ws / split_ws_bytes;
+ * 4 = ... and scale_mode / reserved1; fmoe_fused_args.scale_mode takes the place of a reserved word. */
 int fmoe_version(void);
 /* Message of the last error returned on the calling thread ("" if none). */
 const char* fmoe_last_error(void);
@@ -131,6 +132,14 @@ int fmoe_moe_align_block_size_ws(const int32_t* topk_ids, int64_t numel, int E, 
 int fmoe_quant_fp8_group128(const void* x, int in_dtype, int64_t rows_out, int64_t K,
                             const int32_t* row_map, int map_div, int64_t map_sentinel,
                             const int32_t* num_rows_dev, void* q, float* scale, void* stream);
+/* Per-row dynamic quantisation with ONE scale per row (the activation side of per-channel w8a8, SURVEY of the
+ * reference: `per_channel_quant`, src/flaggems_sglang/ops/fused_moe.py:160, asserted off there at :173-175):
+ *   x [rows_in, K] bf16, K % 8 == 0, K <= 16384; q [rows_out, K] e4m3; scale [rows_out] f32,
+ *   scale = max(amax / 448, 1 / (448 * 512)), q = rne(x / scale) saturated to +-448.
+ * row_map / map_div / map_sentinel / num_rows_dev as for fmoe_quant_fp8_group128. */
+int fmoe_quant_fp8_per_token(const void* x, int in_dtype, int64_t rows_out, int64_t K,
+                             const int32_t* row_map, int map_div, int64_t map_sentinel,
+                             const int32_t* num_rows_dev, void* q, float* scale, void* stream);
 
 /*
  * Row gather into the padded expert-sorted order (bf16/f32 copy):
@@ -146,6 +155,8 @@ int fmoe_gather_rows(const void* x, int elem_bytes, int64_t rows_out, int64_t K,
  * the two matmul_ogs calls and the activation pass of
  * src/flaggems_sglang/ops/fused_moe.py:205-231.
  */
+#define FMOE_SCALE_BLOCK128 0
+#define FMOE_SCALE_CHANNEL 1
 #define FMOE_W_K_MAJOR 0
 #define FMOE_W_N_MAJOR 1
 typedef struct fmoe_gemm_args {
@@ -194,6 +205,10 @@ typedef struct fmoe_gemm_args {
                             along K over the idle CTAs.  NULL: every tile is computed by one CTA.  Results are
                             deterministic either way but differ in the last bits between the two.        */
   int64_t split_ws_bytes;
+  int32_t scale_mode;    /* e4m3: FMOE_SCALE_BLOCK128 (a_scale [a_rows, k/128], w_scale [E, rows/128, k/128]) or
+                            FMOE_SCALE_CHANNEL (a_scale [a_rows], one per row; w_scale [E, rows of w], one per output
+                            channel; applied to the finished accumulator; bf16 out; TCGEN05 variant only)        */
+  int32_t reserved1;     /* 0 */
 } fmoe_gemm_args;
 int64_t fmoe_gemm_split_workspace_bytes(void);
 
@@ -239,12 +254,13 @@ typedef struct fmoe_fused_args {
   int32_t activation;   /* FMOE_ACT_SILU | FMOE_ACT_GELU                                                  */
   int64_t T, H, I;
   float routed_scaling_factor; /* applied after the sum when != 1 (ignored with no_combine)              */
-  float reserved_f;
+  int32_t scale_mode;   /* e4m3: FMOE_SCALE_BLOCK128 (0) or FMOE_SCALE_CHANNEL (w1_scale [E,2I], w2_scale [E,H], one
+                           scale per output channel; activations quantised with one scale per token; TCGEN05 only) */
   const void* hidden;   /* [T,H]                                                                          */
   const void* w1;       /* [E,2I,H]                                                                       */
   const void* w2;       /* [E,H,I]                                                                        */
-  const float* w1_scale;/* e4m3: [E,2I/128,H/128]                                                         */
-  const float* w2_scale;/* e4m3: [E,H/128,I/128]                                                          */
+  const float* w1_scale;/* e4m3: [E,2I/128,H/128] (FMOE_SCALE_CHANNEL: [E,2I])                                */
+  const float* w2_scale;/* e4m3: [E,H/128,I/128]  (FMOE_SCALE_CHANNEL: [E,H])                                 */
   const float* topk_weights; /* [T,k]                                                                     */
   const int32_t* topk_ids;   /* [T,k]                                                                     */
   void* out;            /* [T,H] or [T,k,H]                                                               */

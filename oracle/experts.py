@@ -324,6 +324,39 @@ def fused_experts_fp8(
     return out.to(torch.bfloat16)
 
 
+def fused_experts_fp8_per_channel(x, w1_q, w1_scale, w2_q, w2_scale, topk_weights, topk_ids,
+                                  no_combine: bool = False, routed_scaling_factor: float | None = None) -> torch.Tensor:
+    """w8a8 with per-output-channel weight scales (w1_scale [E,2I], w2_scale [E,H]) and one dynamic scale per
+    activation row.  Builder-defined contract (the reference asserts `per_channel_quant` off,
+    ref:src/flaggems_sglang/ops/fused_moe.py:173-175), the one vLLM's fp8 MoE follows: quantise each token row ->
+    GEMM1 on the e4m3 values in fp32 -> (acc * row scale) * channel scale -> silu*mul in fp32 -> round to bf16 ->
+    quantise each row -> GEMM2 -> (acc * row scale) * channel scale * top-k weight -> bf16 -> combine."""
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E = w1_q.shape[0]
+    xq, xs = Q.quant_act_per_token(x)
+    xf = xq.to(torch.float32)
+    ids = topk_ids.detach().cpu().to(torch.int64).reshape(-1)
+    wts = topk_weights.detach().cpu().to(torch.float32).reshape(-1)
+    Z = torch.zeros(T * k, H, dtype=torch.float32)
+    for e in range(E):
+        slots = torch.nonzero(ids == e).reshape(-1)
+        if slots.numel() == 0:
+            continue
+        tok = slots // k
+        acc1 = (xf[tok] @ w1_q[e].detach().cpu().to(torch.float32).t()) * xs[tok, None] * w1_scale[e].cpu()[None, :]
+        a = _rb(silu_and_mul(acc1, torch.float32), torch.bfloat16)
+        aq, as_ = Q.quant_act_per_token(a)
+        acc2 = (aq.to(torch.float32) @ w2_q[e].detach().cpu().to(torch.float32).t()) * as_[:, None] * w2_scale[e].cpu()[None, :]
+        Z[slots] = _rb(acc2 * wts[slots, None], torch.bfloat16)
+    if no_combine:
+        return Z.view(T, k, H).to(torch.bfloat16)
+    out = moe_sum(Z.view(T, k, H))
+    if routed_scaling_factor is not None and routed_scaling_factor != 1.0:
+        out = _rb(out, torch.bfloat16) * routed_scaling_factor
+    return out.to(torch.bfloat16)
+
+
 def dense_moe(x, w1, w2, topk_weights, topk_ids) -> torch.Tensor:
     """Independent per-token formulation in fp32 with no intermediate rounding;
     used only to cross-check the restatements above (w1 [E,2I,H], w2 [E,H,I])."""

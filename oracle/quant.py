@@ -56,3 +56,26 @@ def dequant_act_group128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     rows, K = q.shape
     xf = q.detach().cpu().to(torch.float32).reshape(rows, K // GROUP, GROUP)
     return (xf * scale.cpu()[..., None]).reshape(rows, K)
+
+
+# ---- per-channel w8a8: one scale per output channel of the weights, one dynamic scale per activation row ----
+# (`per_channel_quant`, asserted off in the reference at src/flaggems_sglang/ops/fused_moe.py:173-175; the rule below
+# is the one vLLM's dynamic per-token quantiser and its fp8 MoE kernels follow: parity unpinned against the reference,
+# cross-checked against vLLM on the GPU.)
+MIN_TOKEN_SCALE = 1.0 / (FP8_MAX * 512.0)
+
+
+def quant_weight_per_channel(w: torch.Tensor):
+    """w [..., N, K] -> (q e4m3 same shape, scale f32 [..., N]); scale = amax(row)/448 (1.0 for a zero row)."""
+    wf = w.detach().cpu().to(torch.float32)
+    amax = wf.abs().amax(dim=-1)
+    scale = torch.where(amax > 0, amax / torch.full_like(amax, FP8_MAX), torch.ones_like(amax))
+    return to_e4m3(wf / scale[..., None]), scale.contiguous()
+
+
+def quant_act_per_token(x: torch.Tensor):
+    """x [rows, K] -> (q e4m3 [rows, K], scale f32 [rows]); scale = max(amax/448, 1/(448*512)), q = rne(x/scale)."""
+    xf = x.detach().cpu().to(torch.float32)
+    amax = xf.abs().amax(dim=-1)
+    scale = (amax / torch.full_like(amax, FP8_MAX)).clamp_min(MIN_TOKEN_SCALE)
+    return to_e4m3(xf / scale[:, None]), scale.contiguous()

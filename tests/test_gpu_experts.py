@@ -542,3 +542,26 @@ def test_reference_entry_point_makes_no_transposed_copy(fg):
     torch.cuda.reset_peak_memory_stats()
     out2 = fg.triton_kernel_fused_experts(xd, w1.cuda().transpose(1, 2), w2.cuda().transpose(1, 2), rd, gi, si)
     assert_close_moe(out2, OE.fused_experts(x, w1, w2, tw, ti), "bf16", "reference entry, transposed views")
+
+
+# ------------------------------------------------------------------ fp8 w8a8 with per-channel / per-token scales
+@pytest.mark.parametrize("T,H,I,E,k", [(9, 512, 256, 16, 4), (200, 512, 256, 16, 4), (1000, 512, 256, 16, 4),
+                                       (300, 352, 96, 8, 2), (64, 2880, 2880, 8, 2)])
+def test_fp8_per_channel_quant(fg, T, H, I, E, k):
+    """`per_channel_quant=True` (ref src/flaggems_sglang/ops/fused_moe.py:160, asserted off there): e4m3 weights with
+    one scale per output channel, activations with one dynamic scale per token; the tensor-core kernel applies both to
+    the finished accumulator."""
+    x, w1, w2, logits = _layer(T, H, I, E, k, torch.bfloat16, 500 + T)
+    w1q, w1s = OQ.quant_weight_per_channel(w1)
+    w2q, w2s = OQ.quant_weight_per_channel(w2)
+    gq, gs = fg.quant_weight_per_channel(w1.cuda())
+    assert torch.equal(gs.cpu(), w1s) and torch.equal(gq.cpu().view(torch.uint8), w1q.view(torch.uint8))
+    tw, ti = OR.softmax_topk(logits, k, True)
+    out = fg.fused_experts(x.cuda(), w1q.cuda(), w2q.cuda(), tw.cuda(), ti.cuda(), use_fp8_w8a8=True,
+                           per_channel_quant=True, w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), routed_scaling_factor=2.5)
+    again = fg.fused_experts(x.cuda(), w1q.cuda(), w2q.cuda(), tw.cuda(), ti.cuda(), use_fp8_w8a8=True,
+                             per_channel_quant=True, w1_scale=w1s.cuda(), w2_scale=w2s.cuda(), routed_scaling_factor=2.5)
+    assert torch.equal(out, again), "run-to-run results differ"
+    idx = torch.linspace(0, T - 1, min(T, 64)).long().unique()
+    ref = OE.fused_experts_fp8_per_channel(x[idx], w1q, w1s, w2q, w2s, tw[idx], ti[idx], routed_scaling_factor=2.5)
+    assert_close_moe(out[idx.cuda()], ref, "fp8", f"fp8 per-channel T={T} H={H} I={I}")

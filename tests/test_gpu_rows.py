@@ -144,3 +144,17 @@ def test_gather_rows_and_fused_gather_quant(fg):
     assert torch.equal(vq[valid], oq.view(torch.uint8)[valid])
     assert torch.equal(qs.cpu()[:used][valid], os_[valid])
     assert (vq[~valid] == 0).all() and (qs.cpu()[:used][~valid] == 1.0).all()
+
+
+@pytest.mark.parametrize("rows,K", [(1, 32), (7, 512), (64, 7168), (300, 2880), (5, 16384)])
+def test_quant_per_token_bit_exact(fg, rows, K):
+    """One dynamic scale per row (the activation side of per-channel w8a8): scales and bytes of the oracle."""
+    torch.manual_seed(rows + K)
+    x = (torch.randn(rows, K) * torch.rand(rows, 1) * 4).bfloat16()
+    if rows > 2:
+        x[1] = 0  # an all-zero row: the scale floor
+        x[2] = x[2] * 1e-9  # tiny row: scale floor again
+    q, s = fg.per_token_quant_fp8(x.cuda())
+    oq, os_ = OQ.quant_act_per_token(x)
+    assert torch.equal(s.cpu(), os_)
+    assert torch.equal(q.cpu().view(torch.uint8), oq.view(torch.uint8))

@@ -110,3 +110,32 @@ def test_routers_keep_ids_in_range_on_nan_and_inf_rows():
     gw, gids = OR.grouped_topk(logits, bias, k, 8, 4, True, 2.5)
     assert gids.min() >= 0 and gids.max() < E
     assert 3 not in gids[3:].reshape(-1).tolist()           # the NaN-biased expert is never chosen over finite ones
+
+
+def test_per_channel_fp8_oracle_tracks_the_unquantised_layer():
+    """Per-channel / per-token w8a8 restatement against the fp32 dense formulation on the same (unquantised) weights:
+    the quantisation noise of e4m3 with row / channel scales stays inside the fp8 bar."""
+    import torch
+
+    from oracle import experts as OE
+    from oracle import quant as OQ
+    from oracle import routing as OR
+
+    g = torch.Generator().manual_seed(3)
+    T, H, I, E, k = 24, 256, 128, 4, 2
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w1 = (torch.randn(E, 2 * I, H, generator=g) / H ** 0.5).bfloat16()
+    w2 = (torch.randn(E, H, I, generator=g) / I ** 0.5).bfloat16()
+    tw, ti = OR.softmax_topk(torch.randn(T, E, generator=g), k, True)
+    w1q, w1s = OQ.quant_weight_per_channel(w1)
+    w2q, w2s = OQ.quant_weight_per_channel(w2)
+    assert w1s.shape == (E, 2 * I) and w2s.shape == (E, H)
+    # de-quantised weights are within half an e4m3 step of the originals
+    assert float(((w1q.float() * w1s[..., None]) - w1.float()).abs().max()) <= float(w1.float().abs().max()) / 16
+    xq, xs = OQ.quant_act_per_token(x)
+    assert xs.shape == (T,) and float((xq.float() * xs[:, None] - x.float()).abs().max()) <= float(x.float().abs().max()) / 16
+    zero_q, zero_s = OQ.quant_act_per_token(torch.zeros(2, 64))
+    assert float(zero_s[0]) == float(torch.tensor(OQ.MIN_TOKEN_SCALE, dtype=torch.float32)) and not zero_q.float().any()
+    out = OE.fused_experts_fp8_per_channel(x, w1q, w1s, w2q, w2s, tw, ti).float()
+    ref = OE.dense_moe(x, w1, w2, tw, ti)
+    assert float((out - ref).norm() / ref.norm()) <= 8e-2  # e4m3 noise of three quantisation points

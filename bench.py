@@ -145,8 +145,9 @@ def run_cpu_oracle(cfg, T, steps, warmup, seed=0, gpu=None):
 
     def step():
         if cfg.dtype == "fp8":
-            return OE.fused_experts_fp8(tok["hidden"], w["w1"], w["w1_scale"], w["w2"], w["w2_scale"], tw, ti_local,
-                                        routed_scaling_factor=cfg.routed_scaling_factor)
+            fn = OE.fused_experts_fp8_per_channel if cfg.fp8_scales == "channel" else OE.fused_experts_fp8
+            return fn(tok["hidden"], w["w1"], w["w1_scale"], w["w2"], w["w2_scale"], tw, ti_local,
+                      routed_scaling_factor=cfg.routed_scaling_factor)
         return OE.fused_experts(tok["hidden"], w["w1"], w["w2"], tw, ti_local)
 
     out = None
@@ -185,7 +186,9 @@ def reference_arm(args, cfg):
 # ----------------------------------------------------------------------------------------------
 def layer_kwargs(cfg, wts):
     kw = {}
-    if cfg.dtype == "fp8":
+    if cfg.dtype == "fp8" and cfg.fp8_scales == "channel":
+        kw = dict(use_fp8_w8a8=True, per_channel_quant=True, w1_scale=wts["w1_scale"], w2_scale=wts["w2_scale"])
+    elif cfg.dtype == "fp8":
         kw = dict(use_fp8_w8a8=True, w1_scale=wts["w1_scale"], w2_scale=wts["w2_scale"], block_shape=[128, 128])
     return kw
 
@@ -319,6 +322,8 @@ def stage_names(cfg, T):
     dt = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp8": torch.float8_e4m3fn}[cfg.dtype]
     name, _ = _pick_variant(dt, T * cfg.top_k, cfg.E, cfg.I, cfg.H, None)
     fp8 = cfg.dtype == "fp8"
+    if fp8 and cfg.fp8_scales == "channel":
+        name = "tcgen05"  # the only kernel family of the per-channel format
     g = ("gemm1_fp8_" if fp8 else "gemm1_") + name, ("gemm2_fp8_" if fp8 else "gemm2_") + name
     prep = "quant_input" if fp8 else ("gather_rows" if name.startswith("tcgen05") else None)
     return ["align", prep, g[0], "quant_act" if fp8 else None, g[1], "moe_sum"]
@@ -676,6 +681,7 @@ def main():
         others["qwen3"] = config_sweep("qwen3", peaks, sweep_steps, skew_T=(512, 8192))
         others["refbench"] = config_sweep("refbench", peaks, sweep_steps)
         others["dsv3"] = config_sweep("dsv3", peaks, sweep_steps, extra_T=(128, 4096), skew_T=(4096,))
+        others["dsv3_channel"] = config_sweep("dsv3_channel", peaks, sweep_steps)
 
     from flaggems_sglang_b200 import _C
 

@@ -53,7 +53,7 @@ class GemmArgs(_SizedStructure):
         ("sorted_token_ids", c_void_p), ("expert_ids", c_void_p), ("num_tokens_post_padded", c_void_p),
         ("row_scale", c_void_p), ("out", c_void_p), ("out_scale", c_void_p),
         ("bias", c_void_p), ("act_alpha", c_float), ("act_limit", c_float), ("out_rows", c_void_p),
-        ("split_ws", c_void_p), ("split_ws_bytes", c_int64), ("scale_mode", c_int32), ("reserved1", c_int32),
+        ("split_ws", c_void_p), ("split_ws_bytes", c_int64), ("scale_mode", c_int32), ("a_scale_gather", c_int32),
     ]
 
 

@@ -131,6 +131,10 @@ int plan_fused(const fmoe_fused_args& a, FusedPlan* pl) {
     // every sorted row is quantised with its own scale; the activation likewise
     p.off_xs = take(p.cap * a.H);
     p.off_xs_scale = take(p.cap * 4);
+    if (a.top_k >= 2 && a.H % 16 == 0) {  // each token row quantised once, its bytes copied into the sorted order
+      p.off_xt = take(a.T * a.H);
+      p.off_xt_scale = take(a.T * 4);
+    }
     p.act_elem = 2;
     p.off_act = take(p.cap * a.I * 2);
     p.off_actq = take(p.cap * a.I);
@@ -280,7 +284,15 @@ int run_fused(const fmoe_fused_args& a, const FusedPlan& p, uint8_t* ws, void* s
     float* xsc = reinterpret_cast<float*>(ws + p.off_xs_scale);
     const bool channel = a.scale_mode == FMOE_SCALE_CHANNEL;
     g1.scale_mode = g2.scale_mode = a.scale_mode;
-    if (channel) {
+    if (channel && p.off_xt >= 0) {
+      void* xt = ws + p.off_xt;
+      float* xtsc = reinterpret_cast<float*>(ws + p.off_xt_scale);
+      rc = fmoe_quant_fp8_per_token(a.hidden, FMOE_BF16, a.T, a.H, nullptr, 1, 0, nullptr, xt, xtsc, stream);
+      if (rc) return rc;
+      rc = fmoe_gather_rows(xt, 1, p.cap, a.H, sorted, a.top_k, p.numel, npp, xq, stream);
+      xsc = xtsc;  // the gate/up GEMM looks the scale up by token
+      g1.a_scale_gather = 1;
+    } else if (channel) {
       rc = fmoe_quant_fp8_per_token(a.hidden, FMOE_BF16, p.cap, a.H, sorted, a.top_k, p.numel, npp, xq, xsc, stream);
     } else if (tc && p.off_xt >= 0) {
       void* xt = ws + p.off_xt;

@@ -55,7 +55,8 @@ struct TcParams {
   const int32_t* expert_ids;
   const int32_t* num_tokens_post_padded;
   const float* row_scale;
-  const float* a_scale;   // F8: [rows] f32, one scale per (sorted) input row
+  const float* a_scale;   // F8: [rows] f32, one scale per (sorted) input row; or per token (a_scale_gather)
+  int32_t a_scale_gather;
   const float* w_scale;   // F8: [E, w_rows] f32, one scale per output channel
   const float* bias;      // optional [E, w_rows] f32
   float act_alpha, act_limit;
@@ -433,7 +434,8 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       const int32_t slot = (pos < p.sorted_cap) ? p.sorted_token_ids[pos] : -1;
       const bool valid = slot >= 0 && slot < p.numel;
       float rs = (valid && p.row_scale) ? p.row_scale[slot] : 1.0f;
-      if constexpr (F8) rs *= (pos < p.sorted_cap) ? p.a_scale[pos] : 0.f;  // activation scale of this sorted row
+      if constexpr (F8)  // activation scale of this row: by sorted position, or by the token the slot belongs to
+        rs *= p.a_scale_gather ? (valid ? p.a_scale[slot / p.top_k] : 0.f) : ((pos < p.sorted_cap) ? p.a_scale[pos] : 0.f);
       const float* wsc = F8 ? p.w_scale + (int64_t)tile_e * p.w_rows + (int64_t)n_tile * (GATED ? 128 : 256) : nullptr;
       // bias entries of this tile's columns (the same for every row: broadcast loads)
       const float* bias = (EXTRA && p.bias)
@@ -720,6 +722,7 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.num_tokens_post_padded = g.num_tokens_post_padded;
   p.row_scale = g.row_scale;
   p.a_scale = g.a_scale;
+  p.a_scale_gather = g.a_scale_gather;
   p.w_scale = g.w_scale;
   p.bias = g.bias;
   p.act_alpha = g.act_alpha;

@@ -119,33 +119,36 @@ quant_group128_kernel(const InT* __restrict__ x, int64_t rows_out, int64_t K, co
   }
 }
 
-// Per-token dynamic quantisation to e4m3 with ONE scale per row (the activation side of per-channel w8a8): a CTA per
-// output row, the row held in registers between the amax pass and the conversion (bf16 rows up to kRowVecs * 256 * 8
-// = 16384 channels).  scale = max(amax / 448, 1 / (448 * 512)), q = rne(x / scale) saturated: the rule of vLLM's
-// dynamic per-token quantiser.
-constexpr int kRowVecs = 8;
+// Per-token dynamic quantisation to e4m3 with ONE scale per row (the activation side of per-channel w8a8).  A team of
+// TEAM threads (a warp for rows up to 4096 channels, the whole CTA above) owns an output row and holds it in
+// registers between the amax pass and the conversion: VECS 16-byte vectors per thread.  scale = max(amax / 448,
+// 1 / (448 * 512)), q = rne(x / scale) saturated: the rule of vLLM's dynamic per-token quantiser.
+template <int TEAM, int VECS>
 __global__ void __launch_bounds__(256)
 quant_row_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows_out, int64_t K, const int32_t* __restrict__ row_map,
                  int map_div, int64_t sentinel, const int32_t* __restrict__ num_rows_dev, uint8_t* __restrict__ q,
                  float* __restrict__ scale) {
   pdl_entry();
   __shared__ float s_max[8];
+  constexpr int kTeams = 256 / TEAM;
+  const int lane = threadIdx.x % TEAM;
   const int64_t limit = num_rows_dev ? min((int64_t)*num_rows_dev, rows_out) : rows_out;
   const int vecs = (int)(K / 8);  // 16-byte vectors per row
-  for (int64_t p = blockIdx.x; p < limit; p += gridDim.x) {
+  for (int64_t p = (int64_t)blockIdx.x * kTeams + threadIdx.x / TEAM; p < limit || TEAM == 256; p += (int64_t)gridDim.x * kTeams) {
+    if (TEAM == 256 && p >= limit) break;  // uniform over the CTA
     const int64_t r = mapped_row(row_map, map_div, sentinel, p);
     uint2* dst = reinterpret_cast<uint2*>(q + p * K);
     if (r < 0) {  // padding position: zeros with a unit scale
-      for (int c = threadIdx.x; c < vecs; c += 256) dst[c] = make_uint2(0, 0);
-      if (threadIdx.x == 0) scale[p] = 1.0f;
+      for (int c = lane; c < vecs; c += TEAM) dst[c] = make_uint2(0, 0);
+      if (lane == 0) scale[p] = 1.0f;
       continue;
     }
     const uint4* src = reinterpret_cast<const uint4*>(x + r * K);
-    uint4 raw[kRowVecs];
+    uint4 raw[VECS];
     float amax = 0.f;
 #pragma unroll
-    for (int i = 0; i < kRowVecs; ++i) {
-      const int c = threadIdx.x + i * 256;
+    for (int i = 0; i < VECS; ++i) {
+      const int c = lane + i * TEAM;
       raw[i] = make_uint4(0, 0, 0, 0);
       if (c < vecs) {
         raw[i] = __ldg(src + c);
@@ -156,18 +159,20 @@ quant_row_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows_out, int64_t 
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-    __syncthreads();  // s_max of the previous row has been read by everyone
-    if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
-    __syncthreads();
-    amax = s_max[0];
+    if constexpr (TEAM == 256) {
+      __syncthreads();  // s_max of the previous row has been read by everyone
+      if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
+      __syncthreads();
+      amax = s_max[0];
 #pragma unroll
-    for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_max[w]);
+      for (int w = 1; w < 8; ++w) amax = fmaxf(amax, s_max[w]);
+    }
     const float s = fmaxf(__fdiv_rn(amax, 448.0f), 1.0f / (448.0f * 512.0f));
     const float rcp = __frcp_rn(s);
     const bool finite = amax <= 3.0e38f;
 #pragma unroll
-    for (int i = 0; i < kRowVecs; ++i) {
-      const int c = threadIdx.x + i * 256;
+    for (int i = 0; i < VECS; ++i) {
+      const int c = lane + i * TEAM;
       if (c >= vecs) continue;
       const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[i]);
       float v[8];
@@ -195,7 +200,7 @@ quant_row_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows_out, int64_t 
       }
       dst[c] = make_uint2(lo, hi);
     }
-    if (threadIdx.x == 0) scale[p] = s;
+    if (lane == 0) scale[p] = s;
   }
 }
 
@@ -279,16 +284,21 @@ extern "C" int fmoe_quant_fp8_per_token(const void* x, int in_dtype, int64_t row
                                         const int32_t* row_map, int map_div, int64_t map_sentinel,
                                         const int32_t* num_rows_dev, void* q, float* scale, void* stream) {
   using namespace fmoe;
-  FMOE_REQUIRE(K > 0 && K % 8 == 0 && K <= (int64_t)kRowVecs * 256 * 8,
-               "quant_fp8_per_token: K must be a multiple of 8 up to %d (got %lld)", kRowVecs * 256 * 8, (long long)K);
+  FMOE_REQUIRE(K > 0 && K % 8 == 0 && K <= 16384, "quant_fp8_per_token: K must be a multiple of 8 up to 16384 (got %lld)",
+               (long long)K);
   FMOE_REQUIRE(in_dtype == FMOE_BF16, "quant_fp8_per_token: in_dtype must be bf16");
   FMOE_REQUIRE(!row_map || map_div >= 0, "quant_fp8_per_token: map_div must be >= 0");
   if (rows_out <= 0) return FMOE_OK;
   FMOE_REQUIRE(x && q && scale, "quant_fp8_per_token: null pointer");
   FMOE_REQUIRE(aligned16(x) && (reinterpret_cast<uintptr_t>(q) & 7u) == 0, "quant_fp8_per_token: misaligned pointer");
-  unsigned grid = (unsigned)std::min<int64_t>(rows_out, 148 * 8);
-  launch_pdl(quant_row_kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, rows_out, K,
-             row_map, map_div, map_sentinel, num_rows_dev, (uint8_t*)q, scale);
+  auto go = [&](auto kernel, int teams) {
+    unsigned grid = (unsigned)std::min<int64_t>(ceil_div<int64_t>(rows_out, teams), 148 * 8);
+    launch_pdl(kernel, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const __nv_bfloat16*)x, rows_out, K, row_map,
+               map_div, map_sentinel, num_rows_dev, (uint8_t*)q, scale);
+  };
+  if (K <= 2048) go(quant_row_kernel<32, 8>, 8);         // a warp per row, 8 rows per CTA
+  else if (K <= 4096) go(quant_row_kernel<32, 16>, 8);
+  else go(quant_row_kernel<256, 8>, 1);                  // a CTA per row
   return launch_status("quant_row_kernel");
 }
 

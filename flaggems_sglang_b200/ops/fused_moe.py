@@ -214,7 +214,6 @@ def fused_experts(
         assert H % 32 == 0 and I % 32 == 0, "per-channel fp8 needs H and I to be multiples of 32"
         assert w1_scale.numel() == E * twoI and w2_scale.numel() == E * H, "w1_scale must be [E,2I], w2_scale [E,H]"
         assert b1 is None and b2 is None and activation != "swiglu_oai", "bias / swiglu_oai are not available with fp8"
-        assert STAGE_EVENTS is None, "the per-stage profiling path does not take per-channel fp8"
         w1_scale = w1_scale.float().reshape(E, twoI).contiguous()
         w2_scale = w2_scale.float().reshape(E, H).contiguous()
     elif use_fp8_w8a8:
@@ -286,7 +285,10 @@ def fused_experts(
         return out
 
     # profiling path (STAGE_EVENTS set): the same kernels launched one by one with events around each launch
-    name, block = _pick_variant(w1.dtype if not use_fp8_w8a8 else torch.float8_e4m3fn, numel, E, I, H, variant)
+    if per_channel_quant:
+        name, block = "tcgen05", 128  # the one kernel family of this format
+    else:
+        name, block = _pick_variant(w1.dtype if not use_fp8_w8a8 else torch.float8_e4m3fn, numel, E, I, H, variant)
     vcode = _C.VARIANTS[name]
 
     with _stage("align"):
@@ -298,7 +300,7 @@ def fused_experts(
     common = dict(variant=vcode, activation=_C.ACTIVATIONS[activation], num_experts=E, top_k=k, block_size=block, numel=numel, sorted_cap=cap,
                   max_blocks=max_blocks, sorted_token_ids=sorted_ids.data_ptr(), expert_ids=expert_ids.data_ptr(),
                   num_tokens_post_padded=num_post.data_ptr())
-    if name == "tcgen05" and not use_fp8_w8a8:
+    if name == "tcgen05" and (not use_fp8_w8a8 or per_channel_quant):
         # the scratch that lets the kernel cut the tiles of a part-filled last round along K, as the one-call path has
         split_ws = torch.empty(int(lib.fmoe_gemm_split_workspace_bytes()), dtype=torch.uint8, device=dev)
         common.update(split_ws=split_ws.data_ptr(), split_ws_bytes=split_ws.numel())
@@ -328,6 +330,29 @@ def fused_experts(
                         w=w2.data_ptr(), row_scale=None if apply_router_weight_on_input else row_w,
                         bias=_C.ptr(b2), **z_args, **common)
         with _stage("gemm2_" + name):
+            _C.check(lib.fmoe_gemm2(g2, st))
+    elif per_channel_quant:
+        common["scale_mode"] = _C.SCALE_CHANNEL
+        xq = torch.empty((cap, H), dtype=torch.float8_e4m3fn, device=dev)
+        xsc = torch.empty(cap, dtype=torch.float32, device=dev)
+        with _stage("quant_input"):  # every sorted row with its own scale
+            _C.check(lib.fmoe_quant_fp8_per_token(x.data_ptr(), _C.BF16, cap, H, sorted_ids.data_ptr(), k, numel,
+                                                  num_post.data_ptr(), xq.data_ptr(), xsc.data_ptr(), st))
+        act = torch.empty((cap, I), dtype=torch.bfloat16, device=dev)
+        g1 = _gemm_args(dtype=_C.E4M3, out_dtype=_C.BF16, a_gather=0, n=I, k=H, a_rows=cap, a=xq.data_ptr(),
+                        a_scale=xsc.data_ptr(), w=w1.data_ptr(), w_scale=w1_scale.data_ptr(),
+                        row_scale=row_w if apply_router_weight_on_input else None, out=act.data_ptr(), **common)
+        with _stage("gemm1_fp8_" + name):
+            _C.check(lib.fmoe_gemm1_silu(g1, st))
+        aq = torch.empty((cap, I), dtype=torch.float8_e4m3fn, device=dev)
+        asc = torch.empty(cap, dtype=torch.float32, device=dev)
+        with _stage("quant_act"):
+            _C.check(lib.fmoe_quant_fp8_per_token(act.data_ptr(), _C.BF16, cap, I, sorted_ids.data_ptr(), 0, numel,
+                                                  num_post.data_ptr(), aq.data_ptr(), asc.data_ptr(), st))
+        g2 = _gemm_args(dtype=_C.E4M3, out_dtype=_C.BF16, a_gather=0, n=H, k=I, a_rows=cap, a=aq.data_ptr(),
+                        a_scale=asc.data_ptr(), w=w2.data_ptr(), w_scale=w2_scale.data_ptr(),
+                        row_scale=None if apply_router_weight_on_input else row_w, **z_args, **common)
+        with _stage("gemm2_fp8_" + name):
             _C.check(lib.fmoe_gemm2(g2, st))
     else:
         if name == "tcgen05":

@@ -27,6 +27,7 @@ class MoEConfig:
     topk_group: int = 1
     routed_scaling_factor: Optional[float] = None
     sweep_T: tuple = field(default_factory=tuple)
+    fp8_scales: str = "block128"     # fp8: "block128" (128x128 weight blocks, 1x128 activation groups) | "channel"
 
 
 CONFIGS = {
@@ -40,6 +41,10 @@ CONFIGS = {
     "dsv3": MoEConfig("dsv3", H=7168, I=2048, E=256, top_k=8, dtype="fp8", router="grouped", n_group=8,
                       topk_group=4, routed_scaling_factor=2.5, sweep_T=(1, 64, 1024, 16384)),
     # 32-expert cut of the DeepSeek-V3 layer (1.4 GB of weights): same tile shapes, small enough to profile
+    # the same layer with per-output-channel weight scales and per-token activation scales (`per_channel_quant`)
+    "dsv3_channel": MoEConfig("dsv3_channel", H=7168, I=2048, E=256, top_k=8, dtype="fp8", router="grouped", n_group=8,
+                              topk_group=4, routed_scaling_factor=2.5, sweep_T=(64, 1024, 4096, 16384),
+                              fp8_scales="channel"),
     "dsv3_small": MoEConfig("dsv3_small", H=7168, I=2048, E=32, top_k=8, dtype="fp8", router="grouped", n_group=8,
                             topk_group=4, routed_scaling_factor=2.5, sweep_T=(64, 2048)),
     # shapes of the reference's own test/benchmark list (M,1280,3072,64,8)
@@ -60,7 +65,7 @@ def zipf_logit_bias(E: int, s: float, gen: torch.Generator, device) -> torch.Ten
 def make_weights(cfg: MoEConfig, device, seed: int = 0, num_experts: Optional[int] = None, expert_offset: int = 0):
     """-> dict(w1, w2[, w1_scale, w2_scale]).  `num_experts`/`expert_offset` build one rank's shard of the
     same global layer (expert e always gets the same values)."""
-    from .ops.quant import quant_weight_block128
+    from .ops.quant import quant_weight_block128, quant_weight_per_channel
 
     E = cfg.E if num_experts is None else num_experts
     dt = TORCH_DTYPE[cfg.dtype]
@@ -69,7 +74,11 @@ def make_weights(cfg: MoEConfig, device, seed: int = 0, num_experts: Optional[in
     w1 = torch.empty(E, 2 * cfg.I, cfg.H, dtype=wdt, device=device)
     w2 = torch.empty(E, cfg.H, cfg.I, dtype=wdt, device=device)
     out = {"w1": w1, "w2": w2}
-    if fp8:
+    channel = fp8 and cfg.fp8_scales == "channel"
+    if channel:
+        out["w1_scale"] = torch.empty(E, 2 * cfg.I, dtype=torch.float32, device=device)
+        out["w2_scale"] = torch.empty(E, cfg.H, dtype=torch.float32, device=device)
+    elif fp8:
         out["w1_scale"] = torch.empty(E, 2 * cfg.I // 128, cfg.H // 128, dtype=torch.float32, device=device)
         out["w2_scale"] = torch.empty(E, cfg.H // 128, cfg.I // 128, dtype=torch.float32, device=device)
     for i in range(E):
@@ -77,7 +86,12 @@ def make_weights(cfg: MoEConfig, device, seed: int = 0, num_experts: Optional[in
         gen.manual_seed(seed * 1000003 + 7919 * (expert_offset + i) + 1)
         a = (torch.randn(2 * cfg.I, cfg.H, generator=gen, device=device) / math.sqrt(cfg.H)).to(dt)
         b = (torch.randn(cfg.H, cfg.I, generator=gen, device=device) / math.sqrt(cfg.I)).to(dt)
-        if fp8:
+        if channel:
+            qa, sa = quant_weight_per_channel(a)
+            qb, sb = quant_weight_per_channel(b)
+            w1[i], out["w1_scale"][i] = qa, sa
+            w2[i], out["w2_scale"][i] = qb, sb
+        elif fp8:
             if torch.device(device).type == "cuda":
                 qa, sa = quant_weight_block128(a)
                 qb, sb = quant_weight_block128(b)
@@ -129,6 +143,8 @@ def algorithmic_bytes_flops(cfg: MoEConfig, T: int, active_experts: int):
     ba = bw
     H, I, k = cfg.H, cfg.I, cfg.top_k
     b = active_experts * 3 * H * I * bw + T * H * ba + T * H * 2 + T * k * 8
-    if cfg.dtype == "fp8":
+    if cfg.dtype == "fp8" and cfg.fp8_scales == "channel":
+        b += active_experts * (2 * I + H) * 4 + T * 4
+    elif cfg.dtype == "fp8":
         b += active_experts * ((2 * I // 128) * (H // 128) + (H // 128) * (I // 128)) * 4 + T * (H // 128) * 4
     return b, 6 * T * k * H * I

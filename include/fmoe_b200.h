@@ -51,7 +51,7 @@ extern "C" {
 #define FMOE_VARIANT_TCGEN05 3 /* TMA + tcgen05/TMEM persistent kernel for large M */
 
 /* ABI version: 2 = argument structs begin with struct_size; 3 = fmoe_gemm_args ends with split_ws / split_ws_bytes;
- * 4 = ... and scale_mode / reserved1; fmoe_fused_args.scale_mode takes the place of a reserved word. */
+ * 4 = ... and scale_mode / a_scale_gather; fmoe_fused_args.scale_mode takes the place of a reserved word. */
 int fmoe_version(void);
 /* Message of the last error returned on the calling thread ("" if none). */
 const char* fmoe_last_error(void);
@@ -208,7 +208,9 @@ typedef struct fmoe_gemm_args {
   int32_t scale_mode;    /* e4m3: FMOE_SCALE_BLOCK128 (a_scale [a_rows, k/128], w_scale [E, rows/128, k/128]) or
                             FMOE_SCALE_CHANNEL (a_scale [a_rows], one per row; w_scale [E, rows of w], one per output
                             channel; applied to the finished accumulator; bf16 out; TCGEN05 variant only)        */
-  int32_t reserved1;     /* 0 */
+  int32_t a_scale_gather;/* FMOE_SCALE_CHANNEL: 1 = a_scale is [tokens] and the scale of sorted position p is
+                            a_scale[slot(p) / top_k] (rows quantised once per token, bytes copied into the sorted
+                            order); 0 = a_scale is [a_rows], one per row of `a`                                 */
 } fmoe_gemm_args;
 int64_t fmoe_gemm_split_workspace_bytes(void);
 

@@ -41,7 +41,7 @@ def test_struct_layout_matches_header():
 
     from flaggems_sglang_b200 import _C
 
-    # struct_size + w_layout, 8 int32, 6 int64, 10 pointers, bias pointer + 2 floats, out_rows, split_ws + its size, scale_mode + reserved
+    # struct_size + w_layout, 8 int32, 6 int64, 10 pointers, bias pointer + 2 floats, out_rows, split_ws + its size, scale_mode + a_scale_gather
     assert ctypes.sizeof(_C.GemmArgs) == 8 + 8 * 4 + 6 * 8 + 10 * 8 + (8 + 4 + 4) + 8 + 16 + 8
     assert _C.GemmArgs.struct_size.offset == 0 and _C.GemmArgs.numel.offset == 40 and _C.GemmArgs.a.offset == 88
     # struct_size + w_layout, 8 int32, 3 int64, 2 float, 9 pointers, 1 int64, 2 pointers + 2 floats, out_rows
@@ -57,7 +57,7 @@ def test_unknown_struct_size_is_refused(lib):
     from flaggems_sglang_b200 import _C
 
     g = _C.GemmArgs(dtype=_C.BF16, num_experts=4, top_k=2, block_size=16, numel=8, n=128, k=128)
-    g.struct_size -= 8  # the size of a struct that ends before scale_mode / reserved1 (ABI version 3)
+    g.struct_size -= 8  # the size of a struct that ends before scale_mode / a_scale_gather (ABI version 3)
     assert lib.fmoe_gemm2(ctypes.byref(g), None) == _C.ERR_INVALID_ARG and b"struct_size" in lib.fmoe_last_error()
     assert lib.fmoe_gemm1_silu(ctypes.byref(g), None) == _C.ERR_INVALID_ARG
     f = _C.FusedArgs(dtype=_C.BF16, num_experts=4, top_k=2, T=4, H=128, I=128)

@@ -394,12 +394,17 @@ def _sampled_oracle_check(fg, cfg_name, T, sample, kind, variant=None, skew=Fals
     tok = W.make_tokens(cfg, T, "cuda", seed=0, skew=skew)
     tw, ti = W.route(cfg, tok)
     kw = {}
-    if cfg.dtype == "fp8":
+    channel = cfg.dtype == "fp8" and cfg.fp8_scales == "channel"
+    if channel:
+        kw = dict(use_fp8_w8a8=True, per_channel_quant=True, w1_scale=wts["w1_scale"], w2_scale=wts["w2_scale"])
+    elif cfg.dtype == "fp8":
         kw = dict(use_fp8_w8a8=True, w1_scale=wts["w1_scale"], w2_scale=wts["w2_scale"], block_shape=[128, 128])
     out = fg.fused_experts(tok["hidden"], wts["w1"], wts["w2"], tw, ti, variant=variant, **kw)
     idx = torch.linspace(0, T - 1, min(sample, T)).long().unique().cuda()
     x_s, tw_s, ti_s = tok["hidden"][idx].cpu(), tw[idx].cpu(), ti[idx].cpu()
-    if cfg.dtype == "fp8":
+    if channel:
+        ref = OE.fused_experts_fp8_per_channel(x_s, wts["w1"], wts["w1_scale"], wts["w2"], wts["w2_scale"], tw_s, ti_s)
+    elif cfg.dtype == "fp8":
         ref = OE.fused_experts_fp8(x_s, wts["w1"], wts["w1_scale"], wts["w2"], wts["w2_scale"], tw_s, ti_s)
     else:
         ref = OE.fused_experts(x_s, wts["w1"], wts["w2"], tw_s, ti_s)
@@ -425,6 +430,11 @@ def test_qwen3_full_size_sampled(fg, T, skew):
 @pytest.mark.parametrize("T", [1, 64, 1024, 4096, 16384])
 def test_dsv3_fp8_full_size_sampled(fg, T):
     _sampled_oracle_check(fg, "dsv3", T, 24, "fp8")
+
+
+@pytest.mark.parametrize("T", [64, 4096])
+def test_dsv3_fp8_per_channel_full_size_sampled(fg, T):
+    _sampled_oracle_check(fg, "dsv3_channel", T, 24, "fp8")
 
 
 def test_two_devices_in_one_process(fg):

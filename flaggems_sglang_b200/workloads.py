@@ -45,6 +45,9 @@ CONFIGS = {
     "dsv3_channel": MoEConfig("dsv3_channel", H=7168, I=2048, E=256, top_k=8, dtype="fp8", router="grouped", n_group=8,
                               topk_group=4, routed_scaling_factor=2.5, sweep_T=(64, 1024, 4096, 16384),
                               fp8_scales="channel"),
+    "dsv3_channel_small": MoEConfig("dsv3_channel_small", H=7168, I=2048, E=32, top_k=8, dtype="fp8", router="grouped",
+                                    n_group=8, topk_group=4, routed_scaling_factor=2.5, sweep_T=(64, 2048),
+                                    fp8_scales="channel"),
     "dsv3_small": MoEConfig("dsv3_small", H=7168, I=2048, E=32, top_k=8, dtype="fp8", router="grouped", n_group=8,
                             topk_group=4, routed_scaling_factor=2.5, sweep_T=(64, 2048)),
     # shapes of the reference's own test/benchmark list (M,1280,3072,64,8)

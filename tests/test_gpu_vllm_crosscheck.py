@@ -150,3 +150,57 @@ def test_fp8_block_quant_experts(vops):
     l2_oracle, l2_ours = rel_l2(out_v, ref), rel_l2(ours, out_v)
     print(f"vLLM fp8 experts vs oracle rel-L2 {l2_oracle:.2e}; this package vs vLLM {l2_ours:.2e}")
     assert l2_oracle <= 3e-2 and l2_ours <= 3e-2
+
+
+def test_per_token_quant(vops):
+    """One dynamic scale per row: this package's kernel and the oracle against vLLM's dynamic per-token quantiser."""
+    import flaggems_sglang_b200 as fg
+
+    g = torch.Generator().manual_seed(9)
+    x = (torch.randn(77, 2048, generator=g) * torch.rand(77, 1, generator=g) * 4).bfloat16()
+    x[3] = 0
+    try:
+        qv, sv = vops.scaled_fp8_quant(x.cuda(), None, use_per_token_if_dynamic=True)
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"vLLM per-token quantiser did not run here: {type(e).__name__}: {e}")
+    oq, os_ = OQ.quant_act_per_token(x)
+    q, s = fg.per_token_quant_fp8(x.cuda())
+    assert torch.equal(s.cpu(), os_) and torch.equal(q.cpu().view(torch.uint8), oq.view(torch.uint8))
+    torch.testing.assert_close(sv.reshape(-1).cpu(), os_, rtol=1e-6, atol=0)
+    # vLLM multiplies by a reciprocal where the oracle divides: bytes may differ by one step on exact ties only
+    diff = (qv.cpu().float() - oq.float()).abs()
+    assert float((diff > 0).float().mean()) <= 2e-3, "more than 0.2 % of the bytes differ from vLLM's quantiser"
+
+
+def test_fp8_per_channel_experts(vops):
+    """Per-channel w8a8 experts (`per_channel_quant`): oracle and this package against vLLM's fused experts with
+    per-token activation scales and per-output-channel weight scales."""
+    try:
+        from vllm.model_executor.layers.fused_moe.config import fp8_w8a8_moe_quant_config
+        from vllm.model_executor.layers.fused_moe.fused_moe import fused_experts as vllm_fused_experts
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"vLLM fused_experts unavailable: {e}")
+    import flaggems_sglang_b200 as fg
+
+    T, H, I, E, k = 48, 512, 256, 8, 2
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(T, H, generator=g).bfloat16()
+    w1 = torch.randn(E, 2 * I, H, generator=g) / H ** 0.5
+    w2 = torch.randn(E, H, I, generator=g) / I ** 0.5
+    q1, s1 = OQ.quant_weight_per_channel(w1)
+    q2, s2 = OQ.quant_weight_per_channel(w2)
+    tw, ti = OR.softmax_topk(torch.randn(T, E, generator=g), k, True)
+    ref = OE.fused_experts_fp8_per_channel(x, q1, s1, q2, s2, tw, ti)
+    ours = fg.fused_experts(x.cuda(), q1.cuda(), q2.cuda(), tw.cuda(), ti.cuda(), use_fp8_w8a8=True,
+                            per_channel_quant=True, w1_scale=s1.cuda(), w2_scale=s2.cuda())
+    assert rel_l2(ours, ref) <= 3e-2
+    try:
+        qc = fp8_w8a8_moe_quant_config(w1_scale=s1.cuda().unsqueeze(-1), w2_scale=s2.cuda().unsqueeze(-1),
+                                       per_act_token_quant=True, per_out_ch_quant=True)
+        out_v = vllm_fused_experts(x.cuda(), q1.cuda(), q2.cuda(), tw.cuda(), ti.cuda().to(torch.int32), quant_config=qc)
+        torch.cuda.synchronize()
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"vLLM per-channel fp8 fused_experts did not run here: {type(e).__name__}: {e}")
+    l2_oracle, l2_ours = rel_l2(out_v, ref), rel_l2(ours, out_v)
+    print(f"vLLM per-channel fp8 experts vs oracle rel-L2 {l2_oracle:.2e}; this package vs vLLM {l2_ours:.2e}")
+    assert l2_oracle <= 3e-2 and l2_ours <= 3e-2

@@ -641,6 +641,7 @@ def main():
     if world > 1:
         from flaggems_sglang_b200 import ep_bench
 
+        args.peaks = load_peaks()
         ep_bench.run(args, cfg, rank, world, local, clock_sampler=ClockSampler(local))
         return
 

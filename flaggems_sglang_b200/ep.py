@@ -412,7 +412,8 @@ def p2p_experts(xc: PeerExchange, state: dict, w1_local, w2_local, fuse_return: 
     g1 = _C.GemmArgs(dtype=code, out_dtype=act_code, n=xc.I, k=xc.H, a=xc.rows.data_ptr(), a_scale=_C.ptr(xc.scales),
                      w=w1c.data_ptr(), w_scale=_C.ptr(w1_scale.float().contiguous()) if xc.fp8 else None,
                      row_scale=row_w if apply_router_weight_on_input else None, out=xc.act.data_ptr(), **common)
-    _C.check(lib.fmoe_gemm1_silu(g1, st))
+    with _phase("gemm1", True):
+        _C.check(lib.fmoe_gemm1_silu(g1, st))
     a2, a2_scale = xc.act, None
     if xc.fp8:
         _C.check(lib.fmoe_quant_fp8_group128(xc.act.data_ptr(), act_code, cap, xc.I, xc.sorted_ids.data_ptr(), 0, cap,
@@ -427,7 +428,8 @@ def p2p_experts(xc: PeerExchange, state: dict, w1_local, w2_local, fuse_return: 
                      w=w2c.data_ptr(), w_scale=_C.ptr(w2_scale.float().contiguous()) if xc.fp8 else None,
                      row_scale=None if apply_router_weight_on_input else row_w, out=_C.ptr(z_local),
                      out_rows=xc.out_rows.data_ptr() if fuse_return else None, **common)
-    _C.check(lib.fmoe_gemm2(g2, st))
+    with _phase("gemm2", True):
+        _C.check(lib.fmoe_gemm2(g2, st))
     return z_local
 
 

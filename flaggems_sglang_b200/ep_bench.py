@@ -215,6 +215,36 @@ def run(args, cfg, rank: int, world: int, local: int, clock_sampler=None) -> Non
         dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
         clocks = clock_sampler.stop() if clock_sampler is not None and rank == 0 else None
 
+        # phases of the exchange and the two GEMMs, timed in five extra steps (events around every phase; the
+        # GEMM events sit inside the "experts" phase): median over the steps, then max over ranks
+        phases_ms, roofline = None, None
+        ep.PHASE_EVENTS = []
+        for _ in range(5):
+            step()
+        torch.cuda.synchronize()
+        names, samples = [], {}
+        for name, a, b in ep.PHASE_EVENTS:
+            if name not in samples:
+                names.append(name)
+            samples.setdefault(name, []).append(a.elapsed_time(b))
+        acc = {n: sorted(v)[len(v) // 2] for n, v in samples.items()}
+        ep.PHASE_EVENTS = None
+        if names:
+            vec = torch.tensor([acc[n] for n in names], device=dev)
+            own_gemm1 = acc.get("gemm1")
+            dist.all_reduce(vec, op=dist.ReduceOp.MAX)
+            phases_ms = {n: round(float(v), 4) for n, v in zip(names, vec.tolist())}
+            if xc is not None and own_gemm1 and getattr(args, "peaks", None):
+                used = int(xc.npp.item())
+                rows = int((xc.sorted_ids[:used] < xc.capacity).sum().item())  # rows this rank's experts received
+                flops = 4.0 * rows * cfg.H * cfg.I
+                peak = args.peaks["bf16_tflops"] * (2.0 if cfg.dtype == "fp8" else 1.0)
+                ach = flops / (own_gemm1 * 1e-3) / 1e12
+                roofline = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak,
+                            "peak_source": args.peaks["source"], "kernel": f"gemm1 on rank 0 of {world} ({rows} rows received)",
+                            "launch_ms": own_gemm1, "timing": "events around the launch, median of five extra steps",
+                            "traffic": None, "alg_flops_per_launch": flops}
+
         parity = _parity_rank0(cfg, tok, step(), rank)
         if xc is not None:
             xc.close()
@@ -239,7 +269,7 @@ def run(args, cfg, rank: int, world: int, local: int, clock_sampler=None) -> Non
                                           if mode == "p2p" else "NCCL all-to-all dispatch/combine"),
                            "tokens_per_step": T_all, "parallelism": f"ep{world}",
                            "l2": "weights re-read every step exceed L2 (no flush needed)"},
-                "roofline": None, "cpu_baseline": None, "parity": parity,
+                "roofline": roofline, "phases_ms": phases_ms, "cpu_baseline": None, "parity": parity,
                 "e2e": {"value": T_all / (ms2_v * 1e-3), "unit": "tokens/s", "ms_per_step": ms2_v,
                         "h2d_bytes_per_step": (h_host.numel() * h_host.element_size() + l_host.numel() * 4) * world,
                         "d2h_bytes_per_step": out_host[0].numel() * out_host[0].element_size() * world,

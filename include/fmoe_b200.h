@@ -132,8 +132,8 @@ int fmoe_moe_align_block_size_ws(const int32_t* topk_ids, int64_t numel, int E, 
 int fmoe_quant_fp8_group128(const void* x, int in_dtype, int64_t rows_out, int64_t K,
                             const int32_t* row_map, int map_div, int64_t map_sentinel,
                             const int32_t* num_rows_dev, void* q, float* scale, void* stream);
-/* Per-row dynamic quantisation with ONE scale per row (the activation side of per-channel w8a8, SURVEY of the
- * reference: `per_channel_quant`, src/flaggems_sglang/ops/fused_moe.py:160, asserted off there at :173-175):
+/* Per-row dynamic quantisation with ONE scale per row (the activation side of per-channel w8a8: the reference's
+ * `per_channel_quant` argument, src/flaggems_sglang/ops/fused_moe.py:160, asserted off there at :173-175):
  *   x [rows_in, K] bf16, K % 8 == 0, K <= 16384; q [rows_out, K] e4m3; scale [rows_out] f32,
  *   scale = max(amax / 448, 1 / (448 * 512)), q = rne(x / scale) saturated to +-448.
  * row_map / map_div / map_sentinel / num_rows_dev as for fmoe_quant_fp8_group128. */

@@ -575,3 +575,22 @@ def test_fp8_per_channel_quant(fg, T, H, I, E, k):
     idx = torch.linspace(0, T - 1, min(T, 64)).long().unique()
     ref = OE.fused_experts_fp8_per_channel(x[idx], w1q, w1s, w2q, w2s, tw[idx], ti[idx], routed_scaling_factor=2.5)
     assert_close_moe(out[idx.cuda()], ref, "fp8", f"fp8 per-channel T={T} H={H} I={I}")
+
+
+# ------------------------------------------------------------------ tail split of the tensor-core GEMMs
+@pytest.mark.parametrize("T,H,I,E,k", [(700, 1024, 768, 8, 2), (1024, 4096, 1024, 4, 2)])
+def test_tail_split_on_and_off(fg, monkeypatch, T, H, I, E, k):
+    """A last round of tiles that fills at most half of the CTAs is cut along K over the idle CTAs (fp32 partials summed
+    strip-wise in a fixed order).  On and off are both deterministic, both match the oracle, and differ from each other
+    by summation order only."""
+    x, w1, w2, logits = _layer(T, H, I, E, k, torch.bfloat16, 900 + T)
+    tw, ti = OR.softmax_topk(logits, k, True)
+    on = _run(fg, x, w1, w2, tw, ti, variant="tcgen05")
+    assert torch.equal(on, _run(fg, x, w1, w2, tw, ti, variant="tcgen05")), "run-to-run results differ"
+    monkeypatch.setenv("FMOE_TC_SPLIT_TAIL", "0")
+    off = _run(fg, x, w1, w2, tw, ti, variant="tcgen05")
+    assert rel_l2(on, off) < 1e-3
+    idx = torch.linspace(0, T - 1, 64).long().unique()
+    ref = OE.fused_experts(x[idx], w1, w2, tw[idx], ti[idx])
+    assert_close_moe(on[idx.cuda()], ref, "bf16", f"tail split on T={T}")
+    assert_close_moe(off[idx.cuda()], ref, "bf16", f"tail split off T={T}")

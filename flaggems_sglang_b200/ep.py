@@ -221,13 +221,13 @@ class PeerExchange:
         wdt = torch.float8_e4m3fn if fp8 else dtype
         self.variant, self.block = _pick_variant(wdt, max(self.max_tokens * self.top_k, 1), self.e_local, self.I,
                                                  self.H, variant)
-        # Result rows go back either from inside the down-projection kernel (its epilogue stores to the peer) or by a
-        # separate copy kernel.  None = by kernel family and group size: the bf16 tcgen05 kernel has dedicated epilogue
-        # warps, so on two ranks (half of the rows remote) the slower peer stores overlap the next tile (measured 2.50
-        # against 2.55 ms, Mixtral); with three quarters or more of the rows remote they hold the GEMM up (Mixtral,
-        # fused against separate: 2.83 / 2.74 ms on 4 GPUs, 3.09 / 2.77 ms on 8: down GEMM 1.27 against 0.79 ms).  In
-        # the fp8 kernel the fold warps do the epilogue and the stores sit on the critical path (4.58 against 4.22 ms,
-        # DeepSeek-V3, 2 GPUs).  FMOE_EP_FUSE_RETURN=0/1 forces one way.
+        # Result rows go back either from inside the down-projection kernel (its epilogue stores to the peer:
+        # fmoe_gemm_args.out_rows) or by a separate copy kernel.  The copy kernel is the default: measured on Mixtral,
+        # fused against separate, 2.60-2.63 / 2.60-2.62 ms on 2 GPUs (a tie: the bf16 kernel's dedicated epilogue warps
+        # hide the peer stores of half of the rows), 2.83 / 2.74 ms on 4 and 3.09 / 2.77 ms on 8 (with three quarters
+        # or more of the rows remote the stores hold the GEMM up: down GEMM 1.27 against 0.79 ms); in the fp8 kernel
+        # the fold warps do the epilogue and the stores sit on the critical path (4.58 against 4.22 ms, DeepSeek-V3,
+        # 2 GPUs).  FMOE_EP_FUSE_RETURN=1 selects the fused return.
         env = os.environ.get("FMOE_EP_FUSE_RETURN")
         self.fuse_return = None if env is None else env != "0"
         eb = torch.empty(0, dtype=dtype).element_size()
@@ -380,7 +380,7 @@ def p2p_experts(xc: PeerExchange, state: dict, w1_local, w2_local, fuse_return: 
     the padded expert-sorted order.  With `fuse_return` (and a kernel family that takes row addresses) the
     down-projection epilogue stores every result row straight into the slot buffer of the rank the row came
     from, and None is returned; otherwise the rows come back for `p2p_return`.
-    `fuse_return=None` decides by kernel family and group size (bf16 on two ranks: fused; otherwise separate)."""
+    `fuse_return=None` means separate (measured faster or equal everywhere, see PeerExchange)."""
     from . import _C
 
     assert use_fp8_w8a8 == xc.fp8, "this PeerExchange was created for the other weight type"
@@ -392,7 +392,7 @@ def p2p_experts(xc: PeerExchange, state: dict, w1_local, w2_local, fuse_return: 
     dev = xc.rows.device
     lib, st = _C.lib(), _C.stream_ptr(dev)
     if fuse_return is None:
-        fuse_return = not xc.fp8 and xc.world <= 2
+        fuse_return = False
     fuse_return = fuse_return and xc.variant in ("stream", "tcgen05")
     cap, blk = xc.capacity, xc.block
     _C.check(lib.fmoe_ep_recv_tables(state["matrix"].data_ptr(), xc.rank, xc.world, xc.total_experts, xc.e_local, blk, cap,

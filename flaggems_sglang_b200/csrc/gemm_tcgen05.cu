@@ -754,7 +754,9 @@ int launch(const GemmParams& g, cudaStream_t st) {
   p.split_max = 0;
   const char* split_env = getenv("FMOE_TC_SPLIT_TAIL");  // "0": off (read per launch, tests flip it)
   const bool split_off = split_env && atoi(split_env) == 0;
-  if (g.split_ws && !split_off && g.split_ws_bytes >= gemm_tcgen05_split_workspace_bytes() && aligned16(g.split_ws)) {
+  // one partial per CTA must fit: the scratch is sized for the SM count, the grid never exceeds it
+  const bool split_fits = g.split_ws_bytes >= 1024 + (int64_t)grid * BM * BN * 4 && grid <= 256;
+  if (g.split_ws && !split_off && split_fits && aligned16(g.split_ws)) {
     p.split_counters = reinterpret_cast<int32_t*>(g.split_ws);
     p.split_partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(g.split_ws) + 1024);
     p.split_max = 8;

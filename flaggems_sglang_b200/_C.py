@@ -78,6 +78,7 @@ class FusedArgs(_SizedStructure):
 SIGNATURES = {
     "fmoe_version": (c_int, []),
     "fmoe_gemm_split_workspace_bytes": (c_int64, []),
+    "fmoe_debug_tail_plan": (c_int, [c_int64, c_int, c_int, c_int, c_int, c_int64, c_void_p]),
     "fmoe_last_error": (c_char_p, []),
     "fmoe_sm_count": (c_int, []),
     "fmoe_topk_softmax": (c_int, [c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),

@@ -104,6 +104,12 @@ extern "C" int fmoe_version(void) { return 4; }
 
 extern "C" int64_t fmoe_gemm_split_workspace_bytes(void) { return fmoe::gemm_tcgen05_split_workspace_bytes(); }
 
+extern "C" int fmoe_debug_tail_plan(int64_t total_tiles, int k_steps, int max_split, int grid, int cta, int64_t unit,
+                                    int64_t* host_out) {
+  if (!host_out || grid < 1 || cta < 0 || cta >= grid || total_tiles < 0 || k_steps < 1 || unit < 0) return -1;
+  return fmoe::tail_plan_unit(total_tiles, k_steps, max_split, grid, cta, unit, host_out);
+}
+
 extern "C" const char* fmoe_last_error(void) { return fmoe::last_error_buffer(); }
 
 extern "C" int fmoe_sm_count(void) {

@@ -21,6 +21,7 @@ int gemm_tcgen05_fp8(const GemmParams& p, bool gated, cudaStream_t st);
 bool gemm_stream_supports(const GemmParams& p, bool gated);
 bool gemm_tcgen05_supports(const GemmParams& p, bool gated);
 int64_t gemm_tcgen05_split_workspace_bytes();
+int tail_plan_unit(int64_t total_tiles, int k_steps, int max_split, int grid, int cta, int64_t it, int64_t* out);
 bool gemm_tcgen05_fp8_supports(const GemmParams& p, bool gated);
 
 // Tile order of the persistent kernels: expert by expert, and inside an expert in groups of at most

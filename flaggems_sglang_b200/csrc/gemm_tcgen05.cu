@@ -107,23 +107,23 @@ __device__ __forceinline__ bool warp_wait_relaxed(uint64_t* bar, uint32_t parity
 struct UnitPlan {
   int64_t total, rounds, left;
   int grid, b, S, k_steps;
-  __device__ __forceinline__ void init(int64_t total_tiles, int k_steps_, int max_split) {
+  __host__ __device__ __forceinline__ void init(int64_t total_tiles, int k_steps_, int max_split, int grid_, int b_) {
     total = total_tiles;
     k_steps = k_steps_;
-    grid = (int)gridDim.x;
-    b = (int)blockIdx.x;
+    grid = grid_;
+    b = b_;
     S = 1;
     rounds = (total + grid - 1) / grid;
     left = total - (rounds - 1) * grid;
     if (total > 0 && max_split >= 2 && left * 2 <= grid) {
-      int s = (int)min((int64_t)max_split, grid / left);
-      s = min(s, k_steps / 8);
+      int s = (int)(max_split < grid / left ? max_split : grid / left);
+      s = s < k_steps / 8 ? s : k_steps / 8;
       while (s & (s - 1)) s &= s - 1;  // largest power of two below
       if (s >= 2) S = s;
     }
   }
   // unit `it` of this CTA: tile, K steps [ks0, ks1), slice (always 0 for whole tiles); false past the last unit
-  __device__ __forceinline__ bool get(int64_t it, int64_t* tile, int* ks0, int* ks1, int* slice) const {
+  __host__ __device__ __forceinline__ bool get(int64_t it, int64_t* tile, int* ks0, int* ks1, int* slice) const {
     *ks0 = 0;
     *ks1 = k_steps;
     *slice = 0;
@@ -138,7 +138,7 @@ struct UnitPlan {
     *ks1 = (int)((int64_t)k_steps * (*slice + 1) / S);
     return true;
   }
-  __device__ __forceinline__ bool is_split(int64_t it) const { return S > 1 && it == rounds - 1; }
+  __host__ __device__ __forceinline__ bool is_split(int64_t it) const { return S > 1 && it == rounds - 1; }
 };
 
 __device__ __forceinline__ void store_partial32(const uint32_t (&r)[32], float* dst) {
@@ -223,7 +223,7 @@ grouped_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   TileCursor cursor;
   const int k_steps = p.k_steps;
   UnitPlan plan;
-  plan.init(total_tiles, k_steps, p.split_partials ? min(p.split_max, GATED ? 4 : 8) : 0);
+  plan.init(total_tiles, k_steps, p.split_partials ? min(p.split_max, GATED ? 4 : 8) : 0, (int)gridDim.x, (int)blockIdx.x);
 
   if (warp == 4) {
     // ---------------- TMA producer ----------------
@@ -651,6 +651,21 @@ int device_sm_count() {
   std::lock_guard<std::mutex> lock(mu);
   if (sm_count[dev] == 0) cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
   return sm_count[dev];
+}
+
+// Host-side view of the work-unit plan (the same code the kernels run), for tests.
+int tail_plan_unit(int64_t total_tiles, int k_steps, int max_split, int grid, int cta, int64_t it, int64_t* out) {
+  UnitPlan plan;
+  plan.init(total_tiles, k_steps, max_split, grid, cta);
+  int64_t tile = 0;
+  int ks0 = 0, ks1 = 0, slice = 0;
+  if (!plan.get(it, &tile, &ks0, &ks1, &slice)) return 0;
+  out[0] = tile;
+  out[1] = ks0;
+  out[2] = ks1;
+  out[3] = slice;
+  out[4] = plan.is_split(it) ? plan.S : 1;
+  return 1;
 }
 
 int64_t gemm_tcgen05_split_workspace_bytes() {

@@ -213,6 +213,12 @@ typedef struct fmoe_gemm_args {
                             order); 0 = a_scale is [a_rows], one per row of `a`                                 */
 } fmoe_gemm_args;
 int64_t fmoe_gemm_split_workspace_bytes(void);
+/* Host-side view of the TCGEN05 kernels' work plan (no GPU needed): unit number `unit` of CTA `cta` in a launch of
+ * `grid` CTAs over `total_tiles` tiles of `k_steps` K steps each, with at most `max_split` slices per tile (8 for the
+ * down GEMM, 4 for the gate/up GEMM, 0 or 1 for no split).  Returns 1 and host_out = {tile, first K step, end K step,
+ * slice, slices of this tile}, 0 past the CTA's last unit, -1 on bad arguments. */
+int fmoe_debug_tail_plan(int64_t total_tiles, int k_steps, int max_split, int grid, int cta, int64_t unit,
+                         int64_t* host_out);
 
 /* gemm1: out[p, c] = act(acc[p, c]) * acc[p, I + c], acc = (a_row(p) . w[e(p)]^T) * row_scale. */
 int fmoe_gemm1_silu(const fmoe_gemm_args* args, void* stream);

@@ -126,7 +126,9 @@ topk_softmax_kernel(const float* __restrict__ logits, int64_t T, int E, int k, i
   }
 }
 
-template <int VPT>
+// COOP (few tokens): one CTA per token; all its threads evaluate the fp64 sigmoids (one expert each instead of VPT in
+// a row per lane), then warp 0 carries on alone.  Same arithmetic, shorter dependent chain.
+template <int VPT, bool COOP>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 topk_grouped_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int64_t T, int E,
                     int k, int n_group, int topk_group, int renorm, float scale,
@@ -135,27 +137,39 @@ topk_grouped_kernel(const float* __restrict__ logits, const float* __restrict__ 
   extern __shared__ float s_dyn[];  // per warp: score[E], choice[E]
   __shared__ int s_ids[kWarpsPerBlock][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t t = (int64_t)blockIdx.x * kWarpsPerBlock + warp;
+  const int64_t t = COOP ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * kWarpsPerBlock + warp;
   if (t >= T) return;
-  float* s_score = s_dyn + (size_t)warp * 2 * E;
+  float* s_score = s_dyn + (COOP ? (size_t)0 : (size_t)warp * 2 * E);
   float* s_choice = s_score + E;
   const float* row = logits + t * E;
   float key[VPT];
+  auto scores = [&](int e, float* c_out) {
+    // correctly rounded fp32 sigmoid: evaluate in fp64, round once
+    const float lg = row[e];
+    double z = (lg != lg) ? -INFINITY : (double)lg;  // NaN ranks as -inf (score 0)
+    float s = (float)(1.0 / (1.0 + exp(-z)));
+    float c = s + (bias ? bias[e] : 0.f);
+    if (c != c) c = kNegInf;
+    s_score[e] = s;
+    s_choice[e] = c;
+    *c_out = c;
+  };
+  if constexpr (COOP) {
+    float unused;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) scores(e, &unused);
+    __syncthreads();
+    if (warp != 0) return;
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    int e = lane + 32 * i;
-    if (e < E) {
-      // correctly rounded fp32 sigmoid: evaluate in fp64, round once
-      const float lg = row[e];
-      double z = (lg != lg) ? -INFINITY : (double)lg;  // NaN ranks as -inf (score 0)
-      float s = (float)(1.0 / (1.0 + exp(-z)));
-      float c = s + (bias ? bias[e] : 0.f);
-      if (c != c) c = kNegInf;
-      s_score[e] = s;
-      s_choice[e] = c;
-      key[i] = c;
-    } else {
-      key[i] = kNegInf;
+    for (int i = 0; i < VPT; ++i) {
+      int e = lane + 32 * i;
+      key[i] = (e < E) ? s_choice[e] : kNegInf;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int e = lane + 32 * i;
+      if (e < E) scores(e, &key[i]);
+      else key[i] = kNegInf;
     }
   }
   __syncwarp();
@@ -233,9 +247,14 @@ template <int VPT>
 struct GroupedLauncher {
   static int run(const float* logits, const float* bias, int64_t T, int E, int k, int n_group,
                  int topk_group, int renorm, float scale, float* w, int32_t* ids, cudaStream_t st) {
-    dim3 grid((unsigned)ceil_div<int64_t>(T, kWarpsPerBlock));
     size_t smem = (size_t)kWarpsPerBlock * 2 * E * sizeof(float);
-    launch_pdl(topk_grouped_kernel<VPT>, grid, dim3(kWarpsPerBlock * 32), smem, st, logits, bias, T, E, k, n_group,
+    if (T <= 64) {  // decode-sized: a CTA per token shortens the chain of fp64 sigmoids (13.3 -> 8.7-9.9 us at T = 1, E = 256)
+      launch_pdl(topk_grouped_kernel<VPT, true>, dim3((unsigned)T), dim3(kWarpsPerBlock * 32), smem, st, logits, bias, T, E,
+                 k, n_group, topk_group, renorm, scale, w, ids);
+      return launch_status("topk_grouped_kernel");
+    }
+    dim3 grid((unsigned)ceil_div<int64_t>(T, kWarpsPerBlock));
+    launch_pdl(topk_grouped_kernel<VPT, false>, grid, dim3(kWarpsPerBlock * 32), smem, st, logits, bias, T, E, k, n_group,
                topk_group, renorm, scale, w, ids);
     return launch_status("topk_grouped_kernel");
   }

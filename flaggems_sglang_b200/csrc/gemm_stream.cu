@@ -289,12 +289,14 @@ int pick_ksplit(int64_t items, int64_t kblocks, int elem_bytes) {
     int w = atoi(env);
     if (w == 1 || w == 2 || w == 4 || w == 8) return w;
   }
-  // Measured on B200: with 2-byte elements a warp touches 256 contiguous bytes of a row per step and
-  // HBM streams best when the warps of a CTA walk one row range together (W = 8 gives 2 KB runs).
-  // With 1-byte elements W = 1 measured fastest at every size tried (also with 256-byte chunks), so only
-  // the work-item rule below raises it.
+  // Measured on B200: with 2-byte elements a warp touches 256 contiguous bytes of a row per step and, for long
+  // reductions (Mixtral: 32 and 112 chunks of 128), HBM streams best when the warps of a CTA walk one row range
+  // together (W = 8 gives 2 KB runs).  For short reductions (Qwen3 2048 / 768, the reference's test shape 1280 /
+  // 3072) an 8-way split leaves a warp two chunks and a reduction: W = 2 measured 0.224 -> 0.196 ms at Qwen3 T=32 and
+  // 0.272 -> 0.222 ms at the reference shape T=17; the work-item rule below raises it when a launch has few items
+  // (T=1: W = 4).  With 1-byte elements W = 1 measured fastest at every size tried (also with 256-byte chunks).
   int W = 1;
-  if (elem_bytes == 2) W = kblocks >= 16 ? 8 : (kblocks >= 8 ? 4 : (kblocks >= 4 ? 2 : 1));
+  if (elem_bytes == 2) W = kblocks >= 32 ? 8 : (kblocks >= 4 ? 2 : 1);
   const int64_t target = 148 * 16;
   while (W < kWarps && items * W < target && kblocks / (2 * W) >= 2) W *= 2;
   return W;

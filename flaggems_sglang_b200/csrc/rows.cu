@@ -134,8 +134,8 @@ quant_row_kernel(const __nv_bfloat16* __restrict__ x, int64_t rows_out, int64_t 
   const int lane = threadIdx.x % TEAM;
   const int64_t limit = num_rows_dev ? min((int64_t)*num_rows_dev, rows_out) : rows_out;
   const int vecs = (int)(K / 8);  // 16-byte vectors per row
-  for (int64_t p = (int64_t)blockIdx.x * kTeams + threadIdx.x / TEAM; p < limit || TEAM == 256; p += (int64_t)gridDim.x * kTeams) {
-    if (TEAM == 256 && p >= limit) break;  // uniform over the CTA
+  // p is the same for all threads of a team (TEAM == 256: of the CTA, so the __syncthreads below are uniform)
+  for (int64_t p = (int64_t)blockIdx.x * kTeams + threadIdx.x / TEAM; p < limit; p += (int64_t)gridDim.x * kTeams) {
     const int64_t r = mapped_row(row_map, map_div, sentinel, p);
     uint2* dst = reinterpret_cast<uint2*>(q + p * K);
     if (r < 0) {  // padding position: zeros with a unit scale

@@ -156,3 +156,32 @@ def test_variant_selection_is_shape_only():
     assert _pick_variant(torch.float8_e4m3fn, 512, 256, 2048, 7168, None) == ("stream", 8)   # DSV3 T=64
     assert _pick_variant(torch.float8_e4m3fn, 2048, 256, 2048, 7168, None)[0] == "tcgen05"   # DSV3 T=256
     assert _pick_variant(torch.float8_e4m3fn, 131072, 256, 2048, 7168, None) == ("tcgen05", 128)
+
+
+def test_header_compiles_as_plain_c_and_cpp(tmp_path):
+    """The boundary is a C ABI: the public header must be self-contained C99 (and valid C++), and a C translation unit
+    that fills both argument structs must agree with the ctypes mirrors on their sizes."""
+    import ctypes
+    import shutil
+    import subprocess
+
+    from flaggems_sglang_b200 import _C
+
+    gcc = shutil.which("gcc")
+    if not gcc:
+        pytest.skip("no gcc")
+    header = os.path.join(ROOT, "include", "fmoe_b200.h")
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-fsyntax-only", "-x", "c", header], check=True)
+    gxx = shutil.which("g++")
+    if gxx:
+        subprocess.run([gxx, "-std=c++11", "-Wall", "-Werror", "-fsyntax-only", "-x", "c++", header], check=True)
+    src = tmp_path / "sizes.c"
+    src.write_text('#include <stdio.h>\n#include "fmoe_b200.h"\nint main(void) {\n'
+                   '  fmoe_gemm_args g = {0}; fmoe_fused_args f = {0};\n'
+                   '  g.struct_size = (uint32_t)sizeof g; f.struct_size = (uint32_t)sizeof f;\n'
+                   '  printf("%u %u %d %d\\n", g.struct_size, f.struct_size, FMOE_W_N_MAJOR, FMOE_SCALE_CHANNEL);\n'
+                   '  return 0;\n}\n')
+    exe = tmp_path / "sizes"
+    subprocess.run([gcc, "-std=c99", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert [int(v) for v in out] == [ctypes.sizeof(_C.GemmArgs), ctypes.sizeof(_C.FusedArgs), _C.W_N_MAJOR, _C.SCALE_CHANNEL]
